@@ -1,0 +1,105 @@
+// Error slot, span checks, version and status strings (the GPU-free part of the ABI).
+#include "common.h"
+
+#include <cstdarg>
+#include <cstdio>
+
+#ifndef FLINT_VERSION
+#define FLINT_VERSION "0.1.0"
+#endif
+
+namespace {
+
+// One message per thread; longer messages are truncated.
+thread_local char g_last_error[512] = "";
+
+}  // namespace
+
+namespace fb {
+
+flint_status fail(flint_status status, const char* format, ...) {
+    va_list args;
+    va_start(args, format);
+    std::vsnprintf(g_last_error, sizeof g_last_error, format, args);
+    va_end(args);
+    return status;
+}
+
+flint_status cuda_fail(cudaError_t error, const char* file, int line) {
+    cudaGetLastError();
+    return fail(FLINT_ERROR_CUDA, "%s: %s (%s:%d)", cudaGetErrorName(error),
+                cudaGetErrorString(error), file, line);
+}
+
+flint_status check_spans(const char* function, const Span* spans, size_t count, size_t outputs) {
+    for (size_t i = 0; i < count; ++i) {
+        const Span& s = spans[i];
+        if (s.pointer == nullptr) {
+            return fail(FLINT_ERROR_INVALID_ARGUMENT, "%s: %s is null", function, s.name);
+        }
+        if (!aligned16(s.pointer)) {
+            return fail(FLINT_ERROR_INVALID_ARGUMENT, "%s: %s is not 16-byte aligned", function,
+                        s.name);
+        }
+        if (!fits(s.pointer, s.bytes)) {
+            return fail(FLINT_ERROR_INVALID_ARGUMENT,
+                        "%s: %s runs past the end of the address space", function, s.name);
+        }
+    }
+    for (size_t i = 0; i < outputs && i < count; ++i) {
+        for (size_t j = i + 1; j < count; ++j) {
+            if (overlap(spans[i].pointer, spans[i].bytes, spans[j].pointer, spans[j].bytes)) {
+                return fail(FLINT_ERROR_INVALID_ARGUMENT, "%s: %s and %s overlap", function,
+                            spans[i].name, spans[j].name);
+            }
+        }
+    }
+    return FLINT_OK;
+}
+
+cudaError_t sm_count(int* sms) {
+    constexpr int kMaxDevices = 64;
+    static int cached[kMaxDevices] = {};
+    int device = 0;
+    cudaError_t error = cudaGetDevice(&device);
+    if (error != cudaSuccess) {
+        return error;
+    }
+    if (device >= 0 && device < kMaxDevices && cached[device] > 0) {
+        *sms = cached[device];
+        return cudaSuccess;
+    }
+    int value = 0;
+    error = cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device);
+    if (error != cudaSuccess) {
+        return error;
+    }
+    if (device >= 0 && device < kMaxDevices) {
+        cached[device] = value;
+    }
+    *sms = value;
+    return cudaSuccess;
+}
+
+}  // namespace fb
+
+extern "C" {
+
+const char* flint_version(void) { return FLINT_VERSION; }
+
+const char* flint_status_string(flint_status status) {
+    switch (status) {
+    case FLINT_OK:
+        return "ok";
+    case FLINT_ERROR_INVALID_ARGUMENT:
+        return "invalid argument";
+    case FLINT_ERROR_CUDA:
+        return "CUDA error";
+    default:
+        return "unknown status";
+    }
+}
+
+const char* flint_last_error(void) { return g_last_error; }
+
+}  // extern "C"

@@ -1,0 +1,72 @@
+// Shared host-side plumbing of the C ABI: the per-thread error message, the
+// pointer checks every entry point performs, and small device helpers.
+//
+// The check order and message texts follow the reference's validation layer
+// (src/common/checks.cpp:7-34, src/common/error.cpp:9-21), because callers
+// match on them.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+
+#include <cuda_runtime_api.h>
+
+#include "flint/flint.h"
+
+namespace fb {
+
+// Stores a printf-style message for flint_last_error() and returns status.
+flint_status fail(flint_status status, const char* format, ...)
+    __attribute__((__format__(__printf__, 2, 3)));
+
+// Reports a CUDA runtime error as FLINT_ERROR_CUDA and clears the sticky
+// last-error slot so the next launch does not inherit it.
+flint_status cuda_fail(cudaError_t error, const char* file, int line);
+
+inline bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
+
+inline bool fits(const void* p, size_t bytes) {
+    return bytes <= UINTPTR_MAX - reinterpret_cast<uintptr_t>(p);
+}
+
+inline bool overlap(const void* a, size_t a_bytes, const void* b, size_t b_bytes) {
+    const uintptr_t a0 = reinterpret_cast<uintptr_t>(a);
+    const uintptr_t b0 = reinterpret_cast<uintptr_t>(b);
+    return a0 < b0 + b_bytes && b0 < a0 + a_bytes;
+}
+
+struct Span {
+    const char* name;
+    const void* pointer;
+    size_t bytes;
+};
+
+// In list order: null, then alignment, then address-space fit for every span;
+// only then each of the first `outputs` spans against every later span.
+flint_status check_spans(const char* function, const Span* spans, size_t count, size_t outputs);
+
+template <size_t N>
+flint_status check_spans(const char* function, const Span (&spans)[N], size_t outputs) {
+    return check_spans(function, spans, N, outputs);
+}
+
+// Number of SMs of the current device (cached per device index).
+cudaError_t sm_count(int* sms);
+
+}  // namespace fb
+
+#define FB_CUDA(call)                                                  \
+    do {                                                               \
+        const cudaError_t fb_cuda_error_ = (call);                     \
+        if (fb_cuda_error_ != cudaSuccess) {                           \
+            return ::fb::cuda_fail(fb_cuda_error_, __FILE__, __LINE__); \
+        }                                                              \
+    } while (0)
+
+#define FB_TRY(call)                               \
+    do {                                           \
+        const flint_status fb_status_ = (call);    \
+        if (fb_status_ != FLINT_OK) {              \
+            return fb_status_;                     \
+        }                                          \
+    } while (0)

@@ -1,0 +1,844 @@
+// FP16 x FP16 -> FP32-accumulate GEMMs on the 5th-generation tensor cores:
+// flint_gemm_nt / _nt_bias / _nt_bias_gelu / _nt_bias_residual / _nn / _nn_dgelu /
+// _tn (+ workspace query) and the three batched forms.
+//
+// One persistent, warp-specialised kernel template serves every layout and
+// epilogue:
+//   warp 0      TMA producer: 128-byte-swizzled operand tiles into a shared
+//               memory ring (no cluster multicast), one mbarrier per stage
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16)
+//               from shared-memory descriptors into a tensor-memory accumulator;
+//               tcgen05.commit releases ring stages and publishes accumulators
+//   warps 2-5   epilogue: tcgen05.ld of the FP32 accumulators, the fused
+//               epilogue in registers, predicated global stores
+// Tensor memory holds two accumulators, so the epilogue of tile i overlaps the
+// main loop of tile i+1. Every k-block is 64 wide for every layout, so all
+// variants of a shape add their products in the same order and the batched
+// forms reproduce the plain ones bit for bit.
+//
+// Operand layouts map onto UMMA "major-ness" instead of register transposes:
+// NT reads both operands K-major, NN reads w (k x n) MN-major, TN reads both x
+// (k x m) and w (k x n) MN-major. Ragged edges come from TMA's zero fill.
+//
+// Reference behaviour: src/kernels/gemm.cu:419-587 (main loop and epilogues),
+// :733-784 (split rule) and src/api/gemm.cpp:27-454 (checks and messages).
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <cstdlib>
+#include <cstring>
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+#include "common.h"
+#include "gemm.h"
+#include "sm100.cuh"
+
+namespace fb {
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 4;
+constexpr int kRingBytes = 192 * 1024;
+constexpr int kGroupM = 8;  // rows of tiles handed out together, for L2 reuse
+
+// Set by a kernel whose bounded wait ran out; read by flint_b200_gemm_error().
+__device__ int g_gemm_error = 0;
+
+struct GemmParams {
+    CUtensorMap map_a;
+    CUtensorMap map_b;
+    void* y;
+    void* aux_out;        // bias+GELU: the pre-activation output
+    const void* aux_in;   // dGELU: pre-activations; residual: the FP32 residual
+    const float* bias;
+    float* partials;      // split TN: [split][m][n] FP32
+    int m, n, k;
+    int batches;          // 1 for the plain forms
+    int splits;           // TN only
+    int split_len;        // k per split, a multiple of 64
+    int tiles_m, tiles_n;
+    long long tiles_total;
+    float scale;
+    int accumulate;
+    int batched;
+};
+
+// ---- epilogue math ----------------------------------------------------------------
+
+// GPT-2's tanh GELU written as x * sigmoid(2u), u = sqrt(2/pi) (x + 0.044715 x^3):
+// the same function without the cancellation of 1 + tanh(u) for negative x.
+__device__ __forceinline__ float gelu_tanh(float x) {
+    constexpr float kNeg2Rt2OverPi = -1.5957691216057308f;
+    const float e = expf(kNeg2Rt2OverPi * x * fmaf(0.044715f, x * x, 1.0f));
+    return __fdiv_rn(x, 1.0f + e);
+}
+
+// d/dx of the above: s + x s (1 - s) * 2u', s = sigmoid(2u). For x >= 0,
+// 1 - s is computed as e * s to keep its relative accuracy near s = 1.
+__device__ __forceinline__ float gelu_tanh_grad(float x) {
+    constexpr float kNeg2Rt2OverPi = -1.5957691216057308f;
+    constexpr float k2Rt2OverPi = 1.5957691216057308f;
+    constexpr float k6KappaRt2OverPi = 0.21406444946504453f;  // 2 sqrt(2/pi) * 3 * 0.044715
+    const float e = expf(kNeg2Rt2OverPi * x * fmaf(0.044715f, x * x, 1.0f));
+    const float s = __fdiv_rn(1.0f, 1.0f + e);
+    const float one_minus_s = x < 0.0f ? 1.0f - s : e * s;
+    const float q = x * one_minus_s * fmaf(k6KappaRt2OverPi, x * x, k2Rt2OverPi);
+    const float g = fmaf(s, q, s);
+    return isinf(x) ? (x > 0.0f ? 1.0f : 0.0f) : g;
+}
+
+__device__ __forceinline__ float half_bits_to_float(unsigned short h) {
+    return __half2float(__ushort_as_half(h));
+}
+
+// One output row segment: 32 consecutive columns starting at `col` of row
+// `row`, FP32 accumulators in acc. `valid` = how many of the 32 columns lie
+// inside the matrix.
+template <Epilogue E>
+__device__ __forceinline__ void store_segment(const GemmParams& p, size_t batch_offset,
+                                              long long split, size_t row, int col,
+                                              float (&acc)[32], int valid) {
+    const size_t n = static_cast<size_t>(p.n);
+    const size_t at = batch_offset + row * n + col;
+    if constexpr (E == Epilogue::kBias || E == Epilogue::kBiasGelu ||
+                  E == Epilogue::kBiasResidual) {
+        const float* bias = p.bias + col;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            if (j < valid) {
+                acc[j] = __fadd_rn(acc[j], bias[j]);
+            }
+        }
+    }
+    if constexpr (E == Epilogue::kScale) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            acc[j] = __fmul_rn(acc[j], p.scale);
+        }
+    }
+    if constexpr (E == Epilogue::kDGelu) {
+        const __half* pre = static_cast<const __half*>(p.aux_in) + at;
+        // NN's n is a multiple of 8, so 8-column groups are whole and 16-byte aligned.
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            if (g * 8 < valid) {
+                const uint4 q = *reinterpret_cast<const uint4*>(pre + g * 8);
+                const unsigned w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float lo = half_bits_to_float(static_cast<unsigned short>(w[j]));
+                    const float hi = half_bits_to_float(static_cast<unsigned short>(w[j] >> 16));
+                    acc[g * 8 + 2 * j] = __fmul_rn(acc[g * 8 + 2 * j], gelu_tanh_grad(lo));
+                    acc[g * 8 + 2 * j + 1] = __fmul_rn(acc[g * 8 + 2 * j + 1], gelu_tanh_grad(hi));
+                }
+            }
+        }
+    }
+
+    if constexpr (E == Epilogue::kBiasResidual || E == Epilogue::kTnStore ||
+                  E == Epilogue::kTnPartial) {
+        // FP32 outputs.
+        float* out;
+        if constexpr (E == Epilogue::kTnPartial) {
+            out = p.partials + static_cast<size_t>(split) * p.m * n + row * n + col;
+        } else {
+            out = static_cast<float*>(p.y) + at;
+        }
+        const float* res = E == Epilogue::kBiasResidual
+                               ? static_cast<const float*>(p.aux_in) + at
+                               : out;
+        const bool add = E == Epilogue::kBiasResidual || (E == Epilogue::kTnStore && p.accumulate);
+        if (p.n % 4 == 0) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+                if (g * 4 < valid) {
+                    float4 v = make_float4(acc[4 * g], acc[4 * g + 1], acc[4 * g + 2],
+                                           acc[4 * g + 3]);
+                    if (add) {
+                        const float4 o = *reinterpret_cast<const float4*>(res + 4 * g);
+                        v = make_float4(__fadd_rn(o.x, v.x), __fadd_rn(o.y, v.y),
+                                        __fadd_rn(o.z, v.z), __fadd_rn(o.w, v.w));
+                    }
+                    *reinterpret_cast<float4*>(out + 4 * g) = v;
+                }
+            }
+        } else {
+            // n even (the residual form's only requirement): 8-byte pairs.
+#pragma unroll
+            for (int g = 0; g < 16; ++g) {
+                if (g * 2 < valid) {
+                    float2 v = make_float2(acc[2 * g], acc[2 * g + 1]);
+                    if (add) {
+                        const float2 o = *reinterpret_cast<const float2*>(res + 2 * g);
+                        v = make_float2(__fadd_rn(o.x, v.x), __fadd_rn(o.y, v.y));
+                    }
+                    *reinterpret_cast<float2*>(out + 2 * g) = v;
+                }
+            }
+        }
+        return;
+    } else {
+        // FP16 outputs; the GELU form writes the pre-activation too.
+        __half* out = static_cast<__half*>(p.y) + at;
+        __half* pre_out = nullptr;
+        if constexpr (E == Epilogue::kBiasGelu) {
+            pre_out = static_cast<__half*>(p.aux_out) + at;
+        }
+        if (p.n % 8 == 0) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                if (g * 8 < valid) {
+                    uint4 q;
+                    unsigned* w = reinterpret_cast<unsigned*>(&q);
+                    if constexpr (E == Epilogue::kBiasGelu) {
+                        uint4 qp;
+                        unsigned* wp = reinterpret_cast<unsigned*>(&qp);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float a = acc[g * 8 + 2 * j];
+                            const float b = acc[g * 8 + 2 * j + 1];
+                            const __half2 hp = __floats2half2_rn(a, b);
+                            const __half2 hy = __floats2half2_rn(gelu_tanh(a), gelu_tanh(b));
+                            wp[j] = *reinterpret_cast<const unsigned*>(&hp);
+                            w[j] = *reinterpret_cast<const unsigned*>(&hy);
+                        }
+                        *reinterpret_cast<uint4*>(pre_out + g * 8) = qp;
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const __half2 h =
+                                __floats2half2_rn(acc[g * 8 + 2 * j], acc[g * 8 + 2 * j + 1]);
+                            w[j] = *reinterpret_cast<const unsigned*>(&h);
+                        }
+                    }
+                    *reinterpret_cast<uint4*>(out + g * 8) = q;
+                }
+            }
+        } else {
+            // Any n (NT allows odd n): rows are only 2-byte aligned.
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                if (j < valid) {
+                    if constexpr (E == Epilogue::kBiasGelu) {
+                        pre_out[j] = __float2half_rn(acc[j]);
+                        out[j] = __float2half_rn(gelu_tanh(acc[j]));
+                    } else {
+                        out[j] = __float2half_rn(acc[j]);
+                    }
+                }
+            }
+        }
+    }
+}
+
+// ---- the tensor-core kernel --------------------------------------------------------------
+
+template <int BN>
+struct Ring {
+    static constexpr int kStageA = kBM * kBK * 2;
+    static constexpr int kStageB = BN * kBK * 2;
+    static constexpr int kStage = kStageA + kStageB;
+    static constexpr int kStages = kRingBytes / kStage;
+    // ring + barriers + the 1,024-byte alignment slack
+    static constexpr int kSmemBytes = kStages * kStage + 1024 + 256;
+};
+
+struct TileCoord {
+    long long z;  // batch (batched forms) or split (TN)
+    int tm, tn;
+};
+
+__device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, long long id) {
+    const long long per = static_cast<long long>(p.tiles_m) * p.tiles_n;
+    TileCoord c;
+    c.z = id / per;
+    const long long r = id - c.z * per;
+    const long long group_span = static_cast<long long>(kGroupM) * p.tiles_n;
+    const long long g = r / group_span;
+    const int first_m = static_cast<int>(g) * kGroupM;
+    const int rows_here = min(kGroupM, p.tiles_m - first_m);
+    const long long in_group = r - g * group_span;
+    c.tm = first_m + static_cast<int>(in_group % rows_here);
+    c.tn = static_cast<int>(in_group / rows_here);
+    return c;
+}
+
+template <Layout L, Epilogue E, int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+    fb_gemm_tc(const __grid_constant__ GemmParams p) {
+    using R = Ring<BN>;
+    constexpr bool kAMn = L == Layout::kTN;
+    constexpr bool kBMn = L != Layout::kNT;
+    constexpr bool kIsTn = L == Layout::kTN;
+    constexpr uint32_t kIdesc = sm100::instr_desc_f16(kBM, BN, kAMn, kBMn);
+    constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t smem_base = (sm100::smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bars = smem_base + R::kStages * R::kStage;
+    // barrier slots (8 bytes each): full[kStages], empty[kStages], acc_full[2], acc_empty[2]
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (R::kStages + s); };
+    auto acc_full_bar = [&](int a) { return bars + 8u * (2 * R::kStages + a); };
+    auto acc_empty_bar = [&](int a) { return bars + 8u * (2 * R::kStages + 2 + a); };
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x / 32;
+    const int lane = threadIdx.x % 32;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < R::kStages; ++s) {
+            sm100::mbar_init(full_bar(s), 1);
+            sm100::mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            sm100::mbar_init(acc_full_bar(a), 1);
+            sm100::mbar_init(acc_empty_bar(a), kEpilogueWarps);
+        }
+        sm100::mbar_fence_init();
+        sm100::tma_prefetch_descriptor(&p.map_a);
+        sm100::tma_prefetch_descriptor(&p.map_b);
+    }
+    if (warp == 1) {
+        sm100::tmem_alloc(sm100::smem_u32(&tmem_base_slot), kTmemCols);
+    }
+    sm100::tc_fence_before_sync();
+    __syncthreads();
+    sm100::tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_slot;
+    volatile int* abort = &abort_flag;
+
+    if (warp == 0) {
+        // ---- TMA producer ----
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (long long id = blockIdx.x; ok && id < p.tiles_total; id += gridDim.x) {
+                const TileCoord t = decode_tile(p, id);
+                const bool split_k = kIsTn && !p.batched;
+                const int k0 = split_k ? static_cast<int>(t.z) * p.split_len : 0;
+                const int k1 = split_k ? min(p.k, k0 + p.split_len) : p.k;
+                const int batch = p.batched ? static_cast<int>(t.z) : 0;
+                const int row_a = t.tm * kBM;
+                const int row_b = t.tn * BN;
+                for (int kk = k0; kk < k1; kk += kBK) {
+                    if (!sm100::mbar_wait(empty_bar(stage), phase ^ 1u, abort)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t a_dst = smem_base + stage * R::kStage;
+                    const uint32_t b_dst = a_dst + R::kStageA;
+                    const uint32_t bar = full_bar(stage);
+                    sm100::mbar_expect_tx(bar, R::kStage);
+                    if constexpr (!kAMn) {
+                        if (p.batched) {
+                            sm100::tma_load_3d(a_dst, &p.map_a, bar, kk, row_a, batch);
+                        } else {
+                            sm100::tma_load_2d(a_dst, &p.map_a, bar, kk, row_a);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < kBM / 64; ++j) {
+                            if (p.batched) {
+                                sm100::tma_load_3d(a_dst + j * 8192, &p.map_a, bar, row_a + 64 * j,
+                                                   kk, batch);
+                            } else {
+                                sm100::tma_load_2d(a_dst + j * 8192, &p.map_a, bar, row_a + 64 * j,
+                                                   kk);
+                            }
+                        }
+                    }
+                    if constexpr (!kBMn) {
+                        if (p.batched) {
+                            sm100::tma_load_3d(b_dst, &p.map_b, bar, kk, row_b, batch);
+                        } else {
+                            sm100::tma_load_2d(b_dst, &p.map_b, bar, kk, row_b);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j) {
+                            if (p.batched) {
+                                sm100::tma_load_3d(b_dst + j * 8192, &p.map_b, bar, row_b + 64 * j,
+                                                   kk, batch);
+                            } else {
+                                sm100::tma_load_2d(b_dst + j * 8192, &p.map_b, bar, row_b + 64 * j,
+                                                   kk);
+                            }
+                        }
+                    }
+                    if (++stage == R::kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer ----
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (long long id = blockIdx.x; ok && id < p.tiles_total; id += gridDim.x) {
+                const TileCoord t = decode_tile(p, id);
+                const bool split_k = kIsTn && !p.batched;
+                const int k0 = split_k ? static_cast<int>(t.z) * p.split_len : 0;
+                const int k1 = split_k ? min(p.k, k0 + p.split_len) : p.k;
+                if (!sm100::mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort)) {
+                    ok = false;
+                    break;
+                }
+                sm100::tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+                uint32_t accumulate = 0;
+                for (int kk = k0; kk < k1; kk += kBK) {
+                    if (!sm100::mbar_wait(full_bar(stage), phase, abort)) {
+                        ok = false;
+                        break;
+                    }
+                    sm100::tc_fence_after_sync();
+                    const uint32_t a_addr = smem_base + stage * R::kStage;
+                    const uint32_t b_addr = a_addr + R::kStageA;
+#pragma unroll
+                    for (int ks = 0; ks < kBK / 16; ++ks) {
+                        // K-major: 16 halves = 32 bytes along the swizzled row.
+                        // MN-major: 16 k-rows of 128 bytes.
+                        const uint64_t a_desc =
+                            kAMn ? sm100::smem_desc_sw128(a_addr + ks * 2048, 8192, 1024)
+                                 : sm100::smem_desc_sw128(a_addr + ks * 32, 16, 1024);
+                        const uint64_t b_desc =
+                            kBMn ? sm100::smem_desc_sw128(b_addr + ks * 2048, 8192, 1024)
+                                 : sm100::smem_desc_sw128(b_addr + ks * 32, 16, 1024);
+                        sm100::mma_f16_ss(d_tmem, a_desc, b_desc, kIdesc, accumulate);
+                        accumulate = 1;
+                    }
+                    sm100::mma_commit(empty_bar(stage));
+                    if (++stage == R::kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) {
+                    break;
+                }
+                sm100::mma_commit(acc_full_bar(acc));
+                acc ^= 1;
+                if (acc == 0) {
+                    acc_phase ^= 1u;
+                }
+            }
+        }
+    } else {
+        // ---- epilogue warps ----
+        const int quadrant = warp % 4;  // the TMEM lanes this warp may read
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (long long id = blockIdx.x; ok && id < p.tiles_total; id += gridDim.x) {
+            const TileCoord t = decode_tile(p, id);
+            if (!sm100::mbar_wait(acc_full_bar(acc), acc_phase, abort)) {
+                ok = false;
+                break;
+            }
+            sm100::tc_fence_after_sync();
+            const size_t row = static_cast<size_t>(t.tm) * kBM + quadrant * 32 + lane;
+            const bool row_ok = row < static_cast<size_t>(p.m);
+            const int col0 = t.tn * BN;
+            const size_t batch_offset =
+                p.batched ? static_cast<size_t>(t.z) * p.m * static_cast<size_t>(p.n) : 0;
+            const uint32_t t_addr = tmem_base + static_cast<uint32_t>(acc * BN) +
+                                    (static_cast<uint32_t>(quadrant * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                const bool last = c + 32 >= BN;
+                const int col = col0 + c;
+                const int valid = min(32, p.n - col);  // warp-uniform
+                uint32_t raw[32];
+                if (valid > 0) {
+                    sm100::tmem_ld_32x32(t_addr + c, raw);
+                    sm100::tmem_ld_wait();
+                }
+                if (last) {
+                    // Every read of this accumulator is complete: hand it back.
+                    sm100::tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) {
+                        sm100::mbar_arrive(acc_empty_bar(acc));
+                    }
+                }
+                if (valid > 0 && row_ok) {
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        v[j] = __uint_as_float(raw[j]);
+                    }
+                    store_segment<E>(p, batch_offset, t.z, row, col, v, valid);
+                }
+            }
+            acc ^= 1;
+            if (acc == 0) {
+                acc_phase ^= 1u;
+            }
+        }
+    }
+
+    // ---- teardown ----
+    __syncthreads();
+    if (abort_flag != 0) {
+        if (threadIdx.x == 0) {
+            atomicExch(&g_gemm_error, 1);
+        }
+        // Let any TMA copy still in flight land before shared memory is released.
+        const long long start = clock64();
+        while (clock64() - start < 2000000LL) {
+        }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        sm100::tc_fence_after_sync();
+        sm100::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---- plain CUDA-core kernel, for debugging the pipeline only -------------------------
+//
+// Selected with FLINT_B200_GEMM=simt in the environment; never the default.
+
+template <Layout L, Epilogue E>
+__global__ void __launch_bounds__(256)
+    fb_gemm_simt(GemmParams p, const __half* __restrict__ x, const __half* __restrict__ w) {
+    const long long total = static_cast<long long>(p.batches) * p.m * p.n;
+    for (long long i = blockIdx.x * 256LL + threadIdx.x; i < total; i += gridDim.x * 256LL) {
+        const long long b = i / (static_cast<long long>(p.m) * p.n);
+        const long long r = i - b * p.m * p.n;
+        const int row = static_cast<int>(r / p.n);
+        const int col = static_cast<int>(r % p.n);
+        const __half* xb = x + b * p.m * p.k;
+        const __half* wb = w + b * p.n * p.k;
+        float acc = 0.0f;
+        for (int kk = 0; kk < p.k; ++kk) {
+            float a;
+            float c;
+            if (L == Layout::kTN) {
+                a = __half2float(xb[static_cast<size_t>(kk) * p.m + row]);
+            } else {
+                a = __half2float(xb[static_cast<size_t>(row) * p.k + kk]);
+            }
+            if (L == Layout::kNT) {
+                c = __half2float(wb[static_cast<size_t>(col) * p.k + kk]);
+            } else {
+                c = __half2float(wb[static_cast<size_t>(kk) * p.n + col]);
+            }
+            acc = fmaf(a, c, acc);
+        }
+        const size_t at = static_cast<size_t>(b) * p.m * p.n + static_cast<size_t>(row) * p.n + col;
+        if (E == Epilogue::kBias || E == Epilogue::kBiasGelu || E == Epilogue::kBiasResidual) {
+            acc = __fadd_rn(acc, p.bias[col]);
+        }
+        if (E == Epilogue::kScale) {
+            acc = __fmul_rn(acc, p.scale);
+        }
+        if (E == Epilogue::kDGelu) {
+            acc = __fmul_rn(acc, gelu_tanh_grad(__half2float(static_cast<const __half*>(p.aux_in)[at])));
+        }
+        if (E == Epilogue::kBiasResidual) {
+            static_cast<float*>(p.y)[at] = __fadd_rn(static_cast<const float*>(p.aux_in)[at], acc);
+        } else if (E == Epilogue::kTnStore) {
+            float* out = static_cast<float*>(p.y) + at;
+            *out = p.accumulate ? __fadd_rn(*out, acc) : acc;
+        } else if (E == Epilogue::kBiasGelu) {
+            static_cast<__half*>(p.aux_out)[at] = __float2half_rn(acc);
+            static_cast<__half*>(p.y)[at] = __float2half_rn(gelu_tanh(acc));
+        } else {
+            static_cast<__half*>(p.y)[at] = __float2half_rn(acc);
+        }
+    }
+}
+
+// y = (old +) p0 + p1 + ... in split order.
+__global__ void __launch_bounds__(256)
+    fb_gemm_tn_reduce(float4* __restrict__ y, const float4* __restrict__ partials, size_t quads,
+                      int splits, int accumulate) {
+    for (size_t i = size_t{blockIdx.x} * 256 + threadIdx.x; i < quads;
+         i += size_t{gridDim.x} * 256) {
+        float4 s = partials[i];
+        for (int k = 1; k < splits; ++k) {
+            const float4 v = partials[static_cast<size_t>(k) * quads + i];
+            s = make_float4(__fadd_rn(s.x, v.x), __fadd_rn(s.y, v.y), __fadd_rn(s.z, v.z),
+                            __fadd_rn(s.w, v.w));
+        }
+        if (accumulate) {
+            const float4 o = y[i];
+            s = make_float4(__fadd_rn(o.x, s.x), __fadd_rn(o.y, s.y), __fadd_rn(o.z, s.z),
+                            __fadd_rn(o.w, s.w));
+        }
+        y[i] = s;
+    }
+}
+
+// ---- host side ----------------------------------------------------------------------------
+
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                 const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+cudaError_t encode_fn(EncodeTiled* out) {
+    static EncodeTiled cached = nullptr;
+    if (cached == nullptr) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult status;
+        const cudaError_t e =
+            cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &status);
+        if (e != cudaSuccess) {
+            return e;
+        }
+        if (status != cudaDriverEntryPointSuccess || fn == nullptr) {
+            return cudaErrorNotSupported;
+        }
+        cached = reinterpret_cast<EncodeTiled>(fn);
+    }
+    *out = cached;
+    return cudaSuccess;
+}
+
+// A row-major FP16 matrix [outer][inner] (inner contiguous), optionally
+// repeated `batches` times back to back; boxes are 64 inner elements (one
+// 128-byte swizzle row) by box_outer rows.
+cudaError_t make_map(CUtensorMap* map, const void* base, size_t inner, size_t outer,
+                     size_t batches, bool batched, int box_outer) {
+    EncodeTiled encode = nullptr;
+    cudaError_t e = encode_fn(&encode);
+    if (e != cudaSuccess) {
+        return e;
+    }
+    const cuuint64_t dims[3] = {inner, outer, batches};
+    const cuuint64_t strides[2] = {inner * 2, inner * outer * 2};
+    const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_outer), 1};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, batched ? 3 : 2,
+                              const_cast<void*>(base), dims, strides, box, elem,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+bool use_simt() {
+    static int cached = -1;
+    if (cached < 0) {
+        const char* v = std::getenv("FLINT_B200_GEMM");
+        cached = (v != nullptr && std::strcmp(v, "simt") == 0) ? 1 : 0;
+    }
+    return cached == 1;
+}
+
+int pick_bn(size_t n) { return n > 128 ? 256 : (n > 64 ? 128 : 64); }
+
+template <Layout L, Epilogue E, int BN>
+cudaError_t launch_tc(GemmParams& p, const void* x, const void* w, int sms, cudaStream_t stream) {
+    using R = Ring<BN>;
+    constexpr bool kAMn = L == Layout::kTN;
+    constexpr bool kBMn = L != Layout::kNT;
+    const bool batched = p.batched != 0;
+    cudaError_t e;
+    if (kAMn) {
+        e = make_map(&p.map_a, x, p.m, p.k, p.batches, batched, kBK);
+    } else {
+        e = make_map(&p.map_a, x, p.k, p.m, p.batches, batched, kBM);
+    }
+    if (e != cudaSuccess) {
+        return e;
+    }
+    if (kBMn) {
+        e = make_map(&p.map_b, w, p.n, p.k, p.batches, batched, kBK);
+    } else {
+        e = make_map(&p.map_b, w, p.k, p.n, p.batches, batched, BN);
+    }
+    if (e != cudaSuccess) {
+        return e;
+    }
+    p.tiles_m = (p.m + kBM - 1) / kBM;
+    p.tiles_n = (p.n + BN - 1) / BN;
+    const long long z = L == Layout::kTN && !batched ? p.splits : p.batches;
+    p.tiles_total = static_cast<long long>(p.tiles_m) * p.tiles_n * z;
+
+    static bool configured = false;
+    auto kernel = fb_gemm_tc<L, E, BN>;
+    if (!configured) {
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 R::kSmemBytes);
+        if (e != cudaSuccess) {
+            return e;
+        }
+        configured = true;
+    }
+    const unsigned grid = static_cast<unsigned>(std::min<long long>(p.tiles_total, sms));
+    kernel<<<grid, kThreads, R::kSmemBytes, stream>>>(p);
+    return cudaGetLastError();
+}
+
+template <Layout L, Epilogue E>
+cudaError_t launch_any(GemmParams& p, const void* x, const void* w, cudaStream_t stream) {
+    int sms = 0;
+    cudaError_t e = sm_count(&sms);
+    if (e != cudaSuccess) {
+        return e;
+    }
+    if (use_simt()) {
+        const long long total = static_cast<long long>(p.batches) * p.m * p.n;
+        const unsigned grid =
+            static_cast<unsigned>(std::min<long long>((total + 255) / 256, sms * 32LL));
+        fb_gemm_simt<L, E><<<grid, 256, 0, stream>>>(p, static_cast<const __half*>(x),
+                                                     static_cast<const __half*>(w));
+        return cudaGetLastError();
+    }
+    switch (pick_bn(static_cast<size_t>(p.n))) {
+    case 256:
+        return launch_tc<L, E, 256>(p, x, w, sms, stream);
+    case 128:
+        return launch_tc<L, E, 128>(p, x, w, sms, stream);
+    default:
+        return launch_tc<L, E, 64>(p, x, w, sms, stream);
+    }
+}
+
+GemmParams base_params(void* y, size_t m, size_t n, size_t k, size_t batches, bool batched) {
+    GemmParams p;
+    std::memset(&p, 0, sizeof p);
+    p.y = y;
+    p.m = static_cast<int>(m);
+    p.n = static_cast<int>(n);
+    p.k = static_cast<int>(k);
+    p.batches = static_cast<int>(batches);
+    p.batched = batched ? 1 : 0;
+    p.splits = 1;
+    p.split_len = static_cast<int>((k + kBK - 1) / kBK * kBK);
+    p.scale = 1.0f;
+    return p;
+}
+
+}  // namespace
+
+// ---- internal launchers (declared in gemm.h) --------------------------------------------
+
+TnSplit tn_split(size_t m, size_t n, size_t k, int sms) {
+    const long long tiles = static_cast<long long>((m + kBM - 1) / kBM) *
+                            static_cast<long long>((n + pick_bn(n) - 1) / pick_bn(n));
+    const long long slots = sms;
+    const int most = static_cast<int>(std::min<size_t>(16, std::max<size_t>(1, k / 1024)));
+    int want = 1;
+    double best = 0.0;
+    for (int s = 1; s <= most; ++s) {
+        const long long blocks = tiles * s;
+        const long long waves = (blocks + slots - 1) / slots;
+        const double fill = static_cast<double>(blocks) / static_cast<double>(waves * slots);
+        if (fill > best) {
+            best = fill;
+            want = s;
+        }
+        if (fill >= 0.75) {
+            want = s;
+            break;
+        }
+    }
+    const size_t per = (k + want - 1) / want;
+    TnSplit r;
+    r.len = static_cast<int>((per + kBK - 1) / kBK * kBK);
+    r.count = static_cast<int>((k + r.len - 1) / r.len);
+    return r;
+}
+
+cudaError_t gemm_nt(Epilogue e, void* y, void* pre, const void* x, const void* w,
+                    const void* bias, const void* residual, size_t m, size_t n, size_t k,
+                    cudaStream_t stream) {
+    GemmParams p = base_params(y, m, n, k, 1, false);
+    p.bias = static_cast<const float*>(bias);
+    p.aux_out = pre;
+    p.aux_in = residual;
+    switch (e) {
+    case Epilogue::kNone:
+        return launch_any<Layout::kNT, Epilogue::kNone>(p, x, w, stream);
+    case Epilogue::kBias:
+        return launch_any<Layout::kNT, Epilogue::kBias>(p, x, w, stream);
+    case Epilogue::kBiasGelu:
+        return launch_any<Layout::kNT, Epilogue::kBiasGelu>(p, x, w, stream);
+    case Epilogue::kBiasResidual:
+        return launch_any<Layout::kNT, Epilogue::kBiasResidual>(p, x, w, stream);
+    default:
+        return cudaErrorInvalidValue;
+    }
+}
+
+cudaError_t gemm_nn(Epilogue e, void* y, const void* x, const void* w, const void* pre, size_t m,
+                    size_t n, size_t k, cudaStream_t stream) {
+    GemmParams p = base_params(y, m, n, k, 1, false);
+    p.aux_in = pre;
+    if (e == Epilogue::kDGelu) {
+        return launch_any<Layout::kNN, Epilogue::kDGelu>(p, x, w, stream);
+    }
+    return launch_any<Layout::kNN, Epilogue::kNone>(p, x, w, stream);
+}
+
+cudaError_t gemm_tn(void* y, const void* x, const void* w, size_t m, size_t n, size_t k,
+                    bool accumulate, void* workspace, cudaStream_t stream) {
+    int sms = 0;
+    cudaError_t e = sm_count(&sms);
+    if (e != cudaSuccess) {
+        return e;
+    }
+    GemmParams p = base_params(y, m, n, k, 1, false);
+    p.accumulate = accumulate ? 1 : 0;
+    const TnSplit s = use_simt() ? TnSplit{1, p.split_len} : tn_split(m, n, k, sms);
+    if (s.count == 1) {
+        return launch_any<Layout::kTN, Epilogue::kTnStore>(p, x, w, stream);
+    }
+    p.splits = s.count;
+    p.split_len = s.len;
+    p.partials = static_cast<float*>(workspace);
+    e = launch_any<Layout::kTN, Epilogue::kTnPartial>(p, x, w, stream);
+    if (e != cudaSuccess) {
+        return e;
+    }
+    const size_t quads = m * n / 4;
+    const unsigned grid =
+        static_cast<unsigned>(std::min<size_t>((quads + 255) / 256, static_cast<size_t>(sms) * 8));
+    fb_gemm_tn_reduce<<<grid, 256, 0, stream>>>(static_cast<float4*>(y),
+                                                static_cast<const float4*>(workspace), quads,
+                                                s.count, p.accumulate);
+    return cudaGetLastError();
+}
+
+cudaError_t gemm_batched(Layout l, void* y, const void* x, const void* w, size_t batches,
+                         size_t m, size_t n, size_t k, float scale, cudaStream_t stream) {
+    GemmParams p = base_params(y, m, n, k, batches, true);
+    p.scale = scale;
+    switch (l) {
+    case Layout::kNT:
+        return launch_any<Layout::kNT, Epilogue::kScale>(p, x, w, stream);
+    case Layout::kNN:
+        return launch_any<Layout::kNN, Epilogue::kNone>(p, x, w, stream);
+    default:
+        return launch_any<Layout::kTN, Epilogue::kNone>(p, x, w, stream);
+    }
+}
+
+cudaError_t gemm_error_flag(int* value, bool reset) {
+    cudaError_t e = cudaMemcpyFromSymbol(value, g_gemm_error, sizeof(int));
+    if (e == cudaSuccess && reset && *value != 0) {
+        const int zero = 0;
+        e = cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int));
+    }
+    return e;
+}
+
+}  // namespace fb

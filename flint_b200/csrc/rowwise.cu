@@ -1,0 +1,632 @@
+// Row-wise entry points: flint_layernorm_forward, flint_causal_softmax_forward,
+// flint_causal_softmax_backward and flint_softmax_cross_entropy.
+//
+// Each kernel reads its row from HBM once. LayerNorm and the attention
+// softmax keep a row in the registers of one warp (GPT-2's rows are 768 FP32
+// and at most 1,024 FP16 values); the cross-entropy stages a 100 KB row of
+// logits in shared memory for its three passes. Sums run in FP32 with
+// compensated (TwoSum) accumulation where the reference does, in the same
+// lane order, so statistics match it to the bit where its tests pin them:
+// src/kernels/layernorm.cu:105-155, src/kernels/softmax.cu:68-122,
+// src/kernels/softmax_backward.cu:111-154, src/kernels/cross_entropy.cu:106-172.
+//
+// Argument checks follow src/api/layernorm.cpp:11-51, src/api/softmax.cpp:11-76
+// and src/api/cross_entropy.cpp:9-49.
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+
+#include <cuda_fp16.h>
+
+#include "common.h"
+#include "device_utils.cuh"
+
+namespace {
+
+using fb::Comp;
+
+constexpr int kWarpsPerBlock = 8;
+constexpr int kThreads = 32 * kWarpsPerBlock;
+constexpr size_t kMaxRows8 = size_t{0x7fffffff} * 8;
+
+// ---- LayerNorm forward -----------------------------------------------------------
+
+// Rows of up to 128 * kQuads values with cols % 4 == 0: the warp holds the row
+// in registers, lane l owning float4 groups l, l + 32, ...
+template <int kQuads>
+__global__ void __launch_bounds__(kThreads)
+    fb_layernorm_forward_regs(__half* __restrict__ y, float* __restrict__ mean,
+                              float* __restrict__ rstd, const float* __restrict__ x,
+                              const float* __restrict__ gamma, const float* __restrict__ beta,
+                              size_t rows, int cols, float eps) {
+    const size_t row = size_t{blockIdx.x} * kWarpsPerBlock + threadIdx.x / 32;
+    if (row >= rows) {
+        return;
+    }
+    const int lane = threadIdx.x % 32;
+    const int groups = cols / 4;
+    const float4* xr = reinterpret_cast<const float4*>(x + row * cols);
+    float4 v[kQuads];
+#pragma unroll
+    for (int j = 0; j < kQuads; ++j) {
+        const int i = lane + 32 * j;
+        v[j] = i < groups ? xr[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    const float n = static_cast<float>(cols);
+
+    Comp sum;
+#pragma unroll
+    for (int j = 0; j < kQuads; ++j) {
+        if (lane + 32 * j < groups) {
+            fb::comp_add(sum, v[j].x);
+            fb::comp_add(sum, v[j].y);
+            fb::comp_add(sum, v[j].z);
+            fb::comp_add(sum, v[j].w);
+        }
+    }
+    sum = fb::comp_warp_merge(sum);
+    const float m = __fdiv_rn(__fadd_rn(sum.s, sum.e), n);
+
+    Comp sq;
+#pragma unroll
+    for (int j = 0; j < kQuads; ++j) {
+        if (lane + 32 * j < groups) {
+            const float d0 = __fsub_rn(v[j].x, m);
+            const float d1 = __fsub_rn(v[j].y, m);
+            const float d2 = __fsub_rn(v[j].z, m);
+            const float d3 = __fsub_rn(v[j].w, m);
+            fb::comp_add_product(sq, d0, d0);
+            fb::comp_add_product(sq, d1, d1);
+            fb::comp_add_product(sq, d2, d2);
+            fb::comp_add_product(sq, d3, d3);
+        }
+    }
+    sq = fb::comp_warp_merge(sq);
+    const float var = __fdiv_rn(__fadd_rn(sq.s, sq.e), n);
+    const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, eps)));
+
+    const float4* g4 = reinterpret_cast<const float4*>(gamma);
+    const float4* b4 = reinterpret_cast<const float4*>(beta);
+    uint2* yr = reinterpret_cast<uint2*>(y + row * cols);
+#pragma unroll
+    for (int j = 0; j < kQuads; ++j) {
+        const int i = lane + 32 * j;
+        if (i < groups) {
+            const float4 g = g4[i];
+            const float4 b = b4[i];
+            const float o0 = fmaf(__fmul_rn(__fsub_rn(v[j].x, m), r), g.x, b.x);
+            const float o1 = fmaf(__fmul_rn(__fsub_rn(v[j].y, m), r), g.y, b.y);
+            const float o2 = fmaf(__fmul_rn(__fsub_rn(v[j].z, m), r), g.z, b.z);
+            const float o3 = fmaf(__fmul_rn(__fsub_rn(v[j].w, m), r), g.w, b.w);
+            yr[i] = make_uint2(fb::pack2(o0, o1), fb::pack2(o2, o3));
+        }
+    }
+    if (lane == 0) {
+        mean[row] = m;
+        rstd[row] = r;
+    }
+}
+
+// Any width: three passes over the row in global memory (the later ones hit
+// L1/L2). kVec is 4 when cols % 4 == 0, else 1.
+template <int kVec>
+__global__ void __launch_bounds__(kThreads)
+    fb_layernorm_forward_stream(__half* __restrict__ y, float* __restrict__ mean,
+                                float* __restrict__ rstd, const float* __restrict__ x,
+                                const float* __restrict__ gamma, const float* __restrict__ beta,
+                                size_t rows, int cols, float eps) {
+    const size_t row = size_t{blockIdx.x} * kWarpsPerBlock + threadIdx.x / 32;
+    if (row >= rows) {
+        return;
+    }
+    const int lane = threadIdx.x % 32;
+    const float* xr = x + row * cols;
+    __half* yr = y + row * cols;
+    const int groups = cols / kVec;
+    const float n = static_cast<float>(cols);
+
+    auto load = [&](const float* p, int i, float (&f)[kVec]) {
+        if constexpr (kVec == 4) {
+            const float4 q = reinterpret_cast<const float4*>(p)[i];
+            f[0] = q.x;
+            f[1] = q.y;
+            f[2] = q.z;
+            f[3] = q.w;
+        } else {
+            f[0] = p[i];
+        }
+    };
+
+    Comp sum;
+    for (int i = lane; i < groups; i += 32) {
+        float f[kVec];
+        load(xr, i, f);
+#pragma unroll
+        for (int j = 0; j < kVec; ++j) {
+            fb::comp_add(sum, f[j]);
+        }
+    }
+    sum = fb::comp_warp_merge(sum);
+    const float m = __fdiv_rn(__fadd_rn(sum.s, sum.e), n);
+
+    Comp sq;
+    for (int i = lane; i < groups; i += 32) {
+        float f[kVec];
+        load(xr, i, f);
+#pragma unroll
+        for (int j = 0; j < kVec; ++j) {
+            const float d = __fsub_rn(f[j], m);
+            fb::comp_add_product(sq, d, d);
+        }
+    }
+    sq = fb::comp_warp_merge(sq);
+    const float var = __fdiv_rn(__fadd_rn(sq.s, sq.e), n);
+    const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, eps)));
+
+    for (int i = lane; i < groups; i += 32) {
+        float f[kVec];
+        float g[kVec];
+        float b[kVec];
+        load(xr, i, f);
+        load(gamma, i, g);
+        load(beta, i, b);
+#pragma unroll
+        for (int j = 0; j < kVec; ++j) {
+            f[j] = fmaf(__fmul_rn(__fsub_rn(f[j], m), r), g[j], b[j]);
+        }
+        if constexpr (kVec == 4) {
+            reinterpret_cast<uint2*>(yr)[i] =
+                make_uint2(fb::pack2(f[0], f[1]), fb::pack2(f[2], f[3]));
+        } else {
+            yr[i] = __float2half_rn(f[0]);
+        }
+    }
+    if (lane == 0) {
+        mean[row] = m;
+        rstd[row] = r;
+    }
+}
+
+// ---- causal softmax ------------------------------------------------------------------
+
+constexpr int kMaxChunksPerLane = 4;  // 1024 columns / 8 per chunk / 32 lanes
+
+// A warp per row; lane l owns the 16-byte chunks l, l + 32, l + 64, l + 96.
+template <int kChunks>
+__global__ void __launch_bounds__(kThreads)
+    fb_causal_softmax_forward(uint4* __restrict__ p, const uint4* __restrict__ s, size_t rows,
+                              int length) {
+    const size_t row = size_t{blockIdx.x} * kWarpsPerBlock + threadIdx.x / 32;
+    if (row >= rows) {
+        return;
+    }
+    const int lane = threadIdx.x % 32;
+    const int chunks = length / 8;
+    const int t = static_cast<int>(row % static_cast<size_t>(length));
+    const int visible_chunks = t / 8 + 1;
+    const uint4* sr = s + row * chunks;
+    uint4* pr = p + row * chunks;
+
+    float v[kChunks][8];
+    int count[kChunks];  // visible values of each owned chunk (0 when masked)
+#pragma unroll
+    for (int j = 0; j < kChunks; ++j) {
+        const int i = lane + 32 * j;
+        count[j] = i < visible_chunks ? min(t + 1 - i * 8, 8) : 0;
+        if (count[j] > 0) {
+            fb::unpack8(v[j], sr[i]);
+        }
+    }
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < kChunks; ++j) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            if (c < count[j]) {
+                mx = fmaxf(mx, v[j][c]);
+            }
+        }
+    }
+    mx = fb::warp_max(mx);
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kChunks; ++j) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            if (c < count[j]) {
+                v[j][c] = expf(__fsub_rn(v[j][c], mx));
+                sum = __fadd_rn(sum, v[j][c]);
+            }
+        }
+    }
+    sum = fb::warp_sum_rn(sum);
+    const float inv = __fdiv_rn(1.0f, sum);
+#pragma unroll
+    for (int j = 0; j < kChunks; ++j) {
+        const int i = lane + 32 * j;
+        if (i >= chunks) {
+            continue;
+        }
+        float o[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            o[c] = c < count[j] ? __fmul_rn(v[j][c], inv) : 0.0f;
+        }
+        pr[i] = fb::pack8(o);
+    }
+}
+
+template <int kChunks>
+__global__ void __launch_bounds__(kThreads)
+    fb_causal_softmax_backward(uint4* ds, const uint4* __restrict__ p, const uint4* dp,
+                               size_t rows, int length, float scale) {
+    const size_t row = size_t{blockIdx.x} * kWarpsPerBlock + threadIdx.x / 32;
+    if (row >= rows) {
+        return;
+    }
+    const int lane = threadIdx.x % 32;
+    const int chunks = length / 8;
+    const int t = static_cast<int>(row % static_cast<size_t>(length));
+    const int visible_chunks = t / 8 + 1;
+    const uint4* pr = p + row * chunks;
+    const uint4* dpr = dp + row * chunks;
+    uint4* dsr = ds + row * chunks;
+
+    float pv[kChunks][8];
+    float dv[kChunks][8];
+    int count[kChunks];
+#pragma unroll
+    for (int j = 0; j < kChunks; ++j) {
+        const int i = lane + 32 * j;
+        count[j] = i < visible_chunks ? min(t + 1 - i * 8, 8) : 0;
+        if (count[j] > 0) {
+            fb::unpack8(pv[j], pr[i]);
+            fb::unpack8(dv[j], dpr[i]);
+        }
+    }
+    // D = sum of p * dp over the visible columns; each product of two FP16
+    // values is exact in FP32.
+    Comp d;
+#pragma unroll
+    for (int j = 0; j < kChunks; ++j) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            if (c < count[j]) {
+                fb::comp_add(d, __fmul_rn(pv[j][c], dv[j][c]));
+            }
+        }
+    }
+    d = fb::comp_warp_merge(d);
+    if (!isfinite(d.s)) {
+        d.e = 0.0f;
+    }
+#pragma unroll
+    for (int j = 0; j < kChunks; ++j) {
+        const int i = lane + 32 * j;
+        if (i >= chunks) {
+            continue;
+        }
+        float o[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const float diff = __fsub_rn(__fsub_rn(dv[j][c], d.s), d.e);
+            o[c] = c < count[j] ? __fmul_rn(__fmul_rn(pv[j][c], diff), scale) : 0.0f;
+        }
+        dsr[i] = fb::pack8(o);
+    }
+}
+
+flint_status check_softmax_dims(const char* name, size_t batches, size_t length) {
+    constexpr size_t kMaxLength = 1024;
+    constexpr size_t kMaxBatches = 65535;
+    if (length % 8 != 0 || length > kMaxLength) {
+        return fb::fail(FLINT_ERROR_INVALID_ARGUMENT,
+                        "%s: length (%zu) must be a multiple of 8 up to %zu", name, length,
+                        kMaxLength);
+    }
+    if (batches > kMaxBatches) {
+        return fb::fail(FLINT_ERROR_INVALID_ARGUMENT, "%s: batches (%zu) can be up to %zu", name,
+                        batches, kMaxBatches);
+    }
+    return FLINT_OK;
+}
+
+// ---- softmax + cross-entropy ------------------------------------------------------------
+
+constexpr int kCeThreads = 512;
+
+// Block-wide max / compensated sum through shared memory, in a fixed order.
+__device__ float block_max(float v, float* scratch) {
+    v = fb::warp_max(v);
+    const int warp = threadIdx.x / 32;
+    const int lane = threadIdx.x % 32;
+    __syncthreads();
+    if (lane == 0) {
+        scratch[warp] = v;
+    }
+    __syncthreads();
+    float m = scratch[0];
+    for (int w = 1; w < kCeThreads / 32; ++w) {
+        m = fmaxf(m, scratch[w]);
+    }
+    return m;
+}
+
+__device__ float block_comp_total(Comp a, float* scratch) {
+    a = fb::comp_warp_merge(a);
+    const int warp = threadIdx.x / 32;
+    const int lane = threadIdx.x % 32;
+    __syncthreads();
+    if (lane == 0) {
+        scratch[2 * warp] = a.s;
+        scratch[2 * warp + 1] = a.e;
+    }
+    __syncthreads();
+    Comp total;
+    total.s = scratch[0];
+    total.e = scratch[1];
+    for (int w = 1; w < kCeThreads / 32; ++w) {
+        fb::comp_merge(total, scratch[2 * w], scratch[2 * w + 1]);
+    }
+    return __fadd_rn(total.s, total.e);
+}
+
+// One CTA per row. The row's logits are read from HBM once into shared memory
+// (cols * 2 bytes, at most 128 KB); max, sum and the gradient pass then run
+// out of shared memory.
+__global__ void __launch_bounds__(kCeThreads)
+    fb_softmax_cross_entropy(uint4* __restrict__ dlogits, float* __restrict__ row_loss,
+                             const uint4* __restrict__ logits,
+                             const uint16_t* __restrict__ targets, float scale, size_t rows,
+                             int vocab, int cols) {
+    extern __shared__ uint4 staged[];
+    __shared__ float scratch[2 * (kCeThreads / 32)];
+    const int chunks = cols / 8;
+    const int vocab_chunks = (vocab + 7) / 8;
+    for (size_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const uint4* in = logits + row * chunks;
+        uint4* out = dlogits + row * chunks;
+        __syncthreads();  // the previous row's readers are done with `staged`
+
+        float mx = -INFINITY;
+        for (int i = threadIdx.x; i < vocab_chunks; i += kCeThreads) {
+            const uint4 q = in[i];
+            staged[i] = q;
+            float v[8];
+            fb::unpack8(v, q);
+            const int count = min(vocab - i * 8, 8);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                if (c < count) {
+                    mx = fmaxf(mx, v[c]);
+                }
+            }
+        }
+        mx = block_max(mx, scratch);
+
+        Comp part;
+        for (int i = threadIdx.x; i < vocab_chunks; i += kCeThreads) {
+            float v[8];
+            fb::unpack8(v, staged[i]);
+            const int count = min(vocab - i * 8, 8);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                if (c < count) {
+                    fb::comp_add(part, expf(__fsub_rn(v[c], mx)));
+                }
+            }
+        }
+        const float sum = block_comp_total(part, scratch);
+        const float inv = __fdiv_rn(1.0f, sum);
+
+        const int target = targets[row];
+        const int target_chunk = target / 8;
+        const int target_slot = target % 8;
+        for (int i = threadIdx.x; i < chunks; i += kCeThreads) {
+            if (i >= vocab_chunks) {
+                out[i] = make_uint4(0u, 0u, 0u, 0u);
+                continue;
+            }
+            float v[8];
+            fb::unpack8(v, staged[i]);
+            const int count = min(vocab - i * 8, 8);
+            float o[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                if (c >= count) {
+                    o[c] = 0.0f;
+                    continue;
+                }
+                const float gap = __fsub_rn(v[c], mx);
+                float prob = __fmul_rn(expf(gap), inv);
+                if (i == target_chunk && c == target_slot) {
+                    row_loss[row] = __fsub_rn(logf(sum), gap);
+                    prob = __fsub_rn(prob, 1.0f);
+                }
+                o[c] = __fmul_rn(prob, scale);
+            }
+            out[i] = fb::pack8(o);
+        }
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+flint_status flint_layernorm_forward(void* y, void* mean, void* rstd, const void* x,
+                                     const void* gamma, const void* beta, size_t rows,
+                                     size_t cols, float eps, flint_stream stream) {
+    constexpr const char* name = "flint_layernorm_forward";
+    constexpr size_t kMaxCols = size_t{1} << 24;
+    if (cols == 0 || cols > kMaxCols) {
+        return fb::fail(FLINT_ERROR_INVALID_ARGUMENT, "%s: cols (%zu) must be from 1 to %zu", name,
+                        cols, kMaxCols);
+    }
+    if (rows > kMaxRows8) {
+        return fb::fail(FLINT_ERROR_INVALID_ARGUMENT, "%s: rows (%zu) can be up to %zu", name,
+                        rows, kMaxRows8);
+    }
+    if (!std::isfinite(eps) || eps < 0.0f) {
+        return fb::fail(FLINT_ERROR_INVALID_ARGUMENT,
+                        "%s: eps (%g) must be finite and non-negative", name,
+                        static_cast<double>(eps));
+    }
+    if (rows == 0) {
+        return FLINT_OK;
+    }
+    const fb::Span spans[] = {
+        {"y", y, rows * cols * 2},   {"mean", mean, rows * 4},   {"rstd", rstd, rows * 4},
+        {"x", x, rows * cols * 4},   {"gamma", gamma, cols * 4}, {"beta", beta, cols * 4},
+    };
+    FB_TRY(fb::check_spans(name, spans, 3));
+
+    const unsigned blocks = static_cast<unsigned>((rows + kWarpsPerBlock - 1) / kWarpsPerBlock);
+    auto* yh = static_cast<__half*>(y);
+    auto* mf = static_cast<float*>(mean);
+    auto* rf = static_cast<float*>(rstd);
+    const auto* xf = static_cast<const float*>(x);
+    const auto* gf = static_cast<const float*>(gamma);
+    const auto* bf = static_cast<const float*>(beta);
+    const int c = static_cast<int>(cols);
+    if (cols % 4 == 0 && cols <= 128 * 2) {
+        fb_layernorm_forward_regs<2><<<blocks, kThreads, 0, stream>>>(yh, mf, rf, xf, gf, bf,
+                                                                       rows, c, eps);
+    } else if (cols % 4 == 0 && cols <= 128 * 6) {
+        fb_layernorm_forward_regs<6><<<blocks, kThreads, 0, stream>>>(yh, mf, rf, xf, gf, bf,
+                                                                       rows, c, eps);
+    } else if (cols % 4 == 0 && cols <= 128 * 12) {
+        fb_layernorm_forward_regs<12><<<blocks, kThreads, 0, stream>>>(yh, mf, rf, xf, gf, bf,
+                                                                        rows, c, eps);
+    } else if (cols % 4 == 0) {
+        fb_layernorm_forward_stream<4><<<blocks, kThreads, 0, stream>>>(yh, mf, rf, xf, gf, bf,
+                                                                         rows, c, eps);
+    } else {
+        fb_layernorm_forward_stream<1><<<blocks, kThreads, 0, stream>>>(yh, mf, rf, xf, gf, bf,
+                                                                         rows, c, eps);
+    }
+    FB_CUDA(cudaGetLastError());
+    return FLINT_OK;
+}
+
+flint_status flint_causal_softmax_forward(void* p, const void* s, size_t batches, size_t length,
+                                          flint_stream stream) {
+    constexpr const char* name = "flint_causal_softmax_forward";
+    FB_TRY(check_softmax_dims(name, batches, length));
+    if (batches == 0 || length == 0) {
+        return FLINT_OK;
+    }
+    const size_t bytes = batches * length * length * 2;
+    const fb::Span spans[] = {{"p", p, bytes}, {"s", s, bytes}};
+    FB_TRY(fb::check_spans(name, spans, 1));
+    const size_t rows = batches * length;
+    const unsigned blocks = static_cast<unsigned>((rows + kWarpsPerBlock - 1) / kWarpsPerBlock);
+    auto* pq = static_cast<uint4*>(p);
+    const auto* sq = static_cast<const uint4*>(s);
+    const int len = static_cast<int>(length);
+    if (length <= 256) {
+        fb_causal_softmax_forward<1><<<blocks, kThreads, 0, stream>>>(pq, sq, rows, len);
+    } else if (length <= 512) {
+        fb_causal_softmax_forward<2><<<blocks, kThreads, 0, stream>>>(pq, sq, rows, len);
+    } else {
+        fb_causal_softmax_forward<kMaxChunksPerLane><<<blocks, kThreads, 0, stream>>>(pq, sq, rows,
+                                                                                      len);
+    }
+    FB_CUDA(cudaGetLastError());
+    return FLINT_OK;
+}
+
+flint_status flint_causal_softmax_backward(void* ds, const void* p, const void* dp, size_t batches,
+                                           size_t length, float scale, flint_stream stream) {
+    constexpr const char* name = "flint_causal_softmax_backward";
+    FB_TRY(check_softmax_dims(name, batches, length));
+    if (!std::isfinite(scale)) {
+        return fb::fail(FLINT_ERROR_INVALID_ARGUMENT, "%s: scale (%g) must be finite", name,
+                        static_cast<double>(scale));
+    }
+    if (batches == 0 || length == 0) {
+        return FLINT_OK;
+    }
+    const size_t bytes = batches * length * length * 2;
+    // Computing in place (ds == dp) is allowed; then dp is not a separate span.
+    const fb::Span spans[] = {{"ds", ds, bytes}, {"p", p, bytes}, {"dp", dp, bytes}};
+    FB_TRY(fb::check_spans(name, spans, ds == dp ? 2 : 3, 1));
+    const size_t rows = batches * length;
+    const unsigned blocks = static_cast<unsigned>((rows + kWarpsPerBlock - 1) / kWarpsPerBlock);
+    auto* dsq = static_cast<uint4*>(ds);
+    const auto* pq = static_cast<const uint4*>(p);
+    const auto* dpq = static_cast<const uint4*>(dp);
+    const int len = static_cast<int>(length);
+    if (length <= 256) {
+        fb_causal_softmax_backward<1><<<blocks, kThreads, 0, stream>>>(dsq, pq, dpq, rows, len,
+                                                                       scale);
+    } else if (length <= 512) {
+        fb_causal_softmax_backward<2><<<blocks, kThreads, 0, stream>>>(dsq, pq, dpq, rows, len,
+                                                                       scale);
+    } else {
+        fb_causal_softmax_backward<kMaxChunksPerLane><<<blocks, kThreads, 0, stream>>>(
+            dsq, pq, dpq, rows, len, scale);
+    }
+    FB_CUDA(cudaGetLastError());
+    return FLINT_OK;
+}
+
+flint_status flint_softmax_cross_entropy(void* dlogits, void* row_loss, const void* logits,
+                                         const void* targets, float scale, size_t rows,
+                                         size_t vocab, size_t cols, flint_stream stream) {
+    constexpr const char* name = "flint_softmax_cross_entropy";
+    constexpr size_t kMaxCols = size_t{1} << 16;
+    if (cols == 0 || cols % 8 != 0 || cols > kMaxCols) {
+        return fb::fail(FLINT_ERROR_INVALID_ARGUMENT,
+                        "%s: cols (%zu) must be a multiple of 8 from 8 to %zu", name, cols,
+                        kMaxCols);
+    }
+    if (vocab == 0 || vocab > cols) {
+        return fb::fail(FLINT_ERROR_INVALID_ARGUMENT,
+                        "%s: vocab (%zu) must be from 1 to cols (%zu)", name, vocab, cols);
+    }
+    if (rows > kMaxRows8) {
+        return fb::fail(FLINT_ERROR_INVALID_ARGUMENT, "%s: rows (%zu) can be up to %zu", name,
+                        rows, kMaxRows8);
+    }
+    if (!std::isfinite(scale)) {
+        return fb::fail(FLINT_ERROR_INVALID_ARGUMENT, "%s: scale (%g) must be finite", name,
+                        static_cast<double>(scale));
+    }
+    if (rows == 0) {
+        return FLINT_OK;
+    }
+    const fb::Span spans[] = {
+        {"dlogits", dlogits, rows * cols * 2},
+        {"row_loss", row_loss, rows * 4},
+        {"logits", logits, rows * cols * 2},
+        {"targets", targets, rows * 2},
+    };
+    FB_TRY(fb::check_spans(name, spans, 2));
+
+    // Only the vocab columns are staged.
+    const size_t staged_bytes = (vocab + 7) / 8 * 16;
+    static bool configured[64] = {};
+    int device = 0;
+    FB_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= 64 || !configured[device]) {
+        FB_CUDA(cudaFuncSetAttribute(fb_softmax_cross_entropy,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(kMaxCols * 2)));
+        if (device >= 0 && device < 64) {
+            configured[device] = true;
+        }
+    }
+    int sms = 148;
+    FB_CUDA(fb::sm_count(&sms));
+    const unsigned blocks =
+        static_cast<unsigned>(std::min<size_t>(rows, static_cast<size_t>(sms) * 8));
+    fb_softmax_cross_entropy<<<blocks, kCeThreads, staged_bytes, stream>>>(
+        static_cast<uint4*>(dlogits), static_cast<float*>(row_loss),
+        static_cast<const uint4*>(logits), static_cast<const uint16_t*>(targets), scale, rows,
+        static_cast<int>(vocab), static_cast<int>(cols));
+    FB_CUDA(cudaGetLastError());
+    return FLINT_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,91 @@
+/* Extensions of the Blackwell build that the reference library does not have:
+ * fused (flash) causal attention, the optimizer and loss-scaling kernels, a
+ * model variant that uses them, and hooks for data-parallel training. None of
+ * these has a counterpart in the reference's include/flint/flint.h; they follow
+ * the same conventions (device pointers, caller's stream, flint_status,
+ * flint_last_error). The PyTorch oracle they are checked against is the
+ * reference's scripts/gpt2_torch.py (attention: :52-60, AdamW groups: :161-175,
+ * train_step: :178-192). */
+#ifndef FLINT_FLINT_B200_H
+#define FLINT_FLINT_B200_H
+
+#include "flint/flint.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* 1 if a GEMM or attention kernel gave up on a barrier wait since the last
+ * call (the flag is cleared), 0 otherwise. Synchronises the device; meant for
+ * tests. */
+FLINT_API flint_status flint_b200_kernel_fault(int* raised);
+
+/* Causal attention without materialising scores or probabilities:
+ * o[b] = softmax(scale * q[b] k[b]^T + causal mask) v[b] for `batches`
+ * (sequence, head) pairs, all FP16 [batches, length, head_width] contiguous;
+ * lse[batches, length] FP32 receives log-sum-exp of the scaled scores (natural
+ * log), which the backward pass needs. head_width must be 64, length a
+ * multiple of 8 up to 1,024. */
+FLINT_API flint_status flint_b200_attention_forward(void* o, void* lse, const void* q,
+                                                    const void* k, const void* v, size_t batches,
+                                                    size_t length, size_t head_width, float scale,
+                                                    flint_stream stream);
+
+/* Gradients of the above: dq, dk, dv from d_o, o, lse and q, k, v (layouts as
+ * above). delta is an FP32 scratch [batches, length] the call overwrites. */
+FLINT_API flint_status flint_b200_attention_backward(void* dq, void* dk, void* dv, const void* d_o,
+                                                     const void* o, const void* lse, void* delta,
+                                                     const void* q, const void* k, const void* v,
+                                                     size_t batches, size_t length,
+                                                     size_t head_width, float scale,
+                                                     flint_stream stream);
+
+/* flint_gpt2_create with a choice of attention: flash_attention non-zero builds
+ * the model on the fused kernels above (no T x T buffers, so far less memory);
+ * zero is flint_gpt2_create. */
+FLINT_API flint_status flint_b200_gpt2_create(const flint_gpt2_config* config, int flash_attention,
+                                              flint_gpt2** model);
+
+/* Called on the launching host thread from inside
+ * flint_b200_gpt2_backward_buckets each time every kernel that writes one
+ * contiguous range of the gradient arena has been enqueued: bucket 0 is ln_f,
+ * buckets 1..layers are the blocks from last to first, and the final bucket is
+ * wte + wpe. A data-parallel trainer records an event there and starts that
+ * range's all-reduce on another stream. */
+typedef void (*flint_b200_bucket_callback)(void* user, int bucket, void* gradients, size_t bytes);
+
+/* flint_gpt2_backward plus the callback above (which may be null). */
+FLINT_API flint_status flint_b200_gpt2_backward_buckets(flint_gpt2* model, const void* tokens,
+                                                        int accumulate, flint_stream stream,
+                                                        flint_b200_bucket_callback callback,
+                                                        void* user);
+
+/* The contiguous FP32 range that holds every gradient, in parameter order. */
+FLINT_API flint_status flint_b200_gpt2_gradient_arena(const flint_gpt2* model, void** base,
+                                                      size_t* bytes);
+
+/* Fused AdamW over `count` FP32 values (PyTorch semantics, decoupled decay):
+ *   g = grad * grad_scale;  m = b1 m + (1 - b1) g;  v = b2 v + (1 - b2) g^2
+ *   p = p - lr * (weight_decay * p + (m / (1 - b1^step)) / (sqrt(v / (1 - b2^step)) + eps))
+ * and, when half_copy is not null, half_copy = half(p). When *skip (a device
+ * int, may be null) is non-zero the call changes nothing: a step whose
+ * gradients overflowed is dropped. */
+FLINT_API flint_status flint_b200_adamw(void* param, void* m, void* v, const void* grad,
+                                        void* half_copy, size_t count, float lr, float beta1,
+                                        float beta2, float eps, float weight_decay,
+                                        float grad_scale, int step, const int* skip,
+                                        flint_stream stream);
+
+/* Sets *found_nonfinite (device int) to 1 if any of the count FP32 values is
+ * inf or NaN; leaves it unchanged otherwise, so several calls can share it.
+ * When sum_squares (device double, may be null) is given, adds the sum of
+ * squares of the values times scale^2 to it (for gradient-norm clipping). */
+FLINT_API flint_status flint_b200_check_gradients(const void* grad, size_t count, float scale,
+                                                  int* found_nonfinite, double* sum_squares,
+                                                  flint_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* FLINT_FLINT_B200_H */
