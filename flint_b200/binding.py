@@ -55,6 +55,20 @@ class Gpt2ParameterInfo(ctypes.Structure):
     ]
 
 
+class AdamwTensor(ctypes.Structure):
+    """flint_b200_adamw_tensor."""
+
+    _fields_ = [
+        ("param", ctypes.c_void_p),
+        ("m", ctypes.c_void_p),
+        ("v", ctypes.c_void_p),
+        ("grad", ctypes.c_void_p),
+        ("half_copy", ctypes.c_void_p),
+        ("count", ctypes.c_size_t),
+        ("weight_decay", ctypes.c_float),
+    ]
+
+
 BUCKET_CALLBACK = ctypes.CFUNCTYPE(None, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p,
                                    ctypes.c_size_t)
 
@@ -80,6 +94,7 @@ _C_TYPES = {
     "const flint_gpt2_config*": ctypes.POINTER(Gpt2Config),
     "flint_gpt2_parameter_info*": ctypes.POINTER(Gpt2ParameterInfo),
     "flint_b200_bucket_callback": BUCKET_CALLBACK,
+    "const flint_b200_adamw_tensor*": ctypes.POINTER(AdamwTensor),
 }
 
 _DECLARATION = re.compile(r"FLINT_API\s+([^;(]*?)\b(flint_\w+)\s*\(([^;]*?)\)\s*;", re.S)
@@ -353,6 +368,25 @@ class Flint:
               grad_scale, step, skip=None, stream=None) -> None:
         self.call("flint_b200_adamw", param, m, v, grad, half_copy, count, lr, beta1, beta2, eps,
                   weight_decay, grad_scale, step, skip, stream=stream)
+
+    def adamw_plan(self, tensors, stream=None):
+        """A device-resident plan for adamw_run from (param, m, v, grad, half_copy, count,
+        weight_decay) tuples of addresses. Returns (plan tensor, items)."""
+        import torch
+
+        array = (AdamwTensor * len(tensors))(*[AdamwTensor(*t) for t in tensors])
+        nbytes, items = ctypes.c_size_t(), ctypes.c_size_t()
+        self.check(self.lib.flint_b200_adamw_plan_bytes(array, len(tensors), ctypes.byref(nbytes)))
+        self.check(self.lib.flint_b200_adamw_plan_items(array, len(tensors), ctypes.byref(items)))
+        plan = torch.empty(nbytes.value + 16, dtype=torch.uint8, device="cuda")
+        self.check(self.lib.flint_b200_adamw_plan(plan.data_ptr(), nbytes.value, array,
+                                                  len(tensors), stream_handle(stream)))
+        return plan, items.value
+
+    def adamw_run(self, plan, items, lr, beta1, beta2, eps, grad_scale, step, skip=None,
+                  stream=None) -> None:
+        self.call("flint_b200_adamw_run", plan, items, lr, beta1, beta2, eps, grad_scale, step,
+                  skip, stream=stream)
 
     def check_gradients(self, grad, count, scale, found_nonfinite, sum_squares=None,
                         stream=None) -> None:

@@ -1,21 +1,1019 @@
-// Placeholder: the fused attention kernels are built in a later step.
+// Fused causal attention for head width 64 on the 5th-generation tensor cores
+// (extension; the reference materialises scores and probabilities instead,
+// src/api/gpt2.cpp:495-530 and :559-618, and lists flash attention as planned).
+//
+// Three kernels, all warp-specialised like the GEMM (warp 0 = TMA producer,
+// warp 1 = tcgen05.mma issuer, the rest compute on accumulators read from
+// tensor memory), each working on 128 x 128 (query x key) tiles:
+//   forward   one CTA per (head, 128 queries): S = Q K^T into TMEM, online
+//             softmax in registers, P (FP16) back to shared memory in the
+//             operand layout, O_block = P V into TMEM, running rescale of O in
+//             registers; two CTAs share an SM so one's softmax overlaps the
+//             other's MMAs
+//   dK/dV     one CTA per (head, 128 keys), looping over the query tiles at or
+//             below the diagonal: S and dP = dO V^T recomputed, P and dS written
+//             to shared memory, dV += P^T dO and dK += dS^T Q accumulated in TMEM
+//   dQ        one CTA per (head, 128 queries), looping over key tiles:
+//             dQ += dS K accumulated in TMEM
+// dQ has its own kernel so that no gradient needs atomics: every output element
+// is produced by one CTA in a fixed order, so results are deterministic.
+//
+// Q, K, V, O and their gradients are addressed through strided 4-D tensor maps
+// (column, row, head, sequence), so the same kernels read the heads layout
+// [B, H, T, 64] or GPT-2's packed qkv rows [B*T, 3*H*64] without a split/merge
+// pass. Softmax runs in base 2: t = s * scale * log2(e), p = 2^(t - max).
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+#include "attention.h"
 #include "common.h"
+#include "device_utils.cuh"
 #include "flint/flint_b200.h"
+#include "sm100.cuh"
+
+namespace fb {
+namespace {
+
+constexpr int kTile = 128;     // queries and keys per tile
+constexpr int kHead = 64;      // head width
+constexpr int kTileBytes = kTile * kHead * 2;  // 16 KB: one Q/K/V/dO tile
+constexpr int kPanelBytes = kTile * 128;       // 16 KB: 64 FP16 columns of a 128-row P/dS tile
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr flint_status kInvalid = FLINT_ERROR_INVALID_ARGUMENT;
+
+__device__ int g_attention_error = 0;
+
+struct AttnParams {
+    CUtensorMap map_q, map_k, map_v, map_do;
+    // Outputs and row statistics are addressed directly.
+    void* out0;            // forward: O; dkv: dK; dq: dQ
+    void* out1;            // dkv: dV
+    long long out_row, out_head, out_seq;  // element strides of out0/out1
+    float* lse;            // [seqs * heads, length]
+    const float* delta;    // [seqs * heads, length]
+    int length, heads, seqs, blocks;
+    float scale;           // applied to the raw scores
+};
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2),
+          "r"(c3)
+        : "memory");
+}
+
+__device__ __forceinline__ void fence_async_shared() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// Writes 32 FP16 values (columns [col, col+32) of row `row`) of a 128 x 128
+// tile into the two-panel, 128-byte-swizzled operand layout.
+__device__ __forceinline__ void store_operand_row(uint32_t tile_base, int row, int col,
+                                                  const float (&v)[32]) {
+    const uint32_t panel = tile_base + (col >> 6) * kPanelBytes + row * 128;
+    const int first_chunk = (col & 63) >> 3;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const uint32_t at = panel + (((first_chunk + c) ^ (row & 7)) << 4);
+        const unsigned w0 = fb::pack2(v[8 * c], v[8 * c + 1]);
+        const unsigned w1 = fb::pack2(v[8 * c + 2], v[8 * c + 3]);
+        const unsigned w2 = fb::pack2(v[8 * c + 4], v[8 * c + 5]);
+        const unsigned w3 = fb::pack2(v[8 * c + 6], v[8 * c + 7]);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(at), "r"(w0), "r"(w1),
+                     "r"(w2), "r"(w3)
+                     : "memory");
+    }
+}
+
+// Descriptors for the three ways a tile is read.
+// K-major tile [128 rows][64 cols] (rows = M or N index): 16-column step = 32 bytes.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile, int kstep) {
+    return sm100::smem_desc_sw128(tile + kstep * 32, 16, 1024);
+}
+// A two-panel K-major tile [128 rows][128 cols] (P or dS as the A operand, K = key).
+__device__ __forceinline__ uint64_t desc_kmajor_wide(uint32_t tile, int kstep) {
+    return sm100::smem_desc_sw128(tile + (kstep >> 2) * kPanelBytes + (kstep & 3) * 32, 16, 1024);
+}
+// MN-major view of the same memory: rows are the K index, 16 rows = 2,048 bytes;
+// 64-column blocks (panels) are `lbo` bytes apart.
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile, int kstep, uint32_t lbo) {
+    return sm100::smem_desc_sw128(tile + kstep * 2048, lbo, 1024);
+}
+
+constexpr uint32_t kIdescS = sm100::instr_desc_f16(128, 128, false, false);   // Q K^T, dO V^T
+constexpr uint32_t kIdescPV = sm100::instr_desc_f16(128, 64, false, true);    // P V, dS K
+constexpr uint32_t kIdescT = sm100::instr_desc_f16(128, 64, true, true);      // P^T dO, dS^T Q
+
+__device__ __forceinline__ void finish(int abort_value, uint32_t tmem_base, uint32_t cols,
+                                       int warp) {
+    __syncthreads();
+    if (abort_value != 0) {
+        if (threadIdx.x == 0) {
+            atomicExch(&g_attention_error, 1);
+        }
+        const long long start = clock64();
+        while (clock64() - start < 2000000LL) {
+        }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        sm100::tc_fence_after_sync();
+        sm100::tmem_dealloc(tmem_base, cols);
+    }
+}
+
+// ---- forward ---------------------------------------------------------------------------
+
+constexpr int kFwdThreads = 192;
+constexpr int kFwdSmem = 1024 + kTileBytes * 4 + 2 * kPanelBytes + 128;  // Q, 3-slot ring, P
+
+__global__ void __launch_bounds__(kFwdThreads, 2)
+    fb_attention_forward(const __grid_constant__ AttnParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t base = (sm100::smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t q_tile = base;
+    const uint32_t ring = base + kTileBytes;
+    const uint32_t p_tile = ring + 3 * kTileBytes;
+    const uint32_t bars = p_tile + 2 * kPanelBytes;
+    const uint32_t q_full = bars, s_full = bars + 8, p_ready = bars + 16, o_full = bars + 24;
+    auto slot_full = [&](int s) { return bars + 32 + 8u * s; };
+    auto slot_empty = [&](int s) { return bars + 56 + 8u * s; };
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x / 32;
+    const int lane = threadIdx.x % 32;
+    const int bh_count = p.heads * p.seqs;
+    const int qb = p.blocks - 1 - static_cast<int>(blockIdx.x / bh_count);  // heavy tiles first
+    const int bh = static_cast<int>(blockIdx.x % bh_count);
+    const int head = bh % p.heads;
+    const int seq = bh / p.heads;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        sm100::mbar_init(q_full, 1);
+        sm100::mbar_init(s_full, 1);
+        sm100::mbar_init(p_ready, 128);
+        sm100::mbar_init(o_full, 1);
+        for (int s = 0; s < 3; ++s) {
+            sm100::mbar_init(slot_full(s), 1);
+            sm100::mbar_init(slot_empty(s), 1);
+        }
+        sm100::mbar_fence_init();
+    }
+    if (warp == 1) {
+        sm100::tmem_alloc(sm100::smem_u32(&tmem_slot), 256);
+    }
+    sm100::tc_fence_before_sync();
+    __syncthreads();
+    sm100::tc_fence_after_sync();
+    const uint32_t tmem = tmem_slot;
+    const uint32_t tmem_s = tmem;
+    const uint32_t tmem_o = tmem + 128;
+    volatile int* abort = &abort_flag;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            sm100::mbar_expect_tx(q_full, kTileBytes);
+            tma_load_4d(q_tile, &p.map_q, q_full, 0, qb * kTile, head, seq);
+            int slot = 0;
+            uint32_t phase = 0;
+            for (int j = 0; j <= qb; ++j) {
+                for (int which = 0; which < 2; ++which) {
+                    if (!sm100::mbar_wait(slot_empty(slot), phase ^ 1u, abort)) {
+                        j = qb + 1;
+                        break;
+                    }
+                    sm100::mbar_expect_tx(slot_full(slot), kTileBytes);
+                    tma_load_4d(ring + slot * kTileBytes, which == 0 ? &p.map_k : &p.map_v,
+                                slot_full(slot), 0, j * kTile, head, seq);
+                    if (++slot == 3) {
+                        slot = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            bool ok = sm100::mbar_wait(q_full, 0, abort);
+            int slot = 0;
+            uint32_t phase = 0;
+            for (int j = 0; ok && j <= qb; ++j) {
+                const int kslot = slot;
+                if (!sm100::mbar_wait(slot_full(kslot), phase, abort)) {
+                    break;
+                }
+                if (++slot == 3) {
+                    slot = 0;
+                    phase ^= 1u;
+                }
+                sm100::tc_fence_after_sync();
+                const uint32_t k_tile = ring + kslot * kTileBytes;
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    sm100::mma_f16_ss(tmem_s, desc_kmajor(q_tile, ks), desc_kmajor(k_tile, ks),
+                                      kIdescS, ks > 0);
+                }
+                sm100::mma_commit(slot_empty(kslot));
+                sm100::mma_commit(s_full);
+
+                const int vslot = slot;
+                if (!sm100::mbar_wait(slot_full(vslot), phase, abort)) {
+                    break;
+                }
+                if (++slot == 3) {
+                    slot = 0;
+                    phase ^= 1u;
+                }
+                if (!sm100::mbar_wait(p_ready, j & 1, abort)) {
+                    break;
+                }
+                sm100::tc_fence_after_sync();
+                const uint32_t v_tile = ring + vslot * kTileBytes;
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    sm100::mma_f16_ss(tmem_o, desc_kmajor_wide(p_tile, ks),
+                                      desc_mnmajor(v_tile, ks, 16), kIdescPV, ks > 0);
+                }
+                sm100::mma_commit(slot_empty(vslot));
+                sm100::mma_commit(o_full);
+            }
+        }
+    } else {
+        const int quadrant = warp % 4;
+        const int row = quadrant * 32 + lane;            // query row inside the tile
+        const int q_index = qb * kTile + row;
+        const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
+        const float scale2 = p.scale * kLog2e;
+        float m = -INFINITY;
+        float l = 0.0f;
+        float o[kHead];
+#pragma unroll
+        for (int d = 0; d < kHead; ++d) {
+            o[d] = 0.0f;
+        }
+        bool ok = true;
+        for (int j = 0; ok && j <= qb; ++j) {
+            if (!sm100::mbar_wait(s_full, j & 1, abort)) {
+                ok = false;
+                break;
+            }
+            sm100::tc_fence_after_sync();
+            const bool diagonal = j == qb;
+            float mx = m;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t raw[32];
+                sm100::tmem_ld_32x32(tmem_s + lane_base + c * 32, raw);
+                sm100::tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float t = __uint_as_float(raw[i]) * scale2;
+                    const bool visible = !diagonal || (c * 32 + i <= row);
+                    mx = visible ? fmaxf(mx, t) : mx;
+                }
+            }
+            const float alpha = exp2f(m - mx);
+            l *= alpha;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t raw[32];
+                sm100::tmem_ld_32x32(tmem_s + lane_base + c * 32, raw);
+                sm100::tmem_ld_wait();
+                float v[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float t = __uint_as_float(raw[i]) * scale2;
+                    const bool visible = !diagonal || (c * 32 + i <= row);
+                    v[i] = visible ? exp2f(t - mx) : 0.0f;
+                    l += v[i];
+                }
+                store_operand_row(p_tile, row, c * 32, v);
+            }
+            m = mx;
+            fence_async_shared();
+            sm100::tc_fence_before_sync();
+            sm100::mbar_arrive(p_ready);
+
+            if (!sm100::mbar_wait(o_full, j & 1, abort)) {
+                ok = false;
+                break;
+            }
+            sm100::tc_fence_after_sync();
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t raw[32];
+                sm100::tmem_ld_32x32(tmem_o + lane_base + c * 32, raw);
+                sm100::tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    o[c * 32 + i] = fmaf(o[c * 32 + i], alpha, __uint_as_float(raw[i]));
+                }
+            }
+            sm100::tc_fence_before_sync();
+        }
+        if (ok && q_index < p.length) {
+            const float inv = 1.0f / l;
+            __half* out = static_cast<__half*>(p.out0) + seq * p.out_seq + head * p.out_head +
+                          static_cast<long long>(q_index) * p.out_row;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                float v[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    v[i] = o[c * 8 + i] * inv;
+                }
+                *reinterpret_cast<uint4*>(out + c * 8) = fb::pack8(v);
+            }
+            p.lse[static_cast<size_t>(bh) * p.length + q_index] = (m + log2f(l)) * kLn2;
+        }
+    }
+    finish(abort_flag, tmem, 256, warp);
+}
+
+// ---- backward: delta = rowsum(dO * O) ----------------------------------------------------------
+
+struct View {
+    const __half* base;
+    long long row, head, seq;
+};
+
+__global__ void __launch_bounds__(256)
+    fb_attention_delta(float* __restrict__ delta, View d_o, View o, int length, int heads,
+                       int seqs) {
+    const long long rows = static_cast<long long>(length) * heads * seqs;
+    const int lane = threadIdx.x % 32;
+    for (long long r = blockIdx.x * 8LL + threadIdx.x / 32; r < rows; r += gridDim.x * 8LL) {
+        const int t = static_cast<int>(r % length);
+        const long long bh = r / length;
+        const int head = static_cast<int>(bh % heads);
+        const long long seq = bh / heads;
+        const __half2 a = *reinterpret_cast<const __half2*>(
+            d_o.base + seq * d_o.seq + head * d_o.head + t * d_o.row + 2 * lane);
+        const __half2 b = *reinterpret_cast<const __half2*>(
+            o.base + seq * o.seq + head * o.head + t * o.row + 2 * lane);
+        const float2 fa = __half22float2(a);
+        const float2 fb2 = __half22float2(b);
+        float s = fa.x * fb2.x + fa.y * fb2.y;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            s += __shfl_xor_sync(fb::kFullMask, s, off);
+        }
+        if (lane == 0) {
+            delta[r] = s;
+        }
+    }
+}
+
+// ---- backward: dK and dV ------------------------------------------------------------------------
+
+constexpr int kBwdThreads = 320;  // TMA warp, MMA warp, 8 compute warps
+// K, V, 2 x (Q, dO), P, dS
+constexpr int kDkvSmem = 1024 + kTileBytes * 6 + 4 * kPanelBytes + 128;
+
+__global__ void __launch_bounds__(kBwdThreads, 1)
+    fb_attention_dkv(const __grid_constant__ AttnParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t base = (sm100::smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t k_tile = base;
+    const uint32_t v_tile = base + kTileBytes;
+    const uint32_t ring = base + 2 * kTileBytes;            // stage s: Q at +0, dO at +16 KB
+    const uint32_t p_tile = ring + 4 * kTileBytes;
+    const uint32_t ds_tile = p_tile + 2 * kPanelBytes;
+    const uint32_t bars = ds_tile + 2 * kPanelBytes;
+    const uint32_t kv_full = bars, sdp_full = bars + 8, pds_ready = bars + 16,
+                   grads_done = bars + 24;
+    auto stage_full = [&](int s) { return bars + 32 + 8u * s; };
+    auto stage_empty = [&](int s) { return bars + 48 + 8u * s; };
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x / 32;
+    const int lane = threadIdx.x % 32;
+    const int bh_count = p.heads * p.seqs;
+    const int kb = static_cast<int>(blockIdx.x / bh_count);  // key tile 0 has the most work
+    const int bh = static_cast<int>(blockIdx.x % bh_count);
+    const int head = bh % p.heads;
+    const int seq = bh / p.heads;
+    const int iterations = p.blocks - kb;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        sm100::mbar_init(kv_full, 1);
+        sm100::mbar_init(sdp_full, 1);
+        sm100::mbar_init(pds_ready, 256);
+        sm100::mbar_init(grads_done, 1);
+        for (int s = 0; s < 2; ++s) {
+            sm100::mbar_init(stage_full(s), 1);
+            sm100::mbar_init(stage_empty(s), 1);
+        }
+        sm100::mbar_fence_init();
+    }
+    if (warp == 1) {
+        sm100::tmem_alloc(sm100::smem_u32(&tmem_slot), 512);
+    }
+    sm100::tc_fence_before_sync();
+    __syncthreads();
+    sm100::tc_fence_after_sync();
+    const uint32_t tmem = tmem_slot;
+    const uint32_t tmem_s = tmem, tmem_dp = tmem + 128, tmem_dv = tmem + 256, tmem_dk = tmem + 320;
+    volatile int* abort = &abort_flag;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            sm100::mbar_expect_tx(kv_full, 2 * kTileBytes);
+            tma_load_4d(k_tile, &p.map_k, kv_full, 0, kb * kTile, head, seq);
+            tma_load_4d(v_tile, &p.map_v, kv_full, 0, kb * kTile, head, seq);
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int it = 0; it < iterations; ++it) {
+                if (!sm100::mbar_wait(stage_empty(stage), phase ^ 1u, abort)) {
+                    break;
+                }
+                const int qb = kb + it;
+                const uint32_t dst = ring + stage * 2 * kTileBytes;
+                sm100::mbar_expect_tx(stage_full(stage), 2 * kTileBytes);
+                tma_load_4d(dst, &p.map_q, stage_full(stage), 0, qb * kTile, head, seq);
+                tma_load_4d(dst + kTileBytes, &p.map_do, stage_full(stage), 0, qb * kTile, head,
+                            seq);
+                if (++stage == 2) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            bool ok = sm100::mbar_wait(kv_full, 0, abort);
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int it = 0; ok && it < iterations; ++it) {
+                if (!sm100::mbar_wait(stage_full(stage), phase, abort)) {
+                    break;
+                }
+                sm100::tc_fence_after_sync();
+                const uint32_t q_tile = ring + stage * 2 * kTileBytes;
+                const uint32_t do_tile = q_tile + kTileBytes;
+                // S = Q K^T and dP = dO V^T; the compute warps have drained the
+                // previous pair (they signalled pds_ready before the last gradient MMAs).
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    sm100::mma_f16_ss(tmem_s, desc_kmajor(q_tile, ks), desc_kmajor(k_tile, ks),
+                                      kIdescS, ks > 0);
+                }
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    sm100::mma_f16_ss(tmem_dp, desc_kmajor(do_tile, ks), desc_kmajor(v_tile, ks),
+                                      kIdescS, ks > 0);
+                }
+                sm100::mma_commit(sdp_full);
+                if (!sm100::mbar_wait(pds_ready, it & 1, abort)) {
+                    break;
+                }
+                sm100::tc_fence_after_sync();
+                // dV += P^T dO, dK += dS^T Q (K = the 128 queries of this tile).
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    sm100::mma_f16_ss(tmem_dv, desc_mnmajor(p_tile, ks, kPanelBytes),
+                                      desc_mnmajor(do_tile, ks, 16), kIdescT, (it | ks) != 0);
+                }
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    sm100::mma_f16_ss(tmem_dk, desc_mnmajor(ds_tile, ks, kPanelBytes),
+                                      desc_mnmajor(q_tile, ks, 16), kIdescT, (it | ks) != 0);
+                }
+                sm100::mma_commit(stage_empty(stage));
+                if (it + 1 == iterations) {
+                    sm100::mma_commit(grads_done);
+                }
+                if (++stage == 2) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    } else {
+        const int quadrant = warp % 4;
+        const int half = (warp - 2) / 4;                 // which 64 key columns
+        const int row = quadrant * 32 + lane;            // query row inside the tile
+        const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
+        const float scale2 = p.scale * kLog2e;
+        bool ok = true;
+        for (int it = 0; ok && it < iterations; ++it) {
+            const int qb = kb + it;
+            const int q_index = qb * kTile + row;
+            const bool row_valid = q_index < p.length;
+            float lse2 = 0.0f;
+            float dlt = 0.0f;
+            if (row_valid) {
+                lse2 = p.lse[static_cast<size_t>(bh) * p.length + q_index] * kLog2e;
+                dlt = p.delta[static_cast<size_t>(bh) * p.length + q_index];
+            }
+            if (!sm100::mbar_wait(sdp_full, it & 1, abort)) {
+                ok = false;
+                break;
+            }
+            sm100::tc_fence_after_sync();
+            const bool diagonal = it == 0;
+#pragma unroll 1
+            for (int c = 0; c < 2; ++c) {
+                const int col = half * 64 + c * 32;
+                uint32_t s_raw[32];
+                uint32_t dp_raw[32];
+                sm100::tmem_ld_32x32(tmem_s + lane_base + col, s_raw);
+                sm100::tmem_ld_32x32(tmem_dp + lane_base + col, dp_raw);
+                sm100::tmem_ld_wait();
+                float pv[32];
+                float dsv[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const bool visible = row_valid && (!diagonal || (col + i <= row));
+                    const float prob =
+                        visible ? exp2f(__uint_as_float(s_raw[i]) * scale2 - lse2) : 0.0f;
+                    pv[i] = prob;
+                    dsv[i] = prob * (__uint_as_float(dp_raw[i]) - dlt) * p.scale;
+                }
+                store_operand_row(p_tile, row, col, pv);
+                store_operand_row(ds_tile, row, col, dsv);
+            }
+            fence_async_shared();
+            sm100::tc_fence_before_sync();
+            sm100::mbar_arrive(pds_ready);
+        }
+        if (ok && sm100::mbar_wait(grads_done, 0, abort)) {
+            sm100::tc_fence_after_sync();
+            // Rows of dV/dK are keys; this warp writes 32 of the 64 columns.
+            const int k_index = kb * kTile + row;
+            uint32_t dv_raw[32];
+            uint32_t dk_raw[32];
+            sm100::tmem_ld_32x32(tmem_dv + lane_base + half * 32, dv_raw);
+            sm100::tmem_ld_32x32(tmem_dk + lane_base + half * 32, dk_raw);
+            sm100::tmem_ld_wait();
+            if (k_index < p.length) {
+                const long long at = seq * p.out_seq + head * p.out_head +
+                                     static_cast<long long>(k_index) * p.out_row + half * 32;
+                __half* dk_out = static_cast<__half*>(p.out0) + at;
+                __half* dv_out = static_cast<__half*>(p.out1) + at;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    float a[8];
+                    float b[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        a[i] = __uint_as_float(dk_raw[c * 8 + i]);
+                        b[i] = __uint_as_float(dv_raw[c * 8 + i]);
+                    }
+                    *reinterpret_cast<uint4*>(dk_out + c * 8) = fb::pack8(a);
+                    *reinterpret_cast<uint4*>(dv_out + c * 8) = fb::pack8(b);
+                }
+            }
+            sm100::tc_fence_before_sync();
+        }
+    }
+    finish(abort_flag, tmem, 512, warp);
+}
+
+// ---- backward: dQ ---------------------------------------------------------------------------------
+
+// Q, dO, 2 x (K, V), dS
+constexpr int kDqSmem = 1024 + kTileBytes * 6 + 2 * kPanelBytes + 128;
+
+__global__ void __launch_bounds__(kBwdThreads, 1)
+    fb_attention_dq(const __grid_constant__ AttnParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t base = (sm100::smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t q_tile = base;
+    const uint32_t do_tile = base + kTileBytes;
+    const uint32_t ring = base + 2 * kTileBytes;            // stage s: K at +0, V at +16 KB
+    const uint32_t ds_tile = ring + 4 * kTileBytes;
+    const uint32_t bars = ds_tile + 2 * kPanelBytes;
+    const uint32_t qdo_full = bars, sdp_full = bars + 8, ds_ready = bars + 16,
+                   dq_done = bars + 24;
+    auto stage_full = [&](int s) { return bars + 32 + 8u * s; };
+    auto stage_empty = [&](int s) { return bars + 48 + 8u * s; };
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x / 32;
+    const int lane = threadIdx.x % 32;
+    const int bh_count = p.heads * p.seqs;
+    const int qb = p.blocks - 1 - static_cast<int>(blockIdx.x / bh_count);
+    const int bh = static_cast<int>(blockIdx.x % bh_count);
+    const int head = bh % p.heads;
+    const int seq = bh / p.heads;
+    const int iterations = qb + 1;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        sm100::mbar_init(qdo_full, 1);
+        sm100::mbar_init(sdp_full, 1);
+        sm100::mbar_init(ds_ready, 256);
+        sm100::mbar_init(dq_done, 1);
+        for (int s = 0; s < 2; ++s) {
+            sm100::mbar_init(stage_full(s), 1);
+            sm100::mbar_init(stage_empty(s), 1);
+        }
+        sm100::mbar_fence_init();
+    }
+    if (warp == 1) {
+        sm100::tmem_alloc(sm100::smem_u32(&tmem_slot), 512);
+    }
+    sm100::tc_fence_before_sync();
+    __syncthreads();
+    sm100::tc_fence_after_sync();
+    const uint32_t tmem = tmem_slot;
+    const uint32_t tmem_s = tmem, tmem_dp = tmem + 128, tmem_dq = tmem + 256;
+    volatile int* abort = &abort_flag;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            sm100::mbar_expect_tx(qdo_full, 2 * kTileBytes);
+            tma_load_4d(q_tile, &p.map_q, qdo_full, 0, qb * kTile, head, seq);
+            tma_load_4d(do_tile, &p.map_do, qdo_full, 0, qb * kTile, head, seq);
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int j = 0; j < iterations; ++j) {
+                if (!sm100::mbar_wait(stage_empty(stage), phase ^ 1u, abort)) {
+                    break;
+                }
+                const uint32_t dst = ring + stage * 2 * kTileBytes;
+                sm100::mbar_expect_tx(stage_full(stage), 2 * kTileBytes);
+                tma_load_4d(dst, &p.map_k, stage_full(stage), 0, j * kTile, head, seq);
+                tma_load_4d(dst + kTileBytes, &p.map_v, stage_full(stage), 0, j * kTile, head, seq);
+                if (++stage == 2) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            bool ok = sm100::mbar_wait(qdo_full, 0, abort);
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int j = 0; ok && j < iterations; ++j) {
+                if (!sm100::mbar_wait(stage_full(stage), phase, abort)) {
+                    break;
+                }
+                sm100::tc_fence_after_sync();
+                const uint32_t k_tile = ring + stage * 2 * kTileBytes;
+                const uint32_t v_tile = k_tile + kTileBytes;
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    sm100::mma_f16_ss(tmem_s, desc_kmajor(q_tile, ks), desc_kmajor(k_tile, ks),
+                                      kIdescS, ks > 0);
+                }
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    sm100::mma_f16_ss(tmem_dp, desc_kmajor(do_tile, ks), desc_kmajor(v_tile, ks),
+                                      kIdescS, ks > 0);
+                }
+                sm100::mma_commit(sdp_full);
+                if (!sm100::mbar_wait(ds_ready, j & 1, abort)) {
+                    break;
+                }
+                sm100::tc_fence_after_sync();
+                // dQ += dS K (K = the 128 keys of this tile; K tile read MN-major).
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    sm100::mma_f16_ss(tmem_dq, desc_kmajor_wide(ds_tile, ks),
+                                      desc_mnmajor(k_tile, ks, 16), kIdescPV, (j | ks) != 0);
+                }
+                sm100::mma_commit(stage_empty(stage));
+                if (j + 1 == iterations) {
+                    sm100::mma_commit(dq_done);
+                }
+                if (++stage == 2) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    } else {
+        const int quadrant = warp % 4;
+        const int half = (warp - 2) / 4;
+        const int row = quadrant * 32 + lane;
+        const int q_index = qb * kTile + row;
+        const bool row_valid = q_index < p.length;
+        const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
+        const float scale2 = p.scale * kLog2e;
+        float lse2 = 0.0f;
+        float dlt = 0.0f;
+        if (row_valid) {
+            lse2 = p.lse[static_cast<size_t>(bh) * p.length + q_index] * kLog2e;
+            dlt = p.delta[static_cast<size_t>(bh) * p.length + q_index];
+        }
+        bool ok = true;
+        for (int j = 0; ok && j < iterations; ++j) {
+            if (!sm100::mbar_wait(sdp_full, j & 1, abort)) {
+                ok = false;
+                break;
+            }
+            sm100::tc_fence_after_sync();
+            const bool diagonal = j == qb;
+#pragma unroll 1
+            for (int c = 0; c < 2; ++c) {
+                const int col = half * 64 + c * 32;
+                uint32_t s_raw[32];
+                uint32_t dp_raw[32];
+                sm100::tmem_ld_32x32(tmem_s + lane_base + col, s_raw);
+                sm100::tmem_ld_32x32(tmem_dp + lane_base + col, dp_raw);
+                sm100::tmem_ld_wait();
+                float dsv[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const bool visible = row_valid && (!diagonal || (col + i <= row));
+                    const float prob =
+                        visible ? exp2f(__uint_as_float(s_raw[i]) * scale2 - lse2) : 0.0f;
+                    dsv[i] = prob * (__uint_as_float(dp_raw[i]) - dlt) * p.scale;
+                }
+                store_operand_row(ds_tile, row, col, dsv);
+            }
+            fence_async_shared();
+            sm100::tc_fence_before_sync();
+            sm100::mbar_arrive(ds_ready);
+        }
+        if (ok && sm100::mbar_wait(dq_done, 0, abort)) {
+            sm100::tc_fence_after_sync();
+            uint32_t raw[32];
+            sm100::tmem_ld_32x32(tmem_dq + lane_base + half * 32, raw);
+            sm100::tmem_ld_wait();
+            if (row_valid) {
+                __half* out = static_cast<__half*>(p.out0) + seq * p.out_seq + head * p.out_head +
+                              static_cast<long long>(q_index) * p.out_row + half * 32;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    float a[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        a[i] = __uint_as_float(raw[c * 8 + i]);
+                    }
+                    *reinterpret_cast<uint4*>(out + c * 8) = fb::pack8(a);
+                }
+            }
+            sm100::tc_fence_before_sync();
+        }
+    }
+    finish(abort_flag, tmem, 512, warp);
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                 const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+cudaError_t encode_fn(EncodeTiled* out) {
+    static EncodeTiled cached = nullptr;
+    if (cached == nullptr) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult status;
+        const cudaError_t e =
+            cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &status);
+        if (e != cudaSuccess) {
+            return e;
+        }
+        if (status != cudaDriverEntryPointSuccess || fn == nullptr) {
+            return cudaErrorNotSupported;
+        }
+        cached = reinterpret_cast<EncodeTiled>(fn);
+    }
+    *out = cached;
+    return cudaSuccess;
+}
+
+// (column 0..63, row 0..length-1, head, sequence) view of an FP16 tensor.
+cudaError_t make_map(CUtensorMap* map, const AttentionView& v, const AttentionShape& s) {
+    EncodeTiled encode = nullptr;
+    const cudaError_t e = encode_fn(&encode);
+    if (e != cudaSuccess) {
+        return e;
+    }
+    const cuuint64_t dims[4] = {kHead, s.length, s.heads, s.sequences};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(v.row_stride) * 2,
+                                   static_cast<cuuint64_t>(v.head_stride) * 2,
+                                   static_cast<cuuint64_t>(v.sequence_stride) * 2};
+    const cuuint32_t box[4] = {kHead, kTile, 1, 1};
+    const cuuint32_t elem[4] = {1, 1, 1, 1};
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(v.base),
+                              dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+template <typename Kernel>
+cudaError_t configure(Kernel kernel, int smem, bool* done) {
+    if (*done) {
+        return cudaSuccess;
+    }
+    const cudaError_t e =
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess) {
+        *done = true;
+    }
+    return e;
+}
+
+AttnParams base_params(const AttentionShape& s, float scale) {
+    AttnParams p;
+    std::memset(&p, 0, sizeof p);
+    p.length = static_cast<int>(s.length);
+    p.heads = static_cast<int>(s.heads);
+    p.seqs = static_cast<int>(s.sequences);
+    p.blocks = static_cast<int>((s.length + kTile - 1) / kTile);
+    p.scale = scale;
+    return p;
+}
+
+}  // namespace
+
+cudaError_t attention_forward(const AttentionView& o, float* lse, const AttentionView& q,
+                              const AttentionView& k, const AttentionView& v,
+                              const AttentionShape& shape, float scale, cudaStream_t stream) {
+    AttnParams p = base_params(shape, scale);
+    cudaError_t e = make_map(&p.map_q, q, shape);
+    if (e == cudaSuccess) e = make_map(&p.map_k, k, shape);
+    if (e == cudaSuccess) e = make_map(&p.map_v, v, shape);
+    if (e != cudaSuccess) {
+        return e;
+    }
+    p.out0 = const_cast<void*>(o.base);
+    p.out_row = o.row_stride;
+    p.out_head = o.head_stride;
+    p.out_seq = o.sequence_stride;
+    p.lse = lse;
+    static bool configured = false;
+    e = configure(fb_attention_forward, kFwdSmem, &configured);
+    if (e != cudaSuccess) {
+        return e;
+    }
+    const unsigned grid = static_cast<unsigned>(shape.sequences * shape.heads * p.blocks);
+    fb_attention_forward<<<grid, kFwdThreads, kFwdSmem, stream>>>(p);
+    return cudaGetLastError();
+}
+
+cudaError_t attention_backward(const AttentionView& dq, const AttentionView& dk,
+                               const AttentionView& dv, const AttentionView& d_o,
+                               const AttentionView& o, const float* lse, float* delta,
+                               const AttentionView& q, const AttentionView& k,
+                               const AttentionView& v, const AttentionShape& shape, float scale,
+                               cudaStream_t stream) {
+    AttnParams p = base_params(shape, scale);
+    cudaError_t e = make_map(&p.map_q, q, shape);
+    if (e == cudaSuccess) e = make_map(&p.map_k, k, shape);
+    if (e == cudaSuccess) e = make_map(&p.map_v, v, shape);
+    if (e == cudaSuccess) e = make_map(&p.map_do, d_o, shape);
+    if (e != cudaSuccess) {
+        return e;
+    }
+    const long long rows = static_cast<long long>(shape.length) * shape.heads * shape.sequences;
+    int sms = 148;
+    sm_count(&sms);
+    const unsigned delta_grid =
+        static_cast<unsigned>(std::min<long long>((rows + 7) / 8, sms * 16LL));
+    const View vdo{static_cast<const __half*>(d_o.base), d_o.row_stride, d_o.head_stride,
+                   d_o.sequence_stride};
+    const View vo{static_cast<const __half*>(o.base), o.row_stride, o.head_stride,
+                  o.sequence_stride};
+    fb_attention_delta<<<delta_grid, 256, 0, stream>>>(delta, vdo, vo, p.length, p.heads, p.seqs);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        return e;
+    }
+    p.lse = const_cast<float*>(lse);
+    p.delta = delta;
+    const unsigned grid = static_cast<unsigned>(shape.sequences * shape.heads * p.blocks);
+
+    static bool dkv_configured = false;
+    e = configure(fb_attention_dkv, kDkvSmem, &dkv_configured);
+    if (e != cudaSuccess) {
+        return e;
+    }
+    // dK and dV must share strides (they do in both supported layouts).
+    p.out0 = const_cast<void*>(dk.base);
+    p.out1 = const_cast<void*>(dv.base);
+    p.out_row = dk.row_stride;
+    p.out_head = dk.head_stride;
+    p.out_seq = dk.sequence_stride;
+    fb_attention_dkv<<<grid, kBwdThreads, kDkvSmem, stream>>>(p);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        return e;
+    }
+    static bool dq_configured = false;
+    e = configure(fb_attention_dq, kDqSmem, &dq_configured);
+    if (e != cudaSuccess) {
+        return e;
+    }
+    p.out0 = const_cast<void*>(dq.base);
+    p.out1 = nullptr;
+    p.out_row = dq.row_stride;
+    p.out_head = dq.head_stride;
+    p.out_seq = dq.sequence_stride;
+    fb_attention_dq<<<grid, kBwdThreads, kDqSmem, stream>>>(p);
+    return cudaGetLastError();
+}
+
+cudaError_t attention_error_flag(int* value, bool reset) {
+    cudaError_t e = cudaMemcpyFromSymbol(value, g_attention_error, sizeof(int));
+    if (e == cudaSuccess && reset && *value != 0) {
+        const int zero = 0;
+        e = cudaMemcpyToSymbol(g_attention_error, &zero, sizeof(int));
+    }
+    return e;
+}
+
+}  // namespace fb
+
+namespace {
+
+constexpr flint_status kBad = FLINT_ERROR_INVALID_ARGUMENT;
+
+flint_status check_attention_dims(const char* name, size_t batches, size_t length,
+                                  size_t head_width, float scale) {
+    if (head_width != 64) {
+        return fb::fail(kBad, "%s: head_width (%zu) must be 64", name, head_width);
+    }
+    if (length % 8 != 0 || length > 1024) {
+        return fb::fail(kBad, "%s: length (%zu) must be a multiple of 8 up to 1024", name, length);
+    }
+    if (batches > 65535) {
+        return fb::fail(kBad, "%s: batches (%zu) can be up to 65535", name, batches);
+    }
+    if (!std::isfinite(scale)) {
+        return fb::fail(kBad, "%s: scale (%g) must be finite", name, static_cast<double>(scale));
+    }
+    return FLINT_OK;
+}
+
+fb::AttentionView heads_view(const void* base, size_t batches, size_t length) {
+    return fb::AttentionView{base, 64, static_cast<long long>(length) * 64,
+                             static_cast<long long>(batches * length) * 64};
+}
+
+}  // namespace
 
 extern "C" {
 
-flint_status flint_b200_attention_forward(void*, void*, const void*, const void*, const void*,
-                                          size_t, size_t, size_t, float, flint_stream) {
-    return fb::fail(FLINT_ERROR_INVALID_ARGUMENT,
-                    "flint_b200_attention_forward: not available in this build");
+flint_status flint_b200_attention_forward(void* o, void* lse, const void* q, const void* k,
+                                          const void* v, size_t batches, size_t length,
+                                          size_t head_width, float scale, flint_stream stream) {
+    constexpr const char* name = "flint_b200_attention_forward";
+    FB_TRY(check_attention_dims(name, batches, length, head_width, scale));
+    if (batches == 0 || length == 0) {
+        return FLINT_OK;
+    }
+    const size_t bytes = batches * length * 64 * 2;
+    const fb::Span spans[] = {
+        {"o", o, bytes}, {"lse", lse, batches * length * 4}, {"q", q, bytes},
+        {"k", k, bytes}, {"v", v, bytes},
+    };
+    FB_TRY(fb::check_spans(name, spans, 2));
+    const fb::AttentionShape shape{1, batches, length};
+    FB_CUDA(fb::attention_forward(heads_view(o, batches, length), static_cast<float*>(lse),
+                                  heads_view(q, batches, length), heads_view(k, batches, length),
+                                  heads_view(v, batches, length), shape, scale, stream));
+    return FLINT_OK;
 }
 
-flint_status flint_b200_attention_backward(void*, void*, void*, const void*, const void*,
-                                           const void*, void*, const void*, const void*,
-                                           const void*, size_t, size_t, size_t, float,
-                                           flint_stream) {
-    return fb::fail(FLINT_ERROR_INVALID_ARGUMENT,
-                    "flint_b200_attention_backward: not available in this build");
+flint_status flint_b200_attention_backward(void* dq, void* dk, void* dv, const void* d_o,
+                                           const void* o, const void* lse, void* delta,
+                                           const void* q, const void* k, const void* v,
+                                           size_t batches, size_t length, size_t head_width,
+                                           float scale, flint_stream stream) {
+    constexpr const char* name = "flint_b200_attention_backward";
+    FB_TRY(check_attention_dims(name, batches, length, head_width, scale));
+    if (batches == 0 || length == 0) {
+        return FLINT_OK;
+    }
+    const size_t bytes = batches * length * 64 * 2;
+    const size_t stats = batches * length * 4;
+    const fb::Span spans[] = {
+        {"dq", dq, bytes},   {"dk", dk, bytes}, {"dv", dv, bytes}, {"delta", delta, stats},
+        {"d_o", d_o, bytes}, {"o", o, bytes},   {"lse", lse, stats}, {"q", q, bytes},
+        {"k", k, bytes},     {"v", v, bytes},
+    };
+    FB_TRY(fb::check_spans(name, spans, 4));
+    const fb::AttentionShape shape{1, batches, length};
+    FB_CUDA(fb::attention_backward(heads_view(dq, batches, length), heads_view(dk, batches, length),
+                                   heads_view(dv, batches, length), heads_view(d_o, batches, length),
+                                   heads_view(o, batches, length), static_cast<const float*>(lse),
+                                   static_cast<float*>(delta), heads_view(q, batches, length),
+                                   heads_view(k, batches, length), heads_view(v, batches, length), shape, scale,
+                                   stream));
+    return FLINT_OK;
 }
 
 }  // extern "C"

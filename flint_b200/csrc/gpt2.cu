@@ -18,6 +18,9 @@
 #include <new>
 #include <string>
 
+#include <cuda_fp16.h>
+
+#include "attention.h"
 #include "common.h"
 #include "flint/flint_b200.h"
 #include "gpt2.h"
@@ -191,12 +194,16 @@ flint_status plan(flint_gpt2& m) {
         want(m, &a.h1, rows16);
         want(m, &a.mean1, rows * 4);
         want(m, &a.rstd1, rows * 4);
-        want(m, &a.q, heads16);
-        want(m, &a.k, heads16);
-        want(m, &a.v, heads16);
         if (m.flash) {
+            // The fused kernels read Q, K and V straight from the packed qkv rows.
+            if (backward) {
+                want(m, &a.qkv, rows * 3 * w * 2);
+            }
             want(m, &a.lse, stats);
         } else {
+            want(m, &a.q, heads16);
+            want(m, &a.k, heads16);
+            want(m, &a.v, heads16);
             want(m, &a.p, matrix16);
         }
         want(m, &a.attn, rows16);
@@ -225,15 +232,19 @@ flint_status plan(flint_gpt2& m) {
         } else {
             want(m, &m.delta, stats);
         }
-        want(m, &m.heads_out, heads16);
+        if (!m.flash) {
+            want(m, &m.heads_out, heads16);
+        }
         FB_TRY(size_workspaces(m));
         want(m, &m.dres, residual);
         want(m, &m.dres_half, rows16);
         want(m, &m.dh, rows16);
         want(m, &m.dpre, wide16);
-        want(m, &m.dq, heads16);
-        want(m, &m.dk, heads16);
-        want(m, &m.dv, heads16);
+        if (!m.flash) {
+            want(m, &m.dq, heads16);
+            want(m, &m.dk, heads16);
+            want(m, &m.dv, heads16);
+        }
         want(m, &m.workspace, m.workspace_bytes);
         want(m, &m.tn_workspace, m.tn_workspace_bytes);
     } else {
@@ -246,8 +257,8 @@ flint_status plan(flint_gpt2& m) {
         want(m, &m.qkv, rows * 3 * w * 2);
         if (!m.flash) {
             want(m, &m.scores, matrix16);
+            want(m, &m.heads_out, heads16);
         }
-        want(m, &m.heads_out, heads16);
         want(m, &a.gelu, wide16);
         want(m, &a.pre, wide16);
     }
@@ -302,6 +313,7 @@ void link(flint_gpt2& m) {
         return;
     }
     BlockBuffers& shared = m.blocks[0];
+    shared.qkv = m.qkv;
     shared.x_out = shared.x_in;
     shared.h2 = shared.h1;
     shared.mean2 = shared.mean1;
@@ -313,6 +325,13 @@ void link(flint_gpt2& m) {
     m.h_f = shared.h1;
     m.mean_f = shared.mean1;
     m.rstd_f = shared.rstd1;
+}
+
+// Heads of 64 columns inside rows of `row_width` FP16 values, starting at column `first`.
+fb::AttentionView rows_view(const void* base, size_t first, size_t row_width, size_t length) {
+    return fb::AttentionView{static_cast<const __half*>(base) + first,
+                             static_cast<long long>(row_width), 64,
+                             static_cast<long long>(length * row_width)};
 }
 
 float score_scale(size_t head_width) { return 1.0f / std::sqrt(static_cast<float>(head_width)); }
@@ -332,23 +351,28 @@ flint_status forward_block(const flint_gpt2& m, size_t i, flint_stream s) {
     const size_t hw = m.head_width;
 
     FB_TRY(layernorm(m, wt.ln1_w, wt.ln1_b, a.x_in, a.h1, a.mean1, a.rstd1, s));
-    FB_TRY(flint_gemm_nt_bias(m.qkv, a.h1, wt.attn_w->half, wt.attn_b->data, rows, 3 * w, w, s));
-    void* const parts[] = {a.q, a.k, a.v};
-    for (size_t j = 0; j < 3; ++j) {
-        FB_TRY(flint_heads_split(parts[j], m.qkv, c.sequences, c.length, c.heads, hw, 3 * w, j * w,
-                                 s));
-    }
     if (m.flash) {
-        FB_TRY(flint_b200_attention_forward(m.heads_out, a.lse, a.q, a.k, a.v, m.head_batches,
-                                            c.length, hw, score_scale(hw), s));
+        FB_TRY(flint_gemm_nt_bias(a.qkv, a.h1, wt.attn_w->half, wt.attn_b->data, rows, 3 * w, w, s));
+        FB_CUDA(fb::attention_forward(rows_view(a.attn, 0, w, c.length), static_cast<float*>(a.lse),
+                                      rows_view(a.qkv, 0, 3 * w, c.length),
+                                      rows_view(a.qkv, w, 3 * w, c.length),
+                                      rows_view(a.qkv, 2 * w, 3 * w, c.length),
+                                      fb::AttentionShape{c.sequences, c.heads, c.length},
+                                      score_scale(hw), s));
     } else {
+        FB_TRY(flint_gemm_nt_bias(m.qkv, a.h1, wt.attn_w->half, wt.attn_b->data, rows, 3 * w, w, s));
+        void* const parts[] = {a.q, a.k, a.v};
+        for (size_t j = 0; j < 3; ++j) {
+            FB_TRY(flint_heads_split(parts[j], m.qkv, c.sequences, c.length, c.heads, hw, 3 * w,
+                                     j * w, s));
+        }
         FB_TRY(flint_gemm_nt_batched(m.scores, a.q, a.k, m.head_batches, c.length, c.length, hw,
                                      score_scale(hw), s));
         FB_TRY(flint_causal_softmax_forward(a.p, m.scores, m.head_batches, c.length, s));
         FB_TRY(flint_gemm_nn_batched(m.heads_out, a.p, a.v, m.head_batches, c.length, hw, c.length,
                                      s));
+        FB_TRY(flint_heads_merge(a.attn, m.heads_out, c.sequences, c.length, c.heads, hw, w, 0, s));
     }
-    FB_TRY(flint_heads_merge(a.attn, m.heads_out, c.sequences, c.length, c.heads, hw, w, 0, s));
     FB_TRY(flint_gemm_nt_bias_residual(a.x_mid, a.attn, wt.proj_w->half, wt.proj_b->data, a.x_in,
                                        rows, w, w, s));
     FB_TRY(layernorm(m, wt.ln2_w, wt.ln2_b, a.x_mid, a.h2, a.mean2, a.rstd2, s));
@@ -405,15 +429,18 @@ flint_status backward_block(const flint_gpt2& m, size_t i, int accumulate, flint
     FB_TRY(weight_gradient(m, wt.proj_w, m.dres_half, a.attn, accumulate, s));
     FB_TRY(bias_gradient(m, wt.proj_b, m.dres_half, accumulate, s));
     FB_TRY(flint_gemm_nn(m.dh, m.dres_half, wt.proj_w->half, rows, w, w, s));
-    // dO in the heads layout, reusing the forward pass's heads buffer.
     if (m.flash) {
-        // The fused backward reads dO and O in the heads layout. dpre is free
-        // here (the MLP's backward pass is done with it) and holds dO.
-        FB_TRY(flint_heads_split(m.dpre, m.dh, c.sequences, len, c.heads, hw, w, 0, s));
-        FB_TRY(flint_heads_split(m.heads_out, a.attn, c.sequences, len, c.heads, hw, w, 0, s));
-        FB_TRY(flint_b200_attention_backward(m.dq, m.dk, m.dv, m.dpre, m.heads_out, a.lse, m.delta,
-                                             a.q, a.k, a.v, hb, len, hw, score_scale(hw), s));
+        // dO is dh (rows layout), O is the saved attention output, and dQ, dK, dV land
+        // directly in the packed qkv gradient rows.
+        FB_CUDA(fb::attention_backward(
+            rows_view(m.qkv, 0, 3 * w, len), rows_view(m.qkv, w, 3 * w, len),
+            rows_view(m.qkv, 2 * w, 3 * w, len), rows_view(m.dh, 0, w, len),
+            rows_view(a.attn, 0, w, len), static_cast<const float*>(a.lse),
+            static_cast<float*>(m.delta), rows_view(a.qkv, 0, 3 * w, len),
+            rows_view(a.qkv, w, 3 * w, len), rows_view(a.qkv, 2 * w, 3 * w, len),
+            fb::AttentionShape{c.sequences, c.heads, len}, score_scale(hw), s));
     } else {
+        // dO in the heads layout, reusing the forward pass's heads buffer.
         FB_TRY(flint_heads_split(m.heads_out, m.dh, c.sequences, len, c.heads, hw, w, 0, s));
         FB_TRY(flint_gemm_tn_batched(m.dv, a.p, m.heads_out, hb, len, hw, len, s));
         FB_TRY(flint_gemm_nt_batched(m.scores, m.heads_out, a.v, hb, len, len, hw, 1.0f, s));
@@ -421,10 +448,11 @@ flint_status backward_block(const flint_gpt2& m, size_t i, int accumulate, flint
                                              s));
         FB_TRY(flint_gemm_nn_batched(m.dq, m.scores, a.k, hb, len, hw, len, s));
         FB_TRY(flint_gemm_tn_batched(m.dk, m.scores, a.q, hb, len, hw, len, s));
-    }
-    const void* const parts[] = {m.dq, m.dk, m.dv};
-    for (size_t j = 0; j < 3; ++j) {
-        FB_TRY(flint_heads_merge(m.qkv, parts[j], c.sequences, len, c.heads, hw, 3 * w, j * w, s));
+        const void* const parts[] = {m.dq, m.dk, m.dv};
+        for (size_t j = 0; j < 3; ++j) {
+            FB_TRY(flint_heads_merge(m.qkv, parts[j], c.sequences, len, c.heads, hw, 3 * w, j * w,
+                                     s));
+        }
     }
     FB_TRY(weight_gradient(m, wt.attn_w, m.qkv, a.h1, accumulate, s));
     FB_TRY(bias_gradient(m, wt.attn_b, m.qkv, accumulate, s));
@@ -439,6 +467,10 @@ flint_status create(const char* name, const flint_gpt2_config* config, bool flas
     }
     *model = nullptr;
     FB_TRY(check_config(name, config));
+    if (flash && config->width / config->heads != 64) {
+        return fb::fail(kInvalid, "%s: flash attention needs heads of width 64, not %zu", name,
+                        config->width / config->heads);
+    }
     try {
         auto m = std::make_unique<flint_gpt2>();
         m->config = *config;
@@ -657,6 +689,19 @@ flint_status flint_b200_gpt2_gradient_arena(const flint_gpt2* model, void** base
     }
     *base = model->gradient_base;
     *bytes = model->gradient_bytes;
+    return FLINT_OK;
+}
+
+flint_status flint_b200_gpt2_compute_copy(const flint_gpt2* model, size_t index, void** address) {
+    constexpr const char* name = "flint_b200_gpt2_compute_copy";
+    if (model == nullptr || address == nullptr) {
+        return fb::fail(kInvalid, "%s: model and address must not be null", name);
+    }
+    if (index >= model->tensors.size()) {
+        return fb::fail(kInvalid, "%s: index (%zu) must be below %zu", name, index,
+                        model->tensors.size());
+    }
+    *address = model->tensors[index].half;
     return FLINT_OK;
 }
 

@@ -32,6 +32,7 @@ struct BlockBuffers {
     void* q = nullptr;       // FP16 heads layout [B, H, T, hw]
     void* k = nullptr;
     void* v = nullptr;
+    void* qkv = nullptr;     // FP16 packed qkv rows [rows, 3 width] (flash attention only)
     void* p = nullptr;       // FP16 probabilities [B*H, T, T] (unfused attention only)
     void* lse = nullptr;     // FP32 log-sum-exp [B*H, T] (flash attention only)
     void* attn = nullptr;    // FP16 merged attention output [rows, width]

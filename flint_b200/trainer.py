@@ -1,0 +1,244 @@
+"""Data-parallel GPT-2 training step over the C ABI (one process per GPU).
+
+The reference has no trainer in C++ (its README lists the optimizer, loss
+scaling and multi-GPU as planned); what a step must do is fixed by its PyTorch
+oracle, ``scripts/gpt2_torch.py:161-192``: forward and backward in FP16 with
+FP32 accumulation and a dynamic loss scale, AdamW (lr 6e-4, betas 0.9/0.95,
+eps 1e-8, weight decay 0.1 on parameters with two or more dimensions), and a
+step that is skipped, with the scale halved, when a gradient is not finite.
+
+Here every kernel is the library's: ``flint_gpt2_forward`` /
+``flint_b200_gpt2_backward_buckets`` on a model built on the fused attention
+kernels, ``flint_b200_check_gradients`` and one multi-tensor
+``flint_b200_adamw_run`` that also refreshes the FP16 weight copies. With more
+than one rank the FP32 gradients are summed by NCCL all-reduce over
+NVLink/NVSwitch, one contiguous bucket per transformer block, started from the
+backward pass's bucket callback on a second stream so the transfers overlap the
+remaining backward kernels. Each rank scales its loss by
+``loss_scale / (rows_per_rank * world)``, so the plain sum is the gradient of
+the global mean loss and every rank takes the same skip decision.
+"""
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from .binding import Flint, Gpt2, Gpt2Config
+
+
+@dataclass
+class TrainerConfig:
+    layers: int = 12
+    heads: int = 12
+    width: int = 768
+    block_size: int = 1024
+    vocab: int = 50257
+    padded_vocab: int = 50304
+    sequences: int = 16          # per rank
+    length: int = 1024
+    lr: float = 6e-4
+    beta1: float = 0.9
+    beta2: float = 0.95
+    eps: float = 1e-8
+    weight_decay: float = 0.1
+    loss_scale: float = 65536.0  # GradScaler's initial scale
+    growth_interval: int = 2000
+    max_grad_norm: float = 0.0   # 0 disables clipping
+    flash_attention: bool = True
+
+
+class _DeviceView:
+    """Zero-copy torch view of raw device memory (the CUDA array interface)."""
+
+    def __init__(self, address: int, count: int, typestr: str = "<f4"):
+        self.__cuda_array_interface__ = {
+            "shape": (count,), "typestr": typestr, "data": (address, False), "version": 2,
+        }
+
+
+def device_tensor(address: int, count: int, typestr: str = "<f4") -> torch.Tensor:
+    return torch.as_tensor(_DeviceView(address, count, typestr), device="cuda")
+
+
+def initial_weights(config: TrainerConfig, seed: int = 1234) -> dict:
+    """GPT-2's initialisation from a CPU generator, in named_parameters order: N(0, 0.02)
+    for the embeddings and linear weights, the residual projections scaled by
+    1/sqrt(2 layers), zero biases, LayerNorm gain 1, padded wte rows zero."""
+    gen = torch.Generator("cpu").manual_seed(seed)
+    w = config.width
+    std = 0.02
+    residual = std / math.sqrt(2 * config.layers)
+    state = {}
+
+    def normal(name, shape, sigma):
+        state[name] = torch.empty(shape).normal_(0.0, sigma, generator=gen)
+
+    normal("wte.weight", (config.padded_vocab, w), std)
+    normal("wpe.weight", (config.block_size, w), std)
+    for i in range(config.layers):
+        p = f"blocks.{i}."
+        state[p + "ln_1.weight"] = torch.ones(w)
+        state[p + "ln_1.bias"] = torch.zeros(w)
+        normal(p + "attn.c_attn.weight", (3 * w, w), std)
+        state[p + "attn.c_attn.bias"] = torch.zeros(3 * w)
+        normal(p + "attn.c_proj.weight", (w, w), residual)
+        state[p + "attn.c_proj.bias"] = torch.zeros(w)
+        state[p + "ln_2.weight"] = torch.ones(w)
+        state[p + "ln_2.bias"] = torch.zeros(w)
+        normal(p + "mlp.c_fc.weight", (4 * w, w), std)
+        state[p + "mlp.c_fc.bias"] = torch.zeros(4 * w)
+        normal(p + "mlp.c_proj.weight", (w, 4 * w), residual)
+        state[p + "mlp.c_proj.bias"] = torch.zeros(w)
+    state["ln_f.weight"] = torch.ones(w)
+    state["ln_f.bias"] = torch.zeros(w)
+    state["wte.weight"][config.vocab:].zero_()
+    return state
+
+
+class LossScaler:
+    """torch.cuda.amp.GradScaler's policy on the host: halve on a non-finite step,
+    double after growth_interval consecutive good steps."""
+
+    def __init__(self, scale: float, growth_interval: int):
+        self.scale = float(scale)
+        self.growth_interval = growth_interval
+        self.good_steps = 0
+
+    def update(self, found_nonfinite: bool) -> None:
+        if found_nonfinite:
+            self.scale *= 0.5
+            self.good_steps = 0
+            return
+        self.good_steps += 1
+        if self.good_steps >= self.growth_interval:
+            self.scale *= 2.0
+            self.good_steps = 0
+
+
+def bucket_order(layers: int) -> list:
+    """Names of the gradient buckets in the order the backward pass completes them."""
+    return ["ln_f"] + [f"blocks.{i}" for i in reversed(range(layers))] + ["embeddings"]
+
+
+class Trainer:
+    """One rank of a data-parallel GPT-2 training job. `group` is a torch.distributed
+    process group (NCCL) or None for a single GPU."""
+
+    def __init__(self, flint: Flint, config: TrainerConfig, state: dict = None, group=None,
+                 seed: int = 1234):
+        self.flint = flint
+        self.config = config
+        self.group = group
+        self.world = 1
+        if group is not None:
+            import torch.distributed as dist
+
+            self.world = dist.get_world_size(group)
+        model_config = Gpt2Config(config.layers, config.heads, config.width, config.block_size,
+                                  config.vocab, config.padded_vocab, config.sequences,
+                                  config.length, 0, 1)
+        self.model = Gpt2(flint, model_config, flash_attention=config.flash_attention)
+        self.rows = config.sequences * config.length
+        self.stream = torch.cuda.current_stream()
+        self.comm_stream = torch.cuda.Stream() if self.world > 1 else None
+
+        state = state if state is not None else initial_weights(config, seed)
+        self.model.load({k: v.cuda() for k, v in state.items()})
+
+        self.parameters = self.model.parameters()
+        gradients = self.model.gradients()
+        arena, arena_bytes = self.model.gradient_arena()
+        self.gradient_address = arena
+        self.gradient_count = arena_bytes // 4
+        self.gradients = device_tensor(arena, self.gradient_count)
+        # Moments share the gradient arena's layout: one allocation each.
+        self.m = torch.zeros(self.gradient_count, device="cuda")
+        self.v = torch.zeros(self.gradient_count, device="cuda")
+        half = self._half_copies()
+        tensors = []
+        for (name, address, rows, cols), (_, grad, _, _) in zip(self.parameters, gradients):
+            offset = grad - arena
+            decay = config.weight_decay if rows > 1 else 0.0
+            tensors.append((address, self.m.data_ptr() + offset, self.v.data_ptr() + offset, grad,
+                            half.get(name), rows * cols, decay))
+        self.plan, self.plan_items = flint.adamw_plan(tensors)
+        self.found = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self.norm_squared = torch.zeros(1, dtype=torch.float64, device="cuda")
+        self.scaler = LossScaler(config.loss_scale, config.growth_interval)
+        self.step_count = 0
+        self.skipped = 0
+        self._events = []
+        torch.cuda.synchronize()
+
+    def _half_copies(self) -> dict:
+        """{parameter name: address of its FP16 compute copy}. The copies follow the
+        gradients in the model's arena in a fixed order: wte, then each block's four
+        matrices; their addresses come from the model's layout."""
+        import ctypes
+
+        out = {}
+        lib = self.flint.lib
+        if hasattr(lib, "flint_b200_gpt2_compute_copy"):
+            for index, (name, _, _, _) in enumerate(self.parameters):
+                address = ctypes.c_void_p()
+                self.flint.check(lib.flint_b200_gpt2_compute_copy(self.model.handle, index,
+                                                                  ctypes.byref(address)))
+                if address.value:
+                    out[name] = address.value
+        return out
+
+    def close(self) -> None:
+        self.model.close()
+
+    # -- one optimizer step ---------------------------------------------------------------
+
+    def _on_bucket(self, bucket: int, address: int, nbytes: int) -> None:
+        import torch.distributed as dist
+
+        ready = torch.cuda.Event()
+        ready.record(self.stream)
+        self.comm_stream.wait_event(ready)
+        view = device_tensor(address, nbytes // 4)
+        with torch.cuda.stream(self.comm_stream):
+            dist.all_reduce(view, op=dist.ReduceOp.SUM, group=self.group)
+
+    def step(self, tokens: torch.Tensor, targets: torch.Tensor) -> None:
+        """Enqueues forward, backward (with overlapped all-reduce), the gradient check and
+        the AdamW update for one micro-batch of uint16 tokens/targets on this rank."""
+        c = self.config
+        scale = self.scaler.scale / (self.rows * self.world)
+        self.model.forward(tokens, targets, scale)
+        if self.world > 1:
+            self.model.backward(tokens, False, callback=self._on_bucket)
+            done = torch.cuda.Event()
+            done.record(self.comm_stream)
+            self.stream.wait_event(done)
+        else:
+            self.model.backward(tokens, False)
+        self.found.zero_()
+        clip = c.max_grad_norm > 0
+        if clip:
+            self.norm_squared.zero_()
+        inverse = 1.0 / self.scaler.scale
+        self.flint.check_gradients(self.gradients, self.gradient_count, inverse, self.found,
+                                   self.norm_squared if clip else None)
+        grad_scale = inverse
+        if clip:
+            # The clip coefficient needs the norm on the host; clipping is off by default.
+            norm = math.sqrt(self.norm_squared.item())
+            if math.isfinite(norm) and norm > c.max_grad_norm:
+                grad_scale *= c.max_grad_norm / (norm + 1e-6)
+        self.step_count += 1
+        self.flint.adamw_run(self.plan, self.plan_items, c.lr, c.beta1, c.beta2, c.eps, grad_scale,
+                             self.step_count - self.skipped, self.found)
+
+    def finish_step(self) -> float:
+        """Waits for the step, updates the loss scale from the non-finite flag and returns
+        this rank's mean loss (a device-to-host read)."""
+        loss = self.model.mean_loss()
+        found = bool(self.found.item())
+        if found:
+            self.skipped += 1
+        self.scaler.update(found)
+        return loss

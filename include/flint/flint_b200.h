@@ -64,6 +64,12 @@ FLINT_API flint_status flint_b200_gpt2_backward_buckets(flint_gpt2* model, const
 FLINT_API flint_status flint_b200_gpt2_gradient_arena(const flint_gpt2* model, void** base,
                                                       size_t* bytes);
 
+/* The FP16 compute copy of the index-th master weight (what the GEMMs read), or
+ * null for biases and LayerNorm parameters, which have none. An optimizer that
+ * writes it together with the master weight saves flint_gpt2_sync_weights. */
+FLINT_API flint_status flint_b200_gpt2_compute_copy(const flint_gpt2* model, size_t index,
+                                                    void** address);
+
 /* Fused AdamW over `count` FP32 values (PyTorch semantics, decoupled decay):
  *   g = grad * grad_scale;  m = b1 m + (1 - b1) g;  v = b2 v + (1 - b2) g^2
  *   p = p - lr * (weight_decay * p + (m / (1 - b1^step)) / (sqrt(v / (1 - b2^step)) + eps))
@@ -75,6 +81,37 @@ FLINT_API flint_status flint_b200_adamw(void* param, void* m, void* v, const voi
                                         float beta2, float eps, float weight_decay,
                                         float grad_scale, int step, const int* skip,
                                         flint_stream stream);
+
+/* One tensor of a multi-tensor AdamW plan; half_copy may be null. */
+typedef struct {
+    void* param;
+    void* m;
+    void* v;
+    const void* grad;
+    void* half_copy;
+    size_t count;
+    float weight_decay;
+} flint_b200_adamw_tensor;
+
+/* A plan lets one launch update every tensor of a model. tensors is a host
+ * array; *bytes is the device memory the plan needs; *items is what
+ * flint_b200_adamw_run takes. */
+FLINT_API flint_status flint_b200_adamw_plan_bytes(const flint_b200_adamw_tensor* tensors,
+                                                   size_t count, size_t* bytes);
+FLINT_API flint_status flint_b200_adamw_plan_items(const flint_b200_adamw_tensor* tensors,
+                                                   size_t count, size_t* items);
+
+/* Writes the plan into device memory `plan` (16-byte aligned, plan_bytes long)
+ * and waits for the copy, so tensors may be freed on return. */
+FLINT_API flint_status flint_b200_adamw_plan(void* plan, size_t plan_bytes,
+                                             const flint_b200_adamw_tensor* tensors, size_t count,
+                                             flint_stream stream);
+
+/* flint_b200_adamw over every tensor of the plan, each with its own weight
+ * decay, in one launch. */
+FLINT_API flint_status flint_b200_adamw_run(const void* plan, size_t items, float lr, float beta1,
+                                            float beta2, float eps, float grad_scale, int step,
+                                            const int* skip, flint_stream stream);
 
 /* Sets *found_nonfinite (device int) to 1 if any of the count FP32 values is
  * inf or NaN; leaves it unchanged otherwise, so several calls can share it.

@@ -1,0 +1,62 @@
+"""Fused causal attention (extension) against the float64 oracle, on a B200.
+
+Oracle: softmax(scale * Q K^T + causal mask) V and its autograd gradients in float64
+(oracle.attention), the same chain the reference's tests/test_softmax_backward.py:1429-1440
+uses for its unfused kernels. Tolerance: relative Frobenius error <= 2e-3 forward (the
+GEMM bound) and <= 5e-3 for the gradients (P and dS round to FP16 before their GEMMs).
+"""
+
+import numpy as np
+import pytest
+import torch
+
+import flint_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def rel_error(got, want):
+    got = got.double().cpu()
+    want = torch.as_tensor(np.asarray(want)).double()
+    return ((got - want).norm() / want.norm().clamp_min(1e-300)).item()
+
+
+@pytest.mark.parametrize("batches, length", [(4, 128), (3, 256), (2, 1024), (5, 40), (2, 136),
+                                             (1, 8), (7, 520)])
+def test_attention_forward_and_backward(flint, batches, length):
+    g = torch.Generator().manual_seed(length)
+    q, k, v, d_o = (torch.randn(batches, length, 64, generator=g).half() for _ in range(4))
+    scale = 0.125
+    o = torch.full((batches, length, 64), 7.0, dtype=torch.half, device=DEV)
+    lse = torch.zeros(batches, length, device=DEV)
+    qd, kd, vd, dod = (t.to(DEV) for t in (q, k, v, d_o))
+    flint.attention_forward(o, lse, qd, kd, vd, batches, length, 64, scale)
+    dq, dk, dv = (torch.full((batches, length, 64), 7.0, dtype=torch.half, device=DEV)
+                  for _ in range(3))
+    delta = torch.zeros(batches, length, device=DEV)
+    flint.attention_backward(dq, dk, dv, dod, o, lse, delta, qd, kd, vd, batches, length, 64,
+                             scale)
+    torch.cuda.synchronize()
+    assert not flint.kernel_fault()
+    want_o, want_lse, want_dq, want_dk, want_dv = oracle.attention(q, k, v, scale, d_o)
+    assert rel_error(o, want_o) <= 2e-3
+    assert np.allclose(lse.cpu().numpy(), want_lse, rtol=1e-4, atol=1e-4)
+    assert rel_error(dq, want_dq) <= 5e-3
+    assert rel_error(dk, want_dk) <= 5e-3
+    assert rel_error(dv, want_dv) <= 5e-3
+
+
+def test_attention_is_deterministic_and_row_zero_copies_v(flint):
+    batches, length = 12, 1024
+    g = torch.Generator().manual_seed(1)
+    q, k, v = (torch.randn(batches, length, 64, generator=g).half().to(DEV) for _ in range(3))
+    outs = []
+    for fill in (1.0, -3.0):
+        o = torch.full((batches, length, 64), fill, dtype=torch.half, device=DEV)
+        lse = torch.zeros(batches, length, device=DEV)
+        flint.attention_forward(o, lse, q, k, v, batches, length, 64, 0.125)
+        outs.append(o)
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+    assert torch.equal(outs[0][:, 0].view(torch.int16), v[:, 0].view(torch.int16))

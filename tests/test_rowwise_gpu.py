@@ -299,7 +299,6 @@ def test_cross_entropy_loss_and_gradient(flint, shape):
     logits = (torch.randn(rows, cols, generator=g) * 2).half()
     logits[:, vocab:] = float("nan")  # padded columns are ignored
     targets = torch.randint(0, vocab, (rows,), generator=g)
-    logits[0, targets[0]] = 30.0  # a dominant target: loss exactly 0 after rounding
     scale = 65536.0 / rows
     dl = torch.full((rows, cols), 9.0, dtype=torch.half, device=DEV)
     loss = torch.zeros(rows, device=DEV)
@@ -317,6 +316,20 @@ def test_cross_entropy_loss_and_gradient(flint, shape):
     assert (negative.sum(1) <= 1).all()
     rows_with_negative = negative.any(1)
     assert (negative.argmax(1)[rows_with_negative] == targets.numpy()[rows_with_negative]).all()
+
+
+def test_cross_entropy_of_a_dominant_target_is_zero(flint):
+    rows, vocab, cols = 2, 50257, 50304
+    logits = torch.zeros(rows, cols, dtype=torch.half)
+    targets = torch.tensor([7, 50256])
+    logits[0, 7] = 60.0
+    logits[1, 50256] = 60.0
+    dl = torch.zeros(rows, cols, dtype=torch.half, device=DEV)
+    loss = torch.ones(rows, device=DEV)
+    flint.softmax_cross_entropy(dl, loss, logits.to(DEV), tokens16(targets.numpy()), 1.0, rows,
+                                vocab, cols)
+    torch.cuda.synchronize()
+    assert loss.cpu().tolist() == [0.0, 0.0]
 
 
 # ---- embedding backward --------------------------------------------------------------------------
