@@ -87,6 +87,7 @@ _C_TYPES = {
     "int*": ctypes.c_void_p,
     "const int*": ctypes.c_void_p,
     "double*": ctypes.c_void_p,
+    "unsigned long long*": ctypes.POINTER(ctypes.c_ulonglong),
     "size_t*": ctypes.POINTER(ctypes.c_size_t),
     "void**": ctypes.POINTER(ctypes.c_void_p),
     "const void**": ctypes.POINTER(ctypes.c_void_p),
@@ -353,6 +354,12 @@ class Flint:
         raised = ctypes.c_int(0)
         self.check(self.lib.flint_b200_kernel_fault(ctypes.addressof(raised)))
         return raised.value != 0
+
+    def launch_count(self) -> int:
+        """Kernels launched by the library in this process so far."""
+        count = ctypes.c_ulonglong(0)
+        self.check(self.lib.flint_b200_launch_count(ctypes.byref(count)))
+        return count.value
 
     def attention_forward(self, o, lse, q, k, v, batches, length, head_width, scale,
                           stream=None) -> None:

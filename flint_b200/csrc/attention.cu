@@ -861,7 +861,7 @@ cudaError_t attention_forward(const AttentionView& o, float* lse, const Attentio
     }
     const unsigned grid = static_cast<unsigned>(shape.sequences * shape.heads * p.blocks);
     fb_attention_forward<<<grid, kFwdThreads, kFwdSmem, stream>>>(p);
-    return cudaGetLastError();
+    return fb::after_launch();
 }
 
 cudaError_t attention_backward(const AttentionView& dq, const AttentionView& dk,
@@ -888,7 +888,7 @@ cudaError_t attention_backward(const AttentionView& dq, const AttentionView& dk,
     const View vo{static_cast<const __half*>(o.base), o.row_stride, o.head_stride,
                   o.sequence_stride};
     fb_attention_delta<<<delta_grid, 256, 0, stream>>>(delta, vdo, vo, p.length, p.heads, p.seqs);
-    e = cudaGetLastError();
+    e = fb::after_launch();
     if (e != cudaSuccess) {
         return e;
     }
@@ -908,7 +908,7 @@ cudaError_t attention_backward(const AttentionView& dq, const AttentionView& dk,
     p.out_head = dk.head_stride;
     p.out_seq = dk.sequence_stride;
     fb_attention_dkv<<<grid, kBwdThreads, kDkvSmem, stream>>>(p);
-    e = cudaGetLastError();
+    e = fb::after_launch();
     if (e != cudaSuccess) {
         return e;
     }
@@ -923,7 +923,7 @@ cudaError_t attention_backward(const AttentionView& dq, const AttentionView& dk,
     p.out_head = dq.head_stride;
     p.out_seq = dq.sequence_stride;
     fb_attention_dq<<<grid, kBwdThreads, kDqSmem, stream>>>(p);
-    return cudaGetLastError();
+    return fb::after_launch();
 }
 
 cudaError_t attention_error_flag(int* value, bool reset) {

@@ -1,6 +1,7 @@
 // Error slot, span checks, version and status strings (the GPU-free part of the ABI).
 #include "common.h"
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 
@@ -56,6 +57,17 @@ flint_status check_spans(const char* function, const Span* spans, size_t count, 
     }
     return FLINT_OK;
 }
+
+namespace {
+std::atomic<unsigned long long> g_launches{0};
+}
+
+cudaError_t after_launch() {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cudaGetLastError();
+}
+
+unsigned long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
 
 cudaError_t sm_count(int* sms) {
     constexpr int kMaxDevices = 64;

@@ -50,6 +50,11 @@ flint_status check_spans(const char* function, const Span (&spans)[N], size_t ou
     return check_spans(function, spans, N, outputs);
 }
 
+// cudaGetLastError() for the line after a kernel launch; also counts the launch
+// (flint_b200_launch_count reports the total).
+cudaError_t after_launch();
+unsigned long long launch_count();
+
 // Number of SMs of the current device (cached per device index).
 cudaError_t sm_count(int* sms);
 

@@ -684,7 +684,7 @@ cudaError_t launch_tc(GemmParams& p, const void* x, const void* w, int sms, cuda
     }
     const unsigned grid = static_cast<unsigned>(std::min<long long>(p.tiles_total, sms));
     kernel<<<grid, kThreads, R::kSmemBytes, stream>>>(p);
-    return cudaGetLastError();
+    return fb::after_launch();
 }
 
 template <Layout L, Epilogue E>
@@ -700,7 +700,7 @@ cudaError_t launch_any(GemmParams& p, const void* x, const void* w, cudaStream_t
             static_cast<unsigned>(std::min<long long>((total + 255) / 256, sms * 32LL));
         fb_gemm_simt<L, E><<<grid, 256, 0, stream>>>(p, static_cast<const __half*>(x),
                                                      static_cast<const __half*>(w));
-        return cudaGetLastError();
+        return fb::after_launch();
     }
     switch (pick_bn(static_cast<size_t>(p.n))) {
     case 256:
@@ -815,7 +815,7 @@ cudaError_t gemm_tn(void* y, const void* x, const void* w, size_t m, size_t n, s
     fb_gemm_tn_reduce<<<grid, 256, 0, stream>>>(static_cast<float4*>(y),
                                                 static_cast<const float4*>(workspace), quads,
                                                 s.count, p.accumulate);
-    return cudaGetLastError();
+    return fb::after_launch();
 }
 
 cudaError_t gemm_batched(Layout l, void* y, const void* x, const void* w, size_t batches,

@@ -188,7 +188,7 @@ flint_status move_heads(bool split, void* y, const void* x, size_t batches, size
             static_cast<unsigned>(head_width / 8), static_cast<unsigned>(row_width / 8),
             static_cast<unsigned>(first / 8), rows_per_block);
     }
-    FB_CUDA(cudaGetLastError());
+    FB_CUDA(fb::after_launch());
     return FLINT_OK;
 }
 
@@ -250,7 +250,7 @@ flint_status flint_copy(void* dst, const void* src, size_t bytes, flint_stream s
     if ((da - sa) % 16 != 0) {
         // No common 16-byte phase: byte loads (rare; the harness paths are aligned).
         fb_copy_bytes<<<grid_for(bytes, kThreads), kThreads, 0, stream>>>(d, s, bytes);
-        FB_CUDA(cudaGetLastError());
+        FB_CUDA(fb::after_launch());
         return FLINT_OK;
     }
     // Head up to the first 16-byte boundary, the aligned body, then the tail.
@@ -259,16 +259,16 @@ flint_status flint_copy(void* dst, const void* src, size_t bytes, flint_stream s
     const size_t tail = bytes - head - words * 16;
     if (head > 0) {
         fb_copy_bytes<<<1, 32, 0, stream>>>(d, s, head);
-        FB_CUDA(cudaGetLastError());
+        FB_CUDA(fb::after_launch());
     }
     if (words > 0) {
         fb_copy_words<<<grid_for(words, 2 * kThreads), kThreads, 0, stream>>>(
             reinterpret_cast<uint4*>(d + head), reinterpret_cast<const uint4*>(s + head), words);
-        FB_CUDA(cudaGetLastError());
+        FB_CUDA(fb::after_launch());
     }
     if (tail > 0) {
         fb_copy_bytes<<<1, 32, 0, stream>>>(d + head + words * 16, s + head + words * 16, tail);
-        FB_CUDA(cudaGetLastError());
+        FB_CUDA(fb::after_launch());
     }
     return FLINT_OK;
 }
@@ -290,7 +290,7 @@ flint_status flint_fp32_to_fp16(void* y, const void* x, size_t count, flint_stre
     FB_TRY(fb::check_spans(name, spans, 1));
     fb_fp32_to_fp16<<<grid_for(count / 8 + 1, kThreads), kThreads, 0, stream>>>(
         static_cast<__half*>(y), static_cast<const float*>(x), count);
-    FB_CUDA(cudaGetLastError());
+    FB_CUDA(fb::after_launch());
     return FLINT_OK;
 }
 
@@ -341,7 +341,7 @@ flint_status flint_embedding_forward(void* x, const void* tokens, const void* wt
         static_cast<float4*>(x), static_cast<const uint16_t*>(tokens),
         static_cast<const float4*>(wte), static_cast<const float4*>(wpe), rows, length,
         static_cast<unsigned>(width / 4));
-    FB_CUDA(cudaGetLastError());
+    FB_CUDA(fb::after_launch());
     return FLINT_OK;
 }
 

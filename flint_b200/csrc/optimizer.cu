@@ -304,7 +304,7 @@ flint_status flint_b200_adamw(void* param, void* m, void* v, const void* grad, v
         static_cast<float4*>(param), static_cast<float4*>(m), static_cast<float4*>(v),
         static_cast<const float4*>(grad), static_cast<uint2*>(half_copy), count / 4, count, a,
         skip);
-    FB_CUDA(cudaGetLastError());
+    FB_CUDA(fb::after_launch());
     return FLINT_OK;
 }
 
@@ -389,7 +389,7 @@ flint_status flint_b200_adamw_run(const void* plan, size_t items, float lr, floa
     fb_adamw_multi<<<grid, kThreads, 0, stream>>>(
         static_cast<const unsigned char*>(plan),
         make_args(lr, beta1, beta2, eps, 0.0f, grad_scale, step), skip);
-    FB_CUDA(cudaGetLastError());
+    FB_CUDA(fb::after_launch());
     return FLINT_OK;
 }
 
@@ -416,7 +416,15 @@ flint_status flint_b200_check_gradients(const void* grad, size_t count, float sc
     FB_TRY(fb::check_spans(name, spans, 0));
     fb_check_gradients<<<grid_for(count / 4 + 1), kThreads, 0, stream>>>(
         static_cast<const float*>(grad), count, scale, found_nonfinite, sum_squares);
-    FB_CUDA(cudaGetLastError());
+    FB_CUDA(fb::after_launch());
+    return FLINT_OK;
+}
+
+flint_status flint_b200_launch_count(unsigned long long* launches) {
+    if (launches == nullptr) {
+        return fb::fail(kInvalid, "flint_b200_launch_count: launches is null");
+    }
+    *launches = fb::launch_count();
     return FLINT_OK;
 }
 

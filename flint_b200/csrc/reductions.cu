@@ -168,7 +168,7 @@ cudaError_t launch_partials(void* workspace, const void* src, const void* x, con
     fb_column_partials<kSource><<<dim3(chunks, tiles), dim3(kTilePieces, kLaneRows), 0, stream>>>(
         static_cast<float4*>(workspace), src, static_cast<const float4*>(x),
         static_cast<const float*>(mean), static_cast<const float*>(rstd), rows, pieces);
-    return cudaGetLastError();
+    return fb::after_launch();
 }
 
 cudaError_t launch_finish(void* out, const void* workspace, size_t rows, size_t cols,
@@ -179,7 +179,7 @@ cudaError_t launch_finish(void* out, const void* workspace, size_t rows, size_t 
     fb_column_finish<<<blocks, 32 * kFinishWarps, 0, stream>>>(
         static_cast<float4*>(out), static_cast<const float4*>(workspace), chunks, quads,
         accumulate);
-    return cudaGetLastError();
+    return fb::after_launch();
 }
 
 // ---- LayerNorm backward: dx -----------------------------------------------------
@@ -634,7 +634,7 @@ cudaError_t launch_layernorm_backward(void* dx, void* dgamma, void* dbeta, const
         fb_layernorm_backward_dx<0><<<blocks, 32 * kWarpsPerBlock, 0, stream>>>(
             dxq, dyq, xq, mf, rf, gq, rows, pieces, accumulate_dx);
     }
-    return cudaGetLastError();
+    return fb::after_launch();
 }
 
 cudaError_t launch_embedding_backward(void* dwte, void* dwpe, const void* dx, const void* tokens,
@@ -661,32 +661,32 @@ cudaError_t launch_embedding_backward(void* dwte, void* dwpe, const void* dx, co
         uint16_t* to_tokens = pass == 0 ? pass_tokens : sorted_tokens;
         unsigned* to_rows = pass == 0 ? pass_rows : sorted_rows;
         fb_sort_count<<<tiles, kSortThreads, 0, stream>>>(counts, from_tokens, rows, shift);
-        cudaError_t e = cudaGetLastError();
+        cudaError_t e = fb::after_launch();
         if (e != cudaSuccess) {
             return e;
         }
         fb_sort_scan<<<1, 1024, 0, stream>>>(counts, entries);
-        e = cudaGetLastError();
+        e = fb::after_launch();
         if (e != cudaSuccess) {
             return e;
         }
         fb_sort_scatter<<<tiles, kSortThreads, 0, stream>>>(to_tokens, to_rows, from_tokens,
                                                             from_rows, counts, rows, shift);
-        e = cudaGetLastError();
+        e = fb::after_launch();
         if (e != cudaSuccess) {
             return e;
         }
     }
     fb_token_offsets<<<static_cast<unsigned>((vocab + 1 + 255) / 256), 256, 0, stream>>>(
         offsets, sorted_tokens, rows, static_cast<unsigned>(vocab));
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = fb::after_launch();
     if (e != cudaSuccess) {
         return e;
     }
     fb_word_gradient<<<static_cast<unsigned>(vocab), kWordThreads, 0, stream>>>(
         static_cast<float4*>(dwte), static_cast<const float4*>(dx), sorted_rows, offsets,
         static_cast<unsigned>(width / 4), accumulate_wte);
-    e = cudaGetLastError();
+    e = fb::after_launch();
     if (e != cudaSuccess) {
         return e;
     }

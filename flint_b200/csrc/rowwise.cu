@@ -505,7 +505,7 @@ flint_status flint_layernorm_forward(void* y, void* mean, void* rstd, const void
         fb_layernorm_forward_stream<1><<<blocks, kThreads, 0, stream>>>(yh, mf, rf, xf, gf, bf,
                                                                          rows, c, eps);
     }
-    FB_CUDA(cudaGetLastError());
+    FB_CUDA(fb::after_launch());
     return FLINT_OK;
 }
 
@@ -532,7 +532,7 @@ flint_status flint_causal_softmax_forward(void* p, const void* s, size_t batches
         fb_causal_softmax_forward<kMaxChunksPerLane><<<blocks, kThreads, 0, stream>>>(pq, sq, rows,
                                                                                       len);
     }
-    FB_CUDA(cudaGetLastError());
+    FB_CUDA(fb::after_launch());
     return FLINT_OK;
 }
 
@@ -567,7 +567,7 @@ flint_status flint_causal_softmax_backward(void* ds, const void* p, const void* 
         fb_causal_softmax_backward<kMaxChunksPerLane><<<blocks, kThreads, 0, stream>>>(
             dsq, pq, dpq, rows, len, scale);
     }
-    FB_CUDA(cudaGetLastError());
+    FB_CUDA(fb::after_launch());
     return FLINT_OK;
 }
 
@@ -625,7 +625,7 @@ flint_status flint_softmax_cross_entropy(void* dlogits, void* row_loss, const vo
         static_cast<uint4*>(dlogits), static_cast<float*>(row_loss),
         static_cast<const uint4*>(logits), static_cast<const uint16_t*>(targets), scale, rows,
         static_cast<int>(vocab), static_cast<int>(cols));
-    FB_CUDA(cudaGetLastError());
+    FB_CUDA(fb::after_launch());
     return FLINT_OK;
 }
 

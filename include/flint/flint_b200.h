@@ -20,6 +20,9 @@ extern "C" {
  * tests. */
 FLINT_API flint_status flint_b200_kernel_fault(int* raised);
 
+/* Kernels this library has launched in this process so far (host counter). */
+FLINT_API flint_status flint_b200_launch_count(unsigned long long* launches);
+
 /* Causal attention without materialising scores or probabilities:
  * o[b] = softmax(scale * q[b] k[b]^T + causal mask) v[b] for `batches`
  * (sequence, head) pairs, all FP16 [batches, length, head_width] contiguous;
