@@ -75,6 +75,18 @@ __device__ __forceinline__ void fence_async_shared() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// 2^x on the special-function unit (relative error about 2^-22, flushes denormals).
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Named barrier among the compute warps only (barrier 0 is __syncthreads).
+__device__ __forceinline__ void compute_sync(int threads) {
+    asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
+}
+
 // Writes 32 FP16 values (columns [col, col+32) of row `row`) of a 128 x 128
 // tile into the two-panel, 128-byte-swizzled operand layout.
 __device__ __forceinline__ void store_operand_row(uint32_t tile_base, int row, int col,
@@ -133,7 +145,7 @@ __device__ __forceinline__ void finish(int abort_value, uint32_t tmem_base, uint
 
 // ---- forward ---------------------------------------------------------------------------
 
-constexpr int kFwdThreads = 192;
+constexpr int kFwdThreads = 320;  // TMA warp, MMA warp, 8 softmax warps (2 threads per row)
 constexpr int kFwdSmem = 1024 + kTileBytes * 4 + 2 * kPanelBytes + 128;  // Q, 3-slot ring, P
 
 __global__ void __launch_bounds__(kFwdThreads, 2)
@@ -149,6 +161,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2)
     auto slot_empty = [&](int s) { return bars + 56 + 8u * s; };
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
+    __shared__ float pair_max[2][2][kTile];  // [iteration parity][column half][row]
 
     const int warp = threadIdx.x / 32;
     const int lane = threadIdx.x % 32;
@@ -162,7 +175,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2)
         abort_flag = 0;
         sm100::mbar_init(q_full, 1);
         sm100::mbar_init(s_full, 1);
-        sm100::mbar_init(p_ready, 128);
+        sm100::mbar_init(p_ready, 256);
         sm100::mbar_init(o_full, 1);
         for (int s = 0; s < 3; ++s) {
             sm100::mbar_init(slot_full(s), 1);
@@ -250,16 +263,19 @@ __global__ void __launch_bounds__(kFwdThreads, 2)
             }
         }
     } else {
+        // Two threads per query row: this one owns score columns [64 half, 64 half + 64)
+        // and output columns [32 half, 32 half + 32).
         const int quadrant = warp % 4;
-        const int row = quadrant * 32 + lane;            // query row inside the tile
+        const int half = (warp - 2) / 4;
+        const int row = quadrant * 32 + lane;
         const int q_index = qb * kTile + row;
         const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
         const float scale2 = p.scale * kLog2e;
-        float m = -INFINITY;
-        float l = 0.0f;
-        float o[kHead];
+        float m = -INFINITY;   // running row maximum (base-2 exponent units), shared by the pair
+        float l = 0.0f;        // this thread's share of the row sum
+        float o[32];
 #pragma unroll
-        for (int d = 0; d < kHead; ++d) {
+        for (int d = 0; d < 32; ++d) {
             o[d] = 0.0f;
         }
         bool ok = true;
@@ -270,35 +286,53 @@ __global__ void __launch_bounds__(kFwdThreads, 2)
             }
             sm100::tc_fence_after_sync();
             const bool diagonal = j == qb;
-            float mx = m;
+            float local = -INFINITY;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
+                const int col = half * 64 + c * 32;
                 uint32_t raw[32];
-                sm100::tmem_ld_32x32(tmem_s + lane_base + c * 32, raw);
+                sm100::tmem_ld_32x32(tmem_s + lane_base + col, raw);
                 sm100::tmem_ld_wait();
+                if (diagonal) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float t = __uint_as_float(raw[i]) * scale2;
-                    const bool visible = !diagonal || (c * 32 + i <= row);
-                    mx = visible ? fmaxf(mx, t) : mx;
+                    for (int i = 0; i < 32; ++i) {
+                        const float t = __uint_as_float(raw[i]) * scale2;
+                        local = (col + i <= row) ? fmaxf(local, t) : local;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        local = fmaxf(local, __uint_as_float(raw[i]) * scale2);
+                    }
                 }
             }
-            const float alpha = exp2f(m - mx);
+            pair_max[j & 1][half][row] = local;
+            compute_sync(256);
+            const float mx = fmaxf(m, fmaxf(local, pair_max[j & 1][half ^ 1][row]));
+            const float alpha = fast_exp2(m - mx);
             l *= alpha;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
+                const int col = half * 64 + c * 32;
                 uint32_t raw[32];
-                sm100::tmem_ld_32x32(tmem_s + lane_base + c * 32, raw);
+                sm100::tmem_ld_32x32(tmem_s + lane_base + col, raw);
                 sm100::tmem_ld_wait();
                 float v[32];
+                if (diagonal) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float t = __uint_as_float(raw[i]) * scale2;
-                    const bool visible = !diagonal || (c * 32 + i <= row);
-                    v[i] = visible ? exp2f(t - mx) : 0.0f;
-                    l += v[i];
+                    for (int i = 0; i < 32; ++i) {
+                        const float e = fast_exp2(fmaf(__uint_as_float(raw[i]), scale2, -mx));
+                        v[i] = (col + i <= row) ? e : 0.0f;
+                        l += v[i];
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        v[i] = fast_exp2(fmaf(__uint_as_float(raw[i]), scale2, -mx));
+                        l += v[i];
+                    }
                 }
-                store_operand_row(p_tile, row, c * 32, v);
+                store_operand_row(p_tile, row, col, v);
             }
             m = mx;
             fence_async_shared();
@@ -310,24 +344,25 @@ __global__ void __launch_bounds__(kFwdThreads, 2)
                 break;
             }
             sm100::tc_fence_after_sync();
+            uint32_t raw[32];
+            sm100::tmem_ld_32x32(tmem_o + lane_base + half * 32, raw);
+            sm100::tmem_ld_wait();
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t raw[32];
-                sm100::tmem_ld_32x32(tmem_o + lane_base + c * 32, raw);
-                sm100::tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    o[c * 32 + i] = fmaf(o[c * 32 + i], alpha, __uint_as_float(raw[i]));
-                }
+            for (int i = 0; i < 32; ++i) {
+                o[i] = fmaf(o[i], alpha, __uint_as_float(raw[i]));
             }
             sm100::tc_fence_before_sync();
         }
+        // The row sum is the two threads' shares added together.
+        pair_max[0][half][row] = l;
+        compute_sync(256);
+        const float total = l + pair_max[0][half ^ 1][row];
         if (ok && q_index < p.length) {
-            const float inv = 1.0f / l;
+            const float inv = 1.0f / total;
             __half* out = static_cast<__half*>(p.out0) + seq * p.out_seq + head * p.out_head +
-                          static_cast<long long>(q_index) * p.out_row;
+                          static_cast<long long>(q_index) * p.out_row + half * 32;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
+            for (int c = 0; c < 4; ++c) {
                 float v[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
@@ -335,7 +370,9 @@ __global__ void __launch_bounds__(kFwdThreads, 2)
                 }
                 *reinterpret_cast<uint4*>(out + c * 8) = fb::pack8(v);
             }
-            p.lse[static_cast<size_t>(bh) * p.length + q_index] = (m + log2f(l)) * kLn2;
+            if (half == 0) {
+                p.lse[static_cast<size_t>(bh) * p.length + q_index] = (m + log2f(total)) * kLn2;
+            }
         }
     }
     finish(abort_flag, tmem, 256, warp);
@@ -377,7 +414,7 @@ __global__ void __launch_bounds__(256)
 
 // ---- backward: dK and dV ------------------------------------------------------------------------
 
-constexpr int kBwdThreads = 320;  // TMA warp, MMA warp, 8 compute warps
+constexpr int kBwdThreads = 576;  // TMA warp, MMA warp, 16 compute warps (32 columns each)
 // K, V, 2 x (Q, dO), P, dS
 constexpr int kDkvSmem = 1024 + kTileBytes * 6 + 4 * kPanelBytes + 128;
 
@@ -411,7 +448,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         abort_flag = 0;
         sm100::mbar_init(kv_full, 1);
         sm100::mbar_init(sdp_full, 1);
-        sm100::mbar_init(pds_ready, 256);
+        sm100::mbar_init(pds_ready, 512);
         sm100::mbar_init(grads_done, 1);
         for (int s = 0; s < 2; ++s) {
             sm100::mbar_init(stage_full(s), 1);
@@ -504,7 +541,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         }
     } else {
         const int quadrant = warp % 4;
-        const int half = (warp - 2) / 4;                 // which 64 key columns
+        const int part = (warp - 2) / 4;                 // which 32 key columns
+        const int col = part * 32;
         const int row = quadrant * 32 + lane;            // query row inside the tile
         const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
         const float scale2 = p.scale * kLog2e;
@@ -513,7 +551,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             const int qb = kb + it;
             const int q_index = qb * kTile + row;
             const bool row_valid = q_index < p.length;
-            float lse2 = 0.0f;
+            // An invalid row gets lse = +inf, so its probabilities are exp2(-inf) = 0.
+            float lse2 = INFINITY;
             float dlt = 0.0f;
             if (row_valid) {
                 lse2 = p.lse[static_cast<size_t>(bh) * p.length + q_index] * kLog2e;
@@ -524,44 +563,47 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                 break;
             }
             sm100::tc_fence_after_sync();
-            const bool diagonal = it == 0;
-#pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-                const int col = half * 64 + c * 32;
-                uint32_t s_raw[32];
-                uint32_t dp_raw[32];
-                sm100::tmem_ld_32x32(tmem_s + lane_base + col, s_raw);
-                sm100::tmem_ld_32x32(tmem_dp + lane_base + col, dp_raw);
-                sm100::tmem_ld_wait();
-                float pv[32];
-                float dsv[32];
+            uint32_t s_raw[32];
+            uint32_t dp_raw[32];
+            sm100::tmem_ld_32x32(tmem_s + lane_base + col, s_raw);
+            sm100::tmem_ld_32x32(tmem_dp + lane_base + col, dp_raw);
+            sm100::tmem_ld_wait();
+            float pv[32];
+            float dsv[32];
+            if (it == 0) {
+                // The diagonal tile: keys after the query are masked.
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    const bool visible = row_valid && (!diagonal || (col + i <= row));
-                    const float prob =
-                        visible ? exp2f(__uint_as_float(s_raw[i]) * scale2 - lse2) : 0.0f;
-                    pv[i] = prob;
-                    dsv[i] = prob * (__uint_as_float(dp_raw[i]) - dlt) * p.scale;
+                    const float e = fast_exp2(fmaf(__uint_as_float(s_raw[i]), scale2, -lse2));
+                    pv[i] = (col + i <= row) ? e : 0.0f;
+                    dsv[i] = pv[i] * (__uint_as_float(dp_raw[i]) - dlt);
                 }
-                store_operand_row(p_tile, row, col, pv);
-                store_operand_row(ds_tile, row, col, dsv);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    pv[i] = fast_exp2(fmaf(__uint_as_float(s_raw[i]), scale2, -lse2));
+                    dsv[i] = pv[i] * (__uint_as_float(dp_raw[i]) - dlt);
+                }
             }
+            store_operand_row(p_tile, row, col, pv);
+            store_operand_row(ds_tile, row, col, dsv);
             fence_async_shared();
             sm100::tc_fence_before_sync();
             sm100::mbar_arrive(pds_ready);
         }
-        if (ok && sm100::mbar_wait(grads_done, 0, abort)) {
+        if (ok && part < 2 && sm100::mbar_wait(grads_done, 0, abort)) {
             sm100::tc_fence_after_sync();
-            // Rows of dV/dK are keys; this warp writes 32 of the 64 columns.
+            // Rows of dV/dK are keys; this warp writes 32 of the 64 columns. dS was kept
+            // unscaled, so the score scale is applied to dK here.
             const int k_index = kb * kTile + row;
             uint32_t dv_raw[32];
             uint32_t dk_raw[32];
-            sm100::tmem_ld_32x32(tmem_dv + lane_base + half * 32, dv_raw);
-            sm100::tmem_ld_32x32(tmem_dk + lane_base + half * 32, dk_raw);
+            sm100::tmem_ld_32x32(tmem_dv + lane_base + part * 32, dv_raw);
+            sm100::tmem_ld_32x32(tmem_dk + lane_base + part * 32, dk_raw);
             sm100::tmem_ld_wait();
             if (k_index < p.length) {
                 const long long at = seq * p.out_seq + head * p.out_head +
-                                     static_cast<long long>(k_index) * p.out_row + half * 32;
+                                     static_cast<long long>(k_index) * p.out_row + part * 32;
                 __half* dk_out = static_cast<__half*>(p.out0) + at;
                 __half* dv_out = static_cast<__half*>(p.out1) + at;
 #pragma unroll
@@ -570,7 +612,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                     float b[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
-                        a[i] = __uint_as_float(dk_raw[c * 8 + i]);
+                        a[i] = __uint_as_float(dk_raw[c * 8 + i]) * p.scale;
                         b[i] = __uint_as_float(dv_raw[c * 8 + i]);
                     }
                     *reinterpret_cast<uint4*>(dk_out + c * 8) = fb::pack8(a);
@@ -617,7 +659,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         abort_flag = 0;
         sm100::mbar_init(qdo_full, 1);
         sm100::mbar_init(sdp_full, 1);
-        sm100::mbar_init(ds_ready, 256);
+        sm100::mbar_init(ds_ready, 512);
         sm100::mbar_init(dq_done, 1);
         for (int s = 0; s < 2; ++s) {
             sm100::mbar_init(stage_full(s), 1);
@@ -701,13 +743,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         }
     } else {
         const int quadrant = warp % 4;
-        const int half = (warp - 2) / 4;
+        const int part = (warp - 2) / 4;
+        const int col = part * 32;
         const int row = quadrant * 32 + lane;
         const int q_index = qb * kTile + row;
         const bool row_valid = q_index < p.length;
         const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
         const float scale2 = p.scale * kLog2e;
-        float lse2 = 0.0f;
+        float lse2 = INFINITY;
         float dlt = 0.0f;
         if (row_valid) {
             lse2 = p.lse[static_cast<size_t>(bh) * p.length + q_index] * kLog2e;
@@ -720,43 +763,44 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                 break;
             }
             sm100::tc_fence_after_sync();
-            const bool diagonal = j == qb;
-#pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-                const int col = half * 64 + c * 32;
-                uint32_t s_raw[32];
-                uint32_t dp_raw[32];
-                sm100::tmem_ld_32x32(tmem_s + lane_base + col, s_raw);
-                sm100::tmem_ld_32x32(tmem_dp + lane_base + col, dp_raw);
-                sm100::tmem_ld_wait();
-                float dsv[32];
+            uint32_t s_raw[32];
+            uint32_t dp_raw[32];
+            sm100::tmem_ld_32x32(tmem_s + lane_base + col, s_raw);
+            sm100::tmem_ld_32x32(tmem_dp + lane_base + col, dp_raw);
+            sm100::tmem_ld_wait();
+            float dsv[32];
+            if (j == qb) {
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    const bool visible = row_valid && (!diagonal || (col + i <= row));
-                    const float prob =
-                        visible ? exp2f(__uint_as_float(s_raw[i]) * scale2 - lse2) : 0.0f;
-                    dsv[i] = prob * (__uint_as_float(dp_raw[i]) - dlt) * p.scale;
+                    const float e = fast_exp2(fmaf(__uint_as_float(s_raw[i]), scale2, -lse2));
+                    dsv[i] = (col + i <= row) ? e * (__uint_as_float(dp_raw[i]) - dlt) : 0.0f;
                 }
-                store_operand_row(ds_tile, row, col, dsv);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float e = fast_exp2(fmaf(__uint_as_float(s_raw[i]), scale2, -lse2));
+                    dsv[i] = e * (__uint_as_float(dp_raw[i]) - dlt);
+                }
             }
+            store_operand_row(ds_tile, row, col, dsv);
             fence_async_shared();
             sm100::tc_fence_before_sync();
             sm100::mbar_arrive(ds_ready);
         }
-        if (ok && sm100::mbar_wait(dq_done, 0, abort)) {
+        if (ok && part < 2 && sm100::mbar_wait(dq_done, 0, abort)) {
             sm100::tc_fence_after_sync();
             uint32_t raw[32];
-            sm100::tmem_ld_32x32(tmem_dq + lane_base + half * 32, raw);
+            sm100::tmem_ld_32x32(tmem_dq + lane_base + part * 32, raw);
             sm100::tmem_ld_wait();
             if (row_valid) {
                 __half* out = static_cast<__half*>(p.out0) + seq * p.out_seq + head * p.out_head +
-                              static_cast<long long>(q_index) * p.out_row + half * 32;
+                              static_cast<long long>(q_index) * p.out_row + part * 32;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     float a[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
-                        a[i] = __uint_as_float(raw[c * 8 + i]);
+                        a[i] = __uint_as_float(raw[c * 8 + i]) * p.scale;
                     }
                     *reinterpret_cast<uint4*>(out + c * 8) = fb::pack8(a);
                 }

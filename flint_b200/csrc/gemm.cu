@@ -9,7 +9,7 @@
 //   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16)
 //               from shared-memory descriptors into a tensor-memory accumulator;
 //               tcgen05.commit releases ring stages and publishes accumulators
-//   warps 2-5   epilogue: tcgen05.ld of the FP32 accumulators, the fused
+//   warps 2-9   epilogue: tcgen05.ld of the FP32 accumulators, the fused
 //               epilogue in registers, predicated global stores
 // Tensor memory holds two accumulators, so the epilogue of tile i overlaps the
 // main loop of tile i+1. Every k-block is 64 wide for every layout, so all
@@ -40,8 +40,8 @@ namespace {
 
 constexpr int kBM = 128;
 constexpr int kBK = 64;
-constexpr int kThreads = 192;
-constexpr int kEpilogueWarps = 4;
+constexpr int kEpilogueWarps = 8;  // two per TMEM lane quadrant, alternating 32-column chunks
+constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 constexpr int kRingBytes = 192 * 1024;
 constexpr int kGroupM = 8;  // rows of tiles handed out together, for L2 reuse
 
@@ -74,7 +74,7 @@ struct GemmParams {
 __device__ __forceinline__ float gelu_tanh(float x) {
     constexpr float kNeg2Rt2OverPi = -1.5957691216057308f;
     const float e = expf(kNeg2Rt2OverPi * x * fmaf(0.044715f, x * x, 1.0f));
-    return __fdiv_rn(x, 1.0f + e);
+    return __fdividef(x, 1.0f + e);
 }
 
 // d/dx of the above: s + x s (1 - s) * 2u', s = sigmoid(2u). For x >= 0,
@@ -84,7 +84,7 @@ __device__ __forceinline__ float gelu_tanh_grad(float x) {
     constexpr float k2Rt2OverPi = 1.5957691216057308f;
     constexpr float k6KappaRt2OverPi = 0.21406444946504453f;  // 2 sqrt(2/pi) * 3 * 0.044715
     const float e = expf(kNeg2Rt2OverPi * x * fmaf(0.044715f, x * x, 1.0f));
-    const float s = __fdiv_rn(1.0f, 1.0f + e);
+    const float s = __fdividef(1.0f, 1.0f + e);
     const float one_minus_s = x < 0.0f ? 1.0f - s : e * s;
     const float q = x * one_minus_s * fmaf(k6KappaRt2OverPi, x * x, k2Rt2OverPi);
     const float g = fmaf(s, q, s);
@@ -439,7 +439,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
     } else {
         // ---- epilogue warps ----
-        const int quadrant = warp % 4;  // the TMEM lanes this warp may read
+        const int quadrant = warp % 4;      // the TMEM lanes this warp may read
+        const int column_half = (warp - 2) / 4;  // which of the alternating 32-column chunks
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
@@ -458,8 +459,8 @@ __global__ void __launch_bounds__(kThreads, 1)
             const uint32_t t_addr = tmem_base + static_cast<uint32_t>(acc * BN) +
                                     (static_cast<uint32_t>(quadrant * 32) << 16);
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                const bool last = c + 32 >= BN;
+            for (int c = column_half * 32; c < BN; c += 64) {
+                const bool last = c + 64 >= BN;
                 const int col = col0 + c;
                 const int valid = min(32, p.n - col);  // warp-uniform
                 uint32_t raw[32];
@@ -468,7 +469,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     sm100::tmem_ld_wait();
                 }
                 if (last) {
-                    // Every read of this accumulator is complete: hand it back.
+                    // This warp's reads of the accumulator are complete: hand it back.
                     sm100::tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) {

@@ -56,35 +56,56 @@ __global__ void __launch_bounds__(kTilePieces * kLaneRows)
     const size_t end = rows - first < kChunkRows ? rows : first + kChunkRows;
 
     Comp acc[8];
-    if (piece < pieces) {
-        for (size_t r = first + ly; r < end; r += kLaneRows) {
-            const size_t at = r * pieces + piece;
-            float v[8];
-            if constexpr (kSource == Source::kFloat) {
-                fb::load8(v, static_cast<const float4*>(src) + at * 2);
+    // One row of this thread's stream: 8 values added in column order.
+    auto add_row = [&](const float (&v)[8], const float (&xs)[8], size_t r) {
+        if constexpr (kSource == Source::kHalfTimesXhat) {
+            const float m = mean[r];
+            const float rs = rstd[r];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    fb::comp_add(acc[j], v[j]);
-                }
-            } else {
-                fb::unpack8(v, static_cast<const uint4*>(src)[at]);
-                if constexpr (kSource == Source::kHalf) {
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        fb::comp_add(acc[j], v[j]);
-                    }
-                } else {
-                    float xs[8];
-                    fb::load8(xs, x + at * 2);
-                    const float m = mean[r];
-                    const float rs = rstd[r];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const float xhat = __fmul_rn(__fsub_rn(xs[j], m), rs);
-                        fb::comp_add_product(acc[j], v[j], xhat);
-                    }
-                }
+            for (int j = 0; j < 8; ++j) {
+                const float xhat = __fmul_rn(__fsub_rn(xs[j], m), rs);
+                fb::comp_add_product(acc[j], v[j], xhat);
             }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                fb::comp_add(acc[j], v[j]);
+            }
+        }
+    };
+    auto load_row = [&](float (&v)[8], float (&xs)[8], size_t r) {
+        const size_t at = r * pieces + piece;
+        if constexpr (kSource == Source::kFloat) {
+            fb::load8(v, static_cast<const float4*>(src) + at * 2);
+        } else {
+            fb::unpack8(v, static_cast<const uint4*>(src)[at]);
+            if constexpr (kSource == Source::kHalfTimesXhat) {
+                fb::load8(xs, x + at * 2);
+            }
+        }
+    };
+    if (piece < pieces) {
+        // The additions stay in row order; only the loads are issued ahead, kDepth rows
+        // at a time, so that their latencies overlap.
+        constexpr int kDepth = kSource == Source::kHalf ? 8 : 4;
+        size_t r = first + ly;
+        for (; r + (kDepth - 1) * kLaneRows < end; r += kDepth * kLaneRows) {
+            float v[kDepth][8];
+            float xs[kDepth][8];
+#pragma unroll
+            for (int d = 0; d < kDepth; ++d) {
+                load_row(v[d], xs[d], r + d * kLaneRows);
+            }
+#pragma unroll
+            for (int d = 0; d < kDepth; ++d) {
+                add_row(v[d], xs[d], r + d * kLaneRows);
+            }
+        }
+        for (; r < end; r += kLaneRows) {
+            float v[8];
+            float xs[8];
+            load_row(v, xs, r);
+            add_row(v, xs, r);
         }
     }
 #pragma unroll

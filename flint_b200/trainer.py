@@ -116,6 +116,12 @@ class LossScaler:
             self.good_steps = 0
 
 
+def cross_entropy_scale(loss_scale: float, rows_per_rank: int, world: int) -> float:
+    """The scale each rank hands to the fused cross-entropy so that the plain sum of the
+    ranks' gradients is loss_scale times the gradient of the global mean loss."""
+    return loss_scale / (rows_per_rank * world)
+
+
 def bucket_order(layers: int) -> list:
     """Names of the gradient buckets in the order the backward pass completes them."""
     return ["ln_f"] + [f"blocks.{i}" for i in reversed(range(layers))] + ["embeddings"]
@@ -207,7 +213,7 @@ class Trainer:
         """Enqueues forward, backward (with overlapped all-reduce), the gradient check and
         the AdamW update for one micro-batch of uint16 tokens/targets on this rank."""
         c = self.config
-        scale = self.scaler.scale / (self.rows * self.world)
+        scale = cross_entropy_scale(self.scaler.scale, self.rows, self.world)
         self.model.forward(tokens, targets, scale)
         if self.world > 1:
             self.model.backward(tokens, False, callback=self._on_bucket)
