@@ -5,7 +5,7 @@
 // One persistent, warp-specialised kernel template serves every layout and
 // epilogue:
 //   warp 0      TMA producer: 128-byte-swizzled operand tiles into a shared
-//               memory ring (no cluster multicast), one mbarrier per stage
+//               memory ring, one mbarrier per stage
 //   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16)
 //               from shared-memory descriptors into a tensor-memory accumulator;
 //               tcgen05.commit releases ring stages and publishes accumulators
@@ -510,6 +510,289 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
 }
 
+// ---- the CTA-pair kernel: 256 x 256 tiles --------------------------------------------------
+//
+// Two CTAs of a cluster work on one 256 x 256 output tile with
+// tcgen05.mma.cta_group::2 (M = 256, N = 256): CTA r of the pair loads rows
+// [128 r, 128 r + 128) of the A tile and the same range of the B tile (its half
+// of N), so each SM moves 32 KB per k-block instead of the 48 KB of a 128 x 256
+// single-CTA tile, and its tensor memory receives its own 128 rows of D. The
+// leader (rank 0) issues every MMA; commits reach both CTAs' barriers; the
+// peer's TMA transactions and epilogue arrivals are counted on the leader's
+// barriers. Roles per CTA are those of fb_gemm_tc.
+
+constexpr int kPairBN = 256;
+constexpr int kPairStageA = kBM * kBK * 2;          // 16 KB
+constexpr int kPairStageB = 128 * kBK * 2;          // 16 KB: half of the 256 B rows
+constexpr int kPairStage = kPairStageA + kPairStageB;
+constexpr int kPairStages = kRingBytes / kPairStage;  // 6
+constexpr int kPairSmemBytes = kPairStages * kPairStage + 1024 + 256;
+constexpr int kPairGroupM = 4;  // rows of 256-row tiles handed out together
+
+__device__ __forceinline__ TileCoord decode_pair_tile(const GemmParams& p, long long id) {
+    const long long per = static_cast<long long>(p.tiles_m) * p.tiles_n;
+    TileCoord c;
+    c.z = id / per;
+    const long long r = id - c.z * per;
+    const long long group_span = static_cast<long long>(kPairGroupM) * p.tiles_n;
+    const long long g = r / group_span;
+    const int first_m = static_cast<int>(g) * kPairGroupM;
+    const int rows_here = min(kPairGroupM, p.tiles_m - first_m);
+    const long long in_group = r - g * group_span;
+    c.tm = first_m + static_cast<int>(in_group % rows_here);
+    c.tn = static_cast<int>(in_group / rows_here);
+    return c;
+}
+
+template <Layout L, Epilogue E>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+    fb_gemm_pair(const __grid_constant__ GemmParams p) {
+    constexpr bool kAMn = L == Layout::kTN;
+    constexpr bool kBMn = L != Layout::kNT;
+    constexpr bool kIsTn = L == Layout::kTN;
+    constexpr uint32_t kIdesc = sm100::instr_desc_f16(256, kPairBN, kAMn, kBMn);
+    constexpr uint32_t kTmemCols = 512;
+
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t smem_base = (sm100::smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bars = smem_base + kPairStages * kPairStage;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (kPairStages + s); };
+    auto acc_full_bar = [&](int a) { return bars + 8u * (2 * kPairStages + a); };
+    auto acc_empty_bar = [&](int a) { return bars + 8u * (2 * kPairStages + 2 + a); };
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x / 32;
+    const int lane = threadIdx.x % 32;
+    const uint32_t rank = sm100::cluster_cta_rank();
+    const bool leader = rank == 0;
+    const long long pair = blockIdx.x / 2;
+    const long long pairs = gridDim.x / 2;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < kPairStages; ++s) {
+            sm100::mbar_init(full_bar(s), 1);
+            sm100::mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            sm100::mbar_init(acc_full_bar(a), 1);
+            sm100::mbar_init(acc_empty_bar(a), 2 * kEpilogueWarps);
+        }
+        sm100::mbar_fence_init();
+        sm100::tma_prefetch_descriptor(&p.map_a);
+        sm100::tma_prefetch_descriptor(&p.map_b);
+    }
+    if (warp == 1) {
+        sm100::tmem_alloc_pair(sm100::smem_u32(&tmem_base_slot), kTmemCols);
+    }
+    sm100::tc_fence_before_sync();
+    __syncthreads();
+    // Both CTAs' barriers exist before either touches the other's.
+    sm100::cluster_sync_all();
+    sm100::tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_slot;
+    volatile int* abort = &abort_flag;
+
+    if (warp == 0) {
+        // ---- TMA producer (both CTAs) ----
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (long long id = pair; ok && id < p.tiles_total; id += pairs) {
+                const TileCoord t = decode_pair_tile(p, id);
+                const bool split_k = kIsTn && !p.batched;
+                const int k0 = split_k ? static_cast<int>(t.z) * p.split_len : 0;
+                const int k1 = split_k ? min(p.k, k0 + p.split_len) : p.k;
+                const int batch = p.batched ? static_cast<int>(t.z) : 0;
+                const int row_a = t.tm * 256 + static_cast<int>(rank) * 128;
+                const int row_b = t.tn * kPairBN + static_cast<int>(rank) * 128;
+                for (int kk = k0; kk < k1; kk += kBK) {
+                    if (!sm100::mbar_wait(empty_bar(stage), phase ^ 1u, abort)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t a_dst = smem_base + stage * kPairStage;
+                    const uint32_t b_dst = a_dst + kPairStageA;
+                    if (leader) {
+                        // The leader's barrier counts both CTAs' bytes.
+                        sm100::mbar_expect_tx(full_bar(stage), 2 * kPairStage);
+                    }
+                    const uint32_t bar = sm100::map_to_cta(full_bar(stage), 0);
+                    if constexpr (!kAMn) {
+                        if (p.batched) {
+                            sm100::tma_load_3d_pair(a_dst, &p.map_a, bar, kk, row_a, batch);
+                        } else {
+                            sm100::tma_load_2d_pair(a_dst, &p.map_a, bar, kk, row_a);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            if (p.batched) {
+                                sm100::tma_load_3d_pair(a_dst + j * 8192, &p.map_a, bar,
+                                                        row_a + 64 * j, kk, batch);
+                            } else {
+                                sm100::tma_load_2d_pair(a_dst + j * 8192, &p.map_a, bar,
+                                                        row_a + 64 * j, kk);
+                            }
+                        }
+                    }
+                    if constexpr (!kBMn) {
+                        if (p.batched) {
+                            sm100::tma_load_3d_pair(b_dst, &p.map_b, bar, kk, row_b, batch);
+                        } else {
+                            sm100::tma_load_2d_pair(b_dst, &p.map_b, bar, kk, row_b);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            if (p.batched) {
+                                sm100::tma_load_3d_pair(b_dst + j * 8192, &p.map_b, bar,
+                                                        row_b + 64 * j, kk, batch);
+                            } else {
+                                sm100::tma_load_2d_pair(b_dst + j * 8192, &p.map_b, bar,
+                                                        row_b + 64 * j, kk);
+                            }
+                        }
+                    }
+                    if (++stage == kPairStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer (leader only) ----
+        if (leader && lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (long long id = pair; ok && id < p.tiles_total; id += pairs) {
+                const TileCoord t = decode_pair_tile(p, id);
+                const bool split_k = kIsTn && !p.batched;
+                const int k0 = split_k ? static_cast<int>(t.z) * p.split_len : 0;
+                const int k1 = split_k ? min(p.k, k0 + p.split_len) : p.k;
+                if (!sm100::mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abort)) {
+                    ok = false;
+                    break;
+                }
+                sm100::tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kPairBN);
+                uint32_t accumulate = 0;
+                for (int kk = k0; kk < k1; kk += kBK) {
+                    if (!sm100::mbar_wait(full_bar(stage), phase, abort)) {
+                        ok = false;
+                        break;
+                    }
+                    sm100::tc_fence_after_sync();
+                    const uint32_t a_addr = smem_base + stage * kPairStage;
+                    const uint32_t b_addr = a_addr + kPairStageA;
+#pragma unroll
+                    for (int ks = 0; ks < kBK / 16; ++ks) {
+                        const uint64_t a_desc =
+                            kAMn ? sm100::smem_desc_sw128(a_addr + ks * 2048, 8192, 1024)
+                                 : sm100::smem_desc_sw128(a_addr + ks * 32, 16, 1024);
+                        const uint64_t b_desc =
+                            kBMn ? sm100::smem_desc_sw128(b_addr + ks * 2048, 8192, 1024)
+                                 : sm100::smem_desc_sw128(b_addr + ks * 32, 16, 1024);
+                        sm100::mma_f16_ss_pair(d_tmem, a_desc, b_desc, kIdesc, accumulate);
+                        accumulate = 1;
+                    }
+                    sm100::mma_commit_pair(empty_bar(stage), 3);
+                    if (++stage == kPairStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) {
+                    break;
+                }
+                sm100::mma_commit_pair(acc_full_bar(acc), 3);
+                acc ^= 1;
+                if (acc == 0) {
+                    acc_phase ^= 1u;
+                }
+            }
+        }
+    } else {
+        // ---- epilogue warps (both CTAs) ----
+        const int quadrant = warp % 4;
+        const int column_half = (warp - 2) / 4;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (long long id = pair; ok && id < p.tiles_total; id += pairs) {
+            const TileCoord t = decode_pair_tile(p, id);
+            if (!sm100::mbar_wait(acc_full_bar(acc), acc_phase, abort)) {
+                ok = false;
+                break;
+            }
+            sm100::tc_fence_after_sync();
+            const size_t row = static_cast<size_t>(t.tm) * 256 + rank * 128 + quadrant * 32 + lane;
+            const bool row_ok = row < static_cast<size_t>(p.m);
+            const int col0 = t.tn * kPairBN;
+            const size_t batch_offset =
+                p.batched ? static_cast<size_t>(t.z) * p.m * static_cast<size_t>(p.n) : 0;
+            const uint32_t t_addr = tmem_base + static_cast<uint32_t>(acc * kPairBN) +
+                                    (static_cast<uint32_t>(quadrant * 32) << 16);
+            const uint32_t leader_empty = sm100::map_to_cta(acc_empty_bar(acc), 0);
+#pragma unroll 1
+            for (int c = column_half * 32; c < kPairBN; c += 64) {
+                const bool last = c + 64 >= kPairBN;
+                const int col = col0 + c;
+                const int valid = min(32, p.n - col);
+                uint32_t raw[32];
+                if (valid > 0) {
+                    sm100::tmem_ld_32x32(t_addr + c, raw);
+                    sm100::tmem_ld_wait();
+                }
+                if (last) {
+                    sm100::tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) {
+                        sm100::mbar_arrive_cluster(leader_empty);
+                    }
+                }
+                if (valid > 0 && row_ok) {
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        v[j] = __uint_as_float(raw[j]);
+                    }
+                    store_segment<E>(p, batch_offset, t.z, row, col, v, valid);
+                }
+            }
+            acc ^= 1;
+            if (acc == 0) {
+                acc_phase ^= 1u;
+            }
+        }
+    }
+
+    // ---- teardown: neither CTA leaves while the other may still signal it ----
+    __syncthreads();
+    if (abort_flag != 0) {
+        if (threadIdx.x == 0) {
+            atomicExch(&g_gemm_error, 1);
+        }
+        const long long start = clock64();
+        while (clock64() - start < 2000000LL) {
+        }
+        __syncthreads();
+    }
+    sm100::tc_fence_before_sync();
+    sm100::cluster_sync_all();
+    if (warp == 1) {
+        sm100::tc_fence_after_sync();
+        sm100::tmem_dealloc_pair(tmem_base, kTmemCols);
+    }
+}
+
 // ---- plain CUDA-core kernel, for debugging the pipeline only -------------------------
 //
 // Selected with FLINT_B200_GEMM=simt in the environment; never the default.
@@ -688,6 +971,63 @@ cudaError_t launch_tc(GemmParams& p, const void* x, const void* w, int sms, cuda
     return fb::after_launch();
 }
 
+bool pair_disabled() {
+    static int cached = -1;
+    if (cached < 0) {
+        const char* v = std::getenv("FLINT_B200_GEMM");
+        cached = (v != nullptr && std::strcmp(v, "single") == 0) ? 1 : 0;
+    }
+    return cached == 1;
+}
+
+// The CTA-pair kernel pays off once both CTAs of a pair have rows to work on
+// and the tile is full width.
+bool use_pair(const GemmParams& p) {
+    return !pair_disabled() && p.m > 128 && p.n > 128;
+}
+
+template <Layout L, Epilogue E>
+cudaError_t launch_pair(GemmParams& p, const void* x, const void* w, int sms, cudaStream_t stream) {
+    constexpr bool kAMn = L == Layout::kTN;
+    constexpr bool kBMn = L != Layout::kNT;
+    const bool batched = p.batched != 0;
+    cudaError_t e;
+    if (kAMn) {
+        e = make_map(&p.map_a, x, p.m, p.k, p.batches, batched, kBK);
+    } else {
+        e = make_map(&p.map_a, x, p.k, p.m, p.batches, batched, kBM);
+    }
+    if (e != cudaSuccess) {
+        return e;
+    }
+    if (kBMn) {
+        e = make_map(&p.map_b, w, p.n, p.k, p.batches, batched, kBK);
+    } else {
+        e = make_map(&p.map_b, w, p.k, p.n, p.batches, batched, 128);
+    }
+    if (e != cudaSuccess) {
+        return e;
+    }
+    p.tiles_m = (p.m + 255) / 256;
+    p.tiles_n = (p.n + kPairBN - 1) / kPairBN;
+    const long long z = L == Layout::kTN && !batched ? p.splits : p.batches;
+    p.tiles_total = static_cast<long long>(p.tiles_m) * p.tiles_n * z;
+
+    static bool configured = false;
+    auto kernel = fb_gemm_pair<L, E>;
+    if (!configured) {
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kPairSmemBytes);
+        if (e != cudaSuccess) {
+            return e;
+        }
+        configured = true;
+    }
+    const long long pairs = std::min<long long>(p.tiles_total, sms / 2);
+    kernel<<<static_cast<unsigned>(2 * pairs), kThreads, kPairSmemBytes, stream>>>(p);
+    return fb::after_launch();
+}
+
 template <Layout L, Epilogue E>
 cudaError_t launch_any(GemmParams& p, const void* x, const void* w, cudaStream_t stream) {
     int sms = 0;
@@ -702,6 +1042,9 @@ cudaError_t launch_any(GemmParams& p, const void* x, const void* w, cudaStream_t
         fb_gemm_simt<L, E><<<grid, 256, 0, stream>>>(p, static_cast<const __half*>(x),
                                                      static_cast<const __half*>(w));
         return fb::after_launch();
+    }
+    if (use_pair(p)) {
+        return launch_pair<L, E>(p, x, w, sms, stream);
     }
     switch (pick_bn(static_cast<size_t>(p.n))) {
     case 256:
@@ -733,9 +1076,13 @@ GemmParams base_params(void* y, size_t m, size_t n, size_t k, size_t batches, bo
 // ---- internal launchers (declared in gemm.h) --------------------------------------------
 
 TnSplit tn_split(size_t m, size_t n, size_t k, int sms) {
-    const long long tiles = static_cast<long long>((m + kBM - 1) / kBM) *
-                            static_cast<long long>((n + pick_bn(n) - 1) / pick_bn(n));
-    const long long slots = sms;
+    // Tiles and the CTAs (or CTA pairs) that run at once, for the kernel this shape gets.
+    const bool pair = !pair_disabled() && m > 128 && n > 128;
+    const long long tiles =
+        pair ? static_cast<long long>((m + 255) / 256) * static_cast<long long>((n + 255) / 256)
+             : static_cast<long long>((m + kBM - 1) / kBM) *
+                   static_cast<long long>((n + pick_bn(n) - 1) / pick_bn(n));
+    const long long slots = pair ? std::max(1, sms / 2) : sms;
     const int most = static_cast<int>(std::min<size_t>(16, std::max<size_t>(1, k / 1024)));
     int want = 1;
     double best = 0.0;

@@ -333,10 +333,10 @@ flint_status check_softmax_dims(const char* name, size_t batches, size_t length)
 
 // ---- softmax + cross-entropy ------------------------------------------------------------
 
-constexpr int kCeThreads = 512;
+constexpr int kCeThreads = 1024;
+constexpr int kCeWarps = kCeThreads / 32;
 
-// Block-wide max / compensated sum through shared memory, in a fixed order.
-__device__ float block_max(float v, float* scratch) {
+__device__ __forceinline__ float ce_block_max(float v, float* scratch) {
     v = fb::warp_max(v);
     const int warp = threadIdx.x / 32;
     const int lane = threadIdx.x % 32;
@@ -345,14 +345,13 @@ __device__ float block_max(float v, float* scratch) {
         scratch[warp] = v;
     }
     __syncthreads();
-    float m = scratch[0];
-    for (int w = 1; w < kCeThreads / 32; ++w) {
-        m = fmaxf(m, scratch[w]);
-    }
-    return m;
+    float m = scratch[lane];  // kCeWarps == 32: one value per lane
+    return fb::warp_max(m);
 }
 
-__device__ float block_comp_total(Comp a, float* scratch) {
+// Every thread receives the same total: warp butterflies, then one butterfly
+// over the 32 warp totals, all in a fixed order.
+__device__ __forceinline__ float ce_block_total(Comp a, float* scratch) {
     a = fb::comp_warp_merge(a);
     const int warp = threadIdx.x / 32;
     const int lane = threadIdx.x % 32;
@@ -363,51 +362,118 @@ __device__ float block_comp_total(Comp a, float* scratch) {
     }
     __syncthreads();
     Comp total;
-    total.s = scratch[0];
-    total.e = scratch[1];
-    for (int w = 1; w < kCeThreads / 32; ++w) {
-        fb::comp_merge(total, scratch[2 * w], scratch[2 * w + 1]);
-    }
+    total.s = scratch[2 * lane];
+    total.e = scratch[2 * lane + 1];
+    total = fb::comp_warp_merge(total);
     return __fadd_rn(total.s, total.e);
 }
 
-// One CTA per row. The row's logits are read from HBM once into shared memory
-// (cols * 2 bytes, at most 128 KB); max, sum and the gradient pass then run
-// out of shared memory.
-__global__ void __launch_bounds__(kCeThreads)
+__device__ __forceinline__ float half_max8(const uint4& q) {
+    const __half2* h = reinterpret_cast<const __half2*>(&q);
+    const __half2 m = __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
+    return fmaxf(__low2float(m), __high2float(m));
+}
+
+// Persistent CTAs, one row at a time. Thread 0 streams each row's logits into
+// shared memory with one bulk asynchronous copy (two row buffers when they fit,
+// so the next row loads while this one is processed); the three passes (max on
+// the raw FP16 values, compensated sum of exp, gradient) then run out of shared
+// memory, and the row leaves as coalesced 16-byte stores.
+__global__ void __launch_bounds__(kCeThreads, 1)
     fb_softmax_cross_entropy(uint4* __restrict__ dlogits, float* __restrict__ row_loss,
                              const uint4* __restrict__ logits,
                              const uint16_t* __restrict__ targets, float scale, size_t rows,
-                             int vocab, int cols) {
+                             int vocab, int cols, int buffers) {
     extern __shared__ uint4 staged[];
-    __shared__ float scratch[2 * (kCeThreads / 32)];
+    __shared__ float scratch[2 * kCeWarps];
+    __shared__ alignas(8) unsigned long long barriers[2];
+    __shared__ int abort_flag;
     const int chunks = cols / 8;
     const int vocab_chunks = (vocab + 7) / 8;
+    const uint32_t copy_bytes = static_cast<uint32_t>(vocab_chunks) * 16u;
+    const uint32_t bar0 = static_cast<uint32_t>(__cvta_generic_to_shared(&barriers[0]));
+    const uint32_t stage0 = static_cast<uint32_t>(__cvta_generic_to_shared(staged));
+
+    auto issue = [&](size_t row, int buffer) {
+        const uint32_t bar = bar0 + 8u * buffer;
+        const uint32_t dst = stage0 + static_cast<uint32_t>(buffer) * copy_bytes;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
+                     "r"(copy_bytes)
+                     : "memory");
+        asm volatile(
+            "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+            ::"r"(dst), "l"(logits + row * chunks), "r"(copy_bytes), "r"(bar)
+            : "memory");
+    };
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar0) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar0 + 8u) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (blockIdx.x < rows) {
+            issue(blockIdx.x, 0);
+        }
+    }
+    __syncthreads();
+
+    int buffer = 0;
+    uint32_t phase[2] = {0u, 0u};
     for (size_t row = blockIdx.x; row < rows; row += gridDim.x) {
-        const uint4* in = logits + row * chunks;
+        const size_t next = row + gridDim.x;
+        if (buffers == 2 && threadIdx.x == 0 && next < rows) {
+            issue(next, buffer ^ 1);  // that buffer's readers finished at the last __syncthreads
+        }
+        // Wait for this row's bytes (bounded; on a timeout the row is skipped).
+        {
+            const uint32_t bar = bar0 + 8u * buffer;
+            bool landed = false;
+            const long long start = clock64();
+            for (uint32_t spin = 0; !landed; ++spin) {
+                uint32_t done = 0;
+                asm volatile(
+                    "{\n.reg .pred p;\n"
+                    "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+                    "selp.u32 %0, 1, 0, p;\n}\n"
+                    : "=r"(done)
+                    : "r"(bar), "r"(phase[buffer])
+                    : "memory");
+                landed = done != 0;
+                if (!landed && (spin & 255u) == 255u &&
+                    (abort_flag != 0 || clock64() - start > 2000000000LL)) {
+                    abort_flag = 1;
+                    break;
+                }
+            }
+            phase[buffer] ^= 1u;
+            if (!landed) {
+                break;
+            }
+        }
+        const uint4* in = staged + static_cast<size_t>(buffer) * vocab_chunks;
         uint4* out = dlogits + row * chunks;
-        __syncthreads();  // the previous row's readers are done with `staged`
+        const int last_count = vocab - (vocab_chunks - 1) * 8;  // values in the last chunk
 
         float mx = -INFINITY;
         for (int i = threadIdx.x; i < vocab_chunks; i += kCeThreads) {
             const uint4 q = in[i];
-            staged[i] = q;
-            float v[8];
-            fb::unpack8(v, q);
-            const int count = min(vocab - i * 8, 8);
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                if (c < count) {
+            if (i + 1 < vocab_chunks || last_count == 8) {
+                mx = fmaxf(mx, half_max8(q));
+            } else {
+                float v[8];
+                fb::unpack8(v, q);
+                for (int c = 0; c < last_count; ++c) {
                     mx = fmaxf(mx, v[c]);
                 }
             }
         }
-        mx = block_max(mx, scratch);
+        mx = ce_block_max(mx, scratch);
 
         Comp part;
         for (int i = threadIdx.x; i < vocab_chunks; i += kCeThreads) {
             float v[8];
-            fb::unpack8(v, staged[i]);
+            fb::unpack8(v, in[i]);
             const int count = min(vocab - i * 8, 8);
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
@@ -416,7 +482,7 @@ __global__ void __launch_bounds__(kCeThreads)
                 }
             }
         }
-        const float sum = block_comp_total(part, scratch);
+        const float sum = ce_block_total(part, scratch);
         const float inv = __fdiv_rn(1.0f, sum);
 
         const int target = targets[row];
@@ -428,24 +494,28 @@ __global__ void __launch_bounds__(kCeThreads)
                 continue;
             }
             float v[8];
-            fb::unpack8(v, staged[i]);
+            fb::unpack8(v, in[i]);
             const int count = min(vocab - i * 8, 8);
             float o[8];
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
-                if (c >= count) {
-                    o[c] = 0.0f;
-                    continue;
-                }
                 const float gap = __fsub_rn(v[c], mx);
-                float prob = __fmul_rn(expf(gap), inv);
-                if (i == target_chunk && c == target_slot) {
-                    row_loss[row] = __fsub_rn(logf(sum), gap);
-                    prob = __fsub_rn(prob, 1.0f);
-                }
-                o[c] = __fmul_rn(prob, scale);
+                o[c] = c < count ? __fmul_rn(__fmul_rn(expf(gap), inv), scale) : 0.0f;
+            }
+            if (i == target_chunk) {
+                const float gap = __fsub_rn(v[target_slot], mx);
+                row_loss[row] = __fsub_rn(logf(sum), gap);
+                o[target_slot] =
+                    __fmul_rn(__fsub_rn(__fmul_rn(expf(gap), inv), 1.0f), scale);
             }
             out[i] = fb::pack8(o);
+        }
+        __syncthreads();  // everyone is done with this buffer before it is refilled
+        if (buffers == 1 && threadIdx.x == 0 && next < rows) {
+            issue(next, 0);
+        }
+        if (buffers == 2) {
+            buffer ^= 1;
         }
     }
 }
@@ -604,27 +674,28 @@ flint_status flint_softmax_cross_entropy(void* dlogits, void* row_loss, const vo
     };
     FB_TRY(fb::check_spans(name, spans, 2));
 
-    // Only the vocab columns are staged.
-    const size_t staged_bytes = (vocab + 7) / 8 * 16;
+    // Only the vocab columns are staged; two row buffers when they fit.
+    const size_t row_bytes = (vocab + 7) / 8 * 16;
+    constexpr size_t kMaxSmem = 220 * 1024;
+    const int buffers = 2 * row_bytes <= kMaxSmem ? 2 : 1;
     static bool configured[64] = {};
     int device = 0;
     FB_CUDA(cudaGetDevice(&device));
     if (device < 0 || device >= 64 || !configured[device]) {
         FB_CUDA(cudaFuncSetAttribute(fb_softmax_cross_entropy,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     static_cast<int>(kMaxCols * 2)));
+                                     static_cast<int>(kMaxSmem)));
         if (device >= 0 && device < 64) {
             configured[device] = true;
         }
     }
     int sms = 148;
     FB_CUDA(fb::sm_count(&sms));
-    const unsigned blocks =
-        static_cast<unsigned>(std::min<size_t>(rows, static_cast<size_t>(sms) * 8));
-    fb_softmax_cross_entropy<<<blocks, kCeThreads, staged_bytes, stream>>>(
+    const unsigned blocks = static_cast<unsigned>(std::min<size_t>(rows, static_cast<size_t>(sms)));
+    fb_softmax_cross_entropy<<<blocks, kCeThreads, buffers * row_bytes, stream>>>(
         static_cast<uint4*>(dlogits), static_cast<float*>(row_loss),
         static_cast<const uint4*>(logits), static_cast<const uint16_t*>(targets), scale, rows,
-        static_cast<int>(vocab), static_cast<int>(cols));
+        static_cast<int>(vocab), static_cast<int>(cols), buffers);
     FB_CUDA(fb::after_launch());
     return FLINT_OK;
 }
