@@ -235,6 +235,199 @@ __device__ __forceinline__ void store_segment(const GemmParams& p, size_t batch_
     }
 }
 
+// ---- coalesced epilogue ------------------------------------------------------------------
+//
+// After tcgen05.ld each lane holds 32 consecutive columns of its own row, so a
+// direct store touches 32 rows per instruction. Instead the warp stages its
+// 32 x 32 chunk in a private 4 KB shared-memory buffer (16-byte slots, swizzled
+// in groups of 8 so both directions are conflict-free) and reads it back so
+// that consecutive lanes hold consecutive 16-byte pieces of a row: every global
+// access then covers whole 64- or 128-byte row segments. Second operands (the
+// saved pre-activation, the residual, the old value when accumulating) are
+// fetched in the same coalesced layout.
+
+__device__ __forceinline__ uint32_t stage_slot(uint32_t base, int logical) {
+    return base + static_cast<uint32_t>(((logical & ~7) | ((logical & 7) ^ ((logical >> 3) & 7)))
+                                        << 4);
+}
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y),
+                 "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "r"(addr)
+                 : "memory");
+    return v;
+}
+
+__device__ __forceinline__ uint4 pack_half8(const float* v) {
+    uint4 q;
+    unsigned* w = reinterpret_cast<unsigned*>(&q);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+        w[j] = *reinterpret_cast<const unsigned*>(&h);
+    }
+    return q;
+}
+
+// Moves the warp's staged FP16 chunk (4 slots per row) to `out` (row-major, ld = n).
+__device__ __forceinline__ void flush_half_chunk(uint32_t stage, __half* out_chunk, size_t n,
+                                                 int rows_left, int valid, int lane) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int logical = lane + 32 * i;
+        const int r = logical >> 2;
+        const int c = logical & 3;
+        if (r < rows_left && c * 8 < valid) {
+            *reinterpret_cast<uint4*>(out_chunk + static_cast<size_t>(r) * n + c * 8) =
+                ld_shared_v4(stage_slot(stage, logical));
+        }
+    }
+}
+
+// The whole warp calls this for one 32 x 32 chunk whose top-left element is
+// (row0, col). acc holds this lane's row. Requires n % 8 == 0 (FP16 outputs) or
+// n % 4 == 0 (FP32 outputs).
+template <Epilogue E>
+__device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t stage,
+                                            size_t batch_offset, long long split, size_t row0,
+                                            int col, float (&acc)[32], int valid, int lane) {
+    const size_t n = static_cast<size_t>(p.n);
+    const size_t at0 = batch_offset + row0 * n + col;  // the chunk's first element
+    const long long rows_long = static_cast<long long>(p.m) - static_cast<long long>(row0);
+    const int rows_left = rows_long > 32 ? 32 : static_cast<int>(rows_long);
+
+    if constexpr (E == Epilogue::kBias || E == Epilogue::kBiasGelu ||
+                  E == Epilogue::kBiasResidual) {
+        const float* bias = p.bias + col;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            if (j < valid) {
+                acc[j] = __fadd_rn(acc[j], bias[j]);
+            }
+        }
+    }
+    if constexpr (E == Epilogue::kScale) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            acc[j] = __fmul_rn(acc[j], p.scale);
+        }
+    }
+
+    if constexpr (E == Epilogue::kBiasResidual || E == Epilogue::kTnStore ||
+                  E == Epilogue::kTnPartial) {
+        // FP32 output: 8 slots per row.
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            st_shared_v4(stage_slot(stage, lane * 8 + c),
+                         make_uint4(__float_as_uint(acc[4 * c]), __float_as_uint(acc[4 * c + 1]),
+                                    __float_as_uint(acc[4 * c + 2]),
+                                    __float_as_uint(acc[4 * c + 3])));
+        }
+        __syncwarp();
+        float* out;
+        if constexpr (E == Epilogue::kTnPartial) {
+            out = p.partials + static_cast<size_t>(split) * p.m * n + row0 * n + col;
+        } else {
+            out = static_cast<float*>(p.y) + at0;
+        }
+        const float* old = E == Epilogue::kBiasResidual
+                               ? static_cast<const float*>(p.aux_in) + at0
+                               : out;
+        const bool add = E == Epilogue::kBiasResidual || (E == Epilogue::kTnStore && p.accumulate);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int logical = lane + 32 * i;
+            const int r = logical >> 3;
+            const int c = logical & 7;
+            if (r < rows_left && c * 4 < valid) {
+                const uint4 q = ld_shared_v4(stage_slot(stage, logical));
+                float4 v = make_float4(__uint_as_float(q.x), __uint_as_float(q.y),
+                                       __uint_as_float(q.z), __uint_as_float(q.w));
+                const size_t off = static_cast<size_t>(r) * n + c * 4;
+                if (add) {
+                    const float4 o = *reinterpret_cast<const float4*>(old + off);
+                    v = make_float4(__fadd_rn(o.x, v.x), __fadd_rn(o.y, v.y), __fadd_rn(o.z, v.z),
+                                    __fadd_rn(o.w, v.w));
+                }
+                *reinterpret_cast<float4*>(out + off) = v;
+            }
+        }
+        __syncwarp();
+        return;
+    } else {
+        __half* out = static_cast<__half*>(p.y) + at0;
+        if constexpr (E == Epilogue::kDGelu) {
+            // Fetch the pre-activations coalesced, then hand each lane its row.
+            const __half* pre = static_cast<const __half*>(p.aux_in) + at0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int logical = lane + 32 * i;
+                const int r = logical >> 2;
+                const int c = logical & 3;
+                uint4 q = make_uint4(0u, 0u, 0u, 0u);
+                if (r < rows_left && c * 8 < valid) {
+                    q = *reinterpret_cast<const uint4*>(pre + static_cast<size_t>(r) * n + c * 8);
+                }
+                st_shared_v4(stage_slot(stage, logical), q);
+            }
+            __syncwarp();
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint4 q = ld_shared_v4(stage_slot(stage, lane * 4 + c));
+                const unsigned w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float lo = half_bits_to_float(static_cast<unsigned short>(w[j]));
+                    const float hi = half_bits_to_float(static_cast<unsigned short>(w[j] >> 16));
+                    acc[c * 8 + 2 * j] = __fmul_rn(acc[c * 8 + 2 * j], gelu_tanh_grad(lo));
+                    acc[c * 8 + 2 * j + 1] = __fmul_rn(acc[c * 8 + 2 * j + 1], gelu_tanh_grad(hi));
+                }
+            }
+            __syncwarp();
+        }
+        if constexpr (E == Epilogue::kBiasGelu) {
+            // The pre-activation first, then GELU of the unrounded sums.
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                st_shared_v4(stage_slot(stage, lane * 4 + c), pack_half8(acc + 8 * c));
+            }
+            __syncwarp();
+            flush_half_chunk(stage, static_cast<__half*>(p.aux_out) + at0, n, rows_left, valid,
+                             lane);
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                acc[j] = gelu_tanh(acc[j]);
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            st_shared_v4(stage_slot(stage, lane * 4 + c), pack_half8(acc + 8 * c));
+        }
+        __syncwarp();
+        flush_half_chunk(stage, out, n, rows_left, valid, lane);
+        __syncwarp();
+    }
+}
+
+template <Epilogue E>
+__device__ __forceinline__ bool chunk_path_ok(const GemmParams& p) {
+    if constexpr (E == Epilogue::kBiasResidual || E == Epilogue::kTnStore ||
+                  E == Epilogue::kTnPartial) {
+        return p.n % 4 == 0;
+    } else {
+        return p.n % 8 == 0;
+    }
+}
+
 // ---- the tensor-core kernel --------------------------------------------------------------
 
 template <int BN>
@@ -243,8 +436,8 @@ struct Ring {
     static constexpr int kStageB = BN * kBK * 2;
     static constexpr int kStage = kStageA + kStageB;
     static constexpr int kStages = kRingBytes / kStage;
-    // ring + barriers + the 1,024-byte alignment slack
-    static constexpr int kSmemBytes = kStages * kStage + 1024 + 256;
+    // ring + epilogue staging (4 KB per epilogue warp) + barriers + alignment slack
+    static constexpr int kSmemBytes = kStages * kStage + kEpilogueWarps * 4096 + 1024 + 256;
 };
 
 struct TileCoord {
@@ -279,7 +472,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     extern __shared__ unsigned char smem_raw[];
     const uint32_t smem_base = (sm100::smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t bars = smem_base + R::kStages * R::kStage;
+    const uint32_t staging = smem_base + R::kStages * R::kStage;
+    const uint32_t bars = staging + kEpilogueWarps * 4096;
     // barrier slots (8 bytes each): full[kStages], empty[kStages], acc_full[2], acc_empty[2]
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (R::kStages + s); };
@@ -441,6 +635,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         // ---- epilogue warps ----
         const int quadrant = warp % 4;      // the TMEM lanes this warp may read
         const int column_half = (warp - 2) / 4;  // which of the alternating 32-column chunks
+        const bool coalesced = chunk_path_ok<E>(p);
+        const uint32_t stage = staging + static_cast<uint32_t>(warp - 2) * 4096u;
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
@@ -476,13 +672,18 @@ __global__ void __launch_bounds__(kThreads, 1)
                         sm100::mbar_arrive(acc_empty_bar(acc));
                     }
                 }
-                if (valid > 0 && row_ok) {
+                if (valid > 0) {
                     float v[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         v[j] = __uint_as_float(raw[j]);
                     }
-                    store_segment<E>(p, batch_offset, t.z, row, col, v, valid);
+                    if (coalesced) {
+                        store_chunk<E>(p, stage, batch_offset, t.z, row - lane, col, v, valid,
+                                       lane);
+                    } else if (row_ok) {
+                        store_segment<E>(p, batch_offset, t.z, row, col, v, valid);
+                    }
                 }
             }
             acc ^= 1;
@@ -526,7 +727,7 @@ constexpr int kPairStageA = kBM * kBK * 2;          // 16 KB
 constexpr int kPairStageB = 128 * kBK * 2;          // 16 KB: half of the 256 B rows
 constexpr int kPairStage = kPairStageA + kPairStageB;
 constexpr int kPairStages = kRingBytes / kPairStage;  // 6
-constexpr int kPairSmemBytes = kPairStages * kPairStage + 1024 + 256;
+constexpr int kPairSmemBytes = kPairStages * kPairStage + kEpilogueWarps * 4096 + 1024 + 256;
 constexpr int kPairGroupM = 4;  // rows of 256-row tiles handed out together
 
 __device__ __forceinline__ TileCoord decode_pair_tile(const GemmParams& p, long long id) {
@@ -555,7 +756,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 
     extern __shared__ unsigned char smem_raw[];
     const uint32_t smem_base = (sm100::smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t bars = smem_base + kPairStages * kPairStage;
+    const uint32_t staging = smem_base + kPairStages * kPairStage;
+    const uint32_t bars = staging + kEpilogueWarps * 4096;
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (kPairStages + s); };
     auto acc_full_bar = [&](int a) { return bars + 8u * (2 * kPairStages + a); };
@@ -723,6 +925,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         // ---- epilogue warps (both CTAs) ----
         const int quadrant = warp % 4;
         const int column_half = (warp - 2) / 4;
+        const bool coalesced = chunk_path_ok<E>(p);
+        const uint32_t stage = staging + static_cast<uint32_t>(warp - 2) * 4096u;
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
@@ -758,13 +962,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                         sm100::mbar_arrive_cluster(leader_empty);
                     }
                 }
-                if (valid > 0 && row_ok) {
+                if (valid > 0) {
                     float v[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         v[j] = __uint_as_float(raw[j]);
                     }
-                    store_segment<E>(p, batch_offset, t.z, row, col, v, valid);
+                    if (coalesced) {
+                        store_chunk<E>(p, stage, batch_offset, t.z, row - lane, col, v, valid,
+                                       lane);
+                    } else if (row_ok) {
+                        store_segment<E>(p, batch_offset, t.z, row, col, v, valid);
+                    }
                 }
             }
             acc ^= 1;
