@@ -304,6 +304,11 @@ class Flint:
         self.call("flint_bias_gradient", dbias, dy, rows, cols, bool(accumulate), workspace,
                   workspace_bytes, stream=stream)
 
+    def bias_gradient_static(self, dbias, dy, rows, cols, accumulate=False, stream=None) -> None:
+        """bias_gradient without a caller workspace (built-in 4 MiB scratch, no allocation)."""
+        self.call("flint_b200_bias_gradient_static", dbias, dy, rows, cols, bool(accumulate),
+                  stream=stream)
+
     def layernorm_forward(self, y, mean, rstd, x, gamma, beta, rows, cols, eps=1e-5,
                           stream=None) -> None:
         self.call("flint_layernorm_forward", y, mean, rstd, x, gamma, beta, rows, cols, eps,

@@ -22,6 +22,7 @@
 
 #include "common.h"
 #include "device_utils.cuh"
+#include "flint/flint_b200.h"
 
 namespace {
 
@@ -723,6 +724,47 @@ cudaError_t launch_embedding_backward(void* dwte, void* dwpe, const void* dx, co
 
 }  // namespace fb
 
+namespace {
+// ---- a bias gradient that needs no workspace from the caller -------------------------------
+//
+// Some hosts cannot hand this library a workspace: a plug-in living inside an
+// application that owns every byte of device memory and gives none away after
+// start-up, or a serving loop whose latency budget rules out cudaMalloc (it
+// synchronises the whole device). For them the partial sums of the first pass go
+// into this fixed array, which is part of the library's image: every GPU that
+// loads the library carries these 4 MiB until the process exits.
+constexpr size_t kStaticScratchBytes = size_t{4} << 20;
+static __device__ __align__(256) unsigned char g_bias_gradient_scratch[kStaticScratchBytes];
+
+// In host code the array's name is only a handle for the runtime, not an address
+// a kernel can use; the device address comes from cudaGetSymbolAddress, asked
+// once per device while that device is current.
+cudaError_t static_scratch(void** pointer) {
+    constexpr int kMaxDevices = 64;
+    static void* cached[kMaxDevices] = {};
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) {
+        return e;
+    }
+    if (device >= 0 && device < kMaxDevices && cached[device] != nullptr) {
+        *pointer = cached[device];
+        return cudaSuccess;
+    }
+    void* address = nullptr;
+    e = cudaGetSymbolAddress(&address, g_bias_gradient_scratch);
+    if (e != cudaSuccess) {
+        return e;
+    }
+    if (device >= 0 && device < kMaxDevices) {
+        cached[device] = address;
+    }
+    *pointer = address;
+    return cudaSuccess;
+}
+
+}  // namespace
+
 extern "C" {
 
 flint_status flint_bias_gradient_workspace(size_t rows, size_t cols, size_t* bytes) {
@@ -756,6 +798,33 @@ flint_status flint_bias_gradient(void* dbias, const void* dy, size_t rows, size_
     };
     FB_TRY(fb::check_spans(name, spans, 2));
     FB_CUDA(fb::launch_bias_gradient(dbias, dy, rows, cols, accumulate != 0, workspace, stream));
+    return FLINT_OK;
+}
+
+flint_status flint_b200_bias_gradient_static(void* dbias, const void* dy, size_t rows, size_t cols,
+                                             int accumulate, flint_stream stream) {
+    constexpr const char* name = "flint_b200_bias_gradient_static";
+    FB_TRY(check_column_dims(name, rows, cols, true, kMaxBiasRows));
+    if (cols == 0) {
+        return FLINT_OK;
+    }
+    const size_t needed = column_sum_workspace(rows, cols);
+    if (needed > kStaticScratchBytes) {
+        return fb::fail(FLINT_ERROR_INVALID_ARGUMENT,
+                        "%s: rows (%zu) x cols (%zu) needs %zu bytes of scratch, and the built-in "
+                        "scratch holds %zu; use flint_bias_gradient with a workspace",
+                        name, rows, cols, needed, kStaticScratchBytes);
+    }
+    void* scratch = nullptr;
+    FB_CUDA(static_scratch(&scratch));
+    const fb::Span spans[] = {
+        {"dbias", dbias, cols * 4},
+        {"dy", dy, rows * cols * 2},
+    };
+    FB_TRY(fb::check_spans(name, spans, 1));
+    // The first pass overwrites every partial sum the second pass reads, so what an
+    // earlier call left in the array never matters and nothing needs clearing.
+    FB_CUDA(fb::launch_bias_gradient(dbias, dy, rows, cols, accumulate != 0, scratch, stream));
     return FLINT_OK;
 }
 

@@ -116,6 +116,28 @@ FLINT_API flint_status flint_b200_adamw_run(const void* plan, size_t items, floa
                                             float beta2, float eps, float grad_scale, int step,
                                             const int* skip, flint_stream stream);
 
+/* flint_bias_gradient for callers that cannot supply a workspace. It has no
+ * counterpart in the reference. The result is flint_bias_gradient's bit for bit;
+ * the partial sums live in a 4 MiB array built into the library instead of a
+ * caller buffer, and the call allocates nothing (no cudaMalloc, no cudaFree).
+ * It exists for hosts that may not allocate device memory once they are running:
+ * a plug-in inside an application that owns the whole memory budget, or a loop
+ * that cannot afford the device-wide synchronisation cudaMalloc implies.
+ *
+ * Limit: ceil(rows / 256) * cols * 8 bytes must fit in 4 MiB (for example 16,384
+ * rows x 3,072 cols needs 1.5 MiB); larger shapes fail with
+ * FLINT_ERROR_INVALID_ARGUMENT and should use flint_bias_gradient. Every GPU
+ * that loads the library holds the 4 MiB until the process exits.
+ *
+ * The first call on each device looks up the array's device address; make that
+ * call before starting any stream capture. All calls share the one array, so two
+ * calls that can overlap on the GPU (different streams, no ordering between
+ * them) race on it; calls ordered on one stream are fine, and nothing has to be
+ * cleared between them. */
+FLINT_API flint_status flint_b200_bias_gradient_static(void* dbias, const void* dy, size_t rows,
+                                                       size_t cols, int accumulate,
+                                                       flint_stream stream);
+
 /* Sets *found_nonfinite (device int) to 1 if any of the count FP32 values is
  * inf or NaN; leaves it unchanged otherwise, so several calls can share it.
  * When sum_squares (device double, may be null) is given, adds the sum of
