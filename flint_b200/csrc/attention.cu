@@ -49,8 +49,19 @@ constexpr flint_status kInvalid = FLINT_ERROR_INVALID_ARGUMENT;
 
 __device__ int g_attention_error = 0;
 
+#ifdef FB_ATTN_TRACE
+__device__ long long g_trace[8][2][40][4];
+#define FB_TRACE(who, h, k)                                   \
+    if (blockIdx.x < 8 && (h) < 40) {                         \
+        g_trace[blockIdx.x][who][h][k] = clock64();           \
+    }
+#else
+#define FB_TRACE(who, h, k)
+#endif
+
 struct AttnParams {
-    CUtensorMap map_q, map_k, map_v, map_do;
+    CUtensorMap map_q, map_k, map_v, map_do;          // 128-row boxes
+    CUtensorMap map_q64, map_k64, map_v64, map_do64;  // 64-row boxes (backward sub-steps)
     // Outputs and row statistics are addressed directly.
     void* out0;            // forward: O; dkv: dK; dq: dQ
     void* out1;            // dkv: dV
@@ -68,6 +79,15 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
         " [%0], [%1, {%3, %4, %5, %6}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2),
           "r"(c3)
+        : "memory");
+}
+
+// Untiled bulk copy global -> shared (both 16-byte aligned, bytes a multiple of 16).
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes,
+                                          uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
         : "memory");
 }
 
@@ -413,10 +433,69 @@ __global__ void __launch_bounds__(256)
 }
 
 // ---- backward: dK and dV ------------------------------------------------------------------------
+//
+// One CTA per (head, 128 keys). Scores are formed transposed, S^T = K Q^T with
+// keys on the TMEM lanes, 64 queries at a time, so that P^T and dS^T leave the
+// compute warps directly in the K-major layout the gradient MMAs want as their
+// A operand (dV += P^T dO, dK += dS^T Q). The two S^T/dP^T accumulators and the
+// two P^T/dS^T shared-memory buffers are double-buffered: the MMA warp issues
+// sub-step h+1's score MMAs before it waits for sub-step h's probabilities, so
+// tensor work and exponentials overlap.
 
-constexpr int kBwdThreads = 576;  // TMA warp, MMA warp, 16 compute warps (32 columns each)
-// K, V, 2 x (Q, dO), P, dS
-constexpr int kDkvSmem = 1024 + kTileBytes * 6 + 4 * kPanelBytes + 128;
+constexpr int kBwdThreads = 320;  // TMA warp, MMA warp, 8 compute warps
+constexpr int kSub = 64;          // queries (dK/dV) or keys (dQ) per sub-step
+constexpr int kSubBytes = kSub * kHead * 2;     // 8 KB: a 64-row Q/dO/K/V tile
+constexpr int kBwdStages = 4;
+// resident pair (2 x 16 KB) + ring (4 x 16 KB) + two P^T and two dS^T buffers (4 x 16 KB)
+// + per stage the sub-step's 64 log-sum-exp and 64 delta values
+constexpr int kStatBytes = kSub * 4;  // one sub-step's log-sum-exp or delta values
+constexpr int kDkvSmem = 1024 + 2 * kTileBytes + kBwdStages * 2 * kSubBytes + 4 * kPanelBytes +
+                         kBwdStages * 2 * kStatBytes + 256;
+constexpr uint32_t kIdescSub = sm100::instr_desc_f16(128, 64, false, false);  // K Q^T, V dO^T
+
+struct BwdBarriers {
+    uint32_t base;
+    __device__ uint32_t resident() const { return base; }
+    __device__ uint32_t done() const { return base + 8; }
+    __device__ uint32_t scores_full(int b) const { return base + 16 + 8u * b; }
+    __device__ uint32_t operands_ready(int b) const { return base + 32 + 8u * b; }
+    __device__ uint32_t operands_free(int b) const { return base + 48 + 8u * b; }
+    __device__ uint32_t stage_full(int s) const { return base + 64 + 8u * s; }
+    __device__ uint32_t stage_empty(int s) const { return base + 96 + 8u * s; }
+};
+
+__device__ __forceinline__ void init_bwd_barriers(const BwdBarriers& b, int compute_threads) {
+    sm100::mbar_init(b.resident(), 1);
+    sm100::mbar_init(b.done(), 1);
+    for (int i = 0; i < 2; ++i) {
+        sm100::mbar_init(b.scores_full(i), 1);
+        sm100::mbar_init(b.operands_ready(i), compute_threads);
+        sm100::mbar_init(b.operands_free(i), 1);
+    }
+    for (int s = 0; s < kBwdStages; ++s) {
+        sm100::mbar_init(b.stage_full(s), 1);
+        sm100::mbar_init(b.stage_empty(s), 1);
+    }
+    sm100::mbar_fence_init();
+}
+
+// Writes 32 FP16 values into columns [col, col + 32) of row `row` of a one-panel
+// (64-column) swizzled operand tile.
+__device__ __forceinline__ void store_panel_row(uint32_t tile, int row, int col,
+                                                const float (&v)[32]) {
+    const uint32_t line = tile + row * 128;
+    const int first_chunk = col >> 3;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const uint32_t at = line + (((first_chunk + c) ^ (row & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(at),
+                     "r"(fb::pack2(v[8 * c], v[8 * c + 1])),
+                     "r"(fb::pack2(v[8 * c + 2], v[8 * c + 3])),
+                     "r"(fb::pack2(v[8 * c + 4], v[8 * c + 5])),
+                     "r"(fb::pack2(v[8 * c + 6], v[8 * c + 7]))
+                     : "memory");
+    }
+}
 
 __global__ void __launch_bounds__(kBwdThreads, 1)
     fb_attention_dkv(const __grid_constant__ AttnParams p) {
@@ -424,14 +503,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     const uint32_t base = (sm100::smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t k_tile = base;
     const uint32_t v_tile = base + kTileBytes;
-    const uint32_t ring = base + 2 * kTileBytes;            // stage s: Q at +0, dO at +16 KB
-    const uint32_t p_tile = ring + 4 * kTileBytes;
-    const uint32_t ds_tile = p_tile + 2 * kPanelBytes;
-    const uint32_t bars = ds_tile + 2 * kPanelBytes;
-    const uint32_t kv_full = bars, sdp_full = bars + 8, pds_ready = bars + 16,
-                   grads_done = bars + 24;
-    auto stage_full = [&](int s) { return bars + 32 + 8u * s; };
-    auto stage_empty = [&](int s) { return bars + 48 + 8u * s; };
+    const uint32_t ring = base + 2 * kTileBytes;                 // stage: Q_h then dO_h
+    const uint32_t pt_tiles = ring + kBwdStages * 2 * kSubBytes;  // P^T[0], P^T[1]
+    const uint32_t dst_tiles = pt_tiles + 2 * kPanelBytes;        // dS^T[0], dS^T[1]
+    const uint32_t stats = dst_tiles + 2 * kPanelBytes;           // stage: lse[64] then delta[64]
+    const BwdBarriers bar{stats + kBwdStages * 2 * kStatBytes};
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -442,19 +518,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     const int bh = static_cast<int>(blockIdx.x % bh_count);
     const int head = bh % p.heads;
     const int seq = bh / p.heads;
-    const int iterations = p.blocks - kb;
+    const int steps = 2 * (p.blocks - kb);  // 64-query sub-steps from the diagonal tile on
 
+    if (threadIdx.x == 64) {
+        FB_TRACE(0, 38, 0);
+    }
     if (threadIdx.x == 0) {
         abort_flag = 0;
-        sm100::mbar_init(kv_full, 1);
-        sm100::mbar_init(sdp_full, 1);
-        sm100::mbar_init(pds_ready, 512);
-        sm100::mbar_init(grads_done, 1);
-        for (int s = 0; s < 2; ++s) {
-            sm100::mbar_init(stage_full(s), 1);
-            sm100::mbar_init(stage_empty(s), 1);
-        }
-        sm100::mbar_fence_init();
+        init_bwd_barriers(bar, 256);
     }
     if (warp == 1) {
         sm100::tmem_alloc(sm100::smem_u32(&tmem_slot), 512);
@@ -463,27 +534,41 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     __syncthreads();
     sm100::tc_fence_after_sync();
     const uint32_t tmem = tmem_slot;
-    const uint32_t tmem_s = tmem, tmem_dp = tmem + 128, tmem_dv = tmem + 256, tmem_dk = tmem + 320;
+    auto tmem_st = [&](int b) { return tmem + 64u * b; };
+    auto tmem_dpt = [&](int b) { return tmem + 128u + 64u * b; };
+    const uint32_t tmem_dv = tmem + 256, tmem_dk = tmem + 320;
     volatile int* abort = &abort_flag;
+    if (threadIdx.x == 64) {
+        FB_TRACE(0, 38, 1);
+    }
 
     if (warp == 0) {
         if (lane == 0) {
-            sm100::mbar_expect_tx(kv_full, 2 * kTileBytes);
-            tma_load_4d(k_tile, &p.map_k, kv_full, 0, kb * kTile, head, seq);
-            tma_load_4d(v_tile, &p.map_v, kv_full, 0, kb * kTile, head, seq);
+            sm100::mbar_expect_tx(bar.resident(), 2 * kTileBytes);
+            tma_load_4d(k_tile, &p.map_k, bar.resident(), 0, kb * kTile, head, seq);
+            tma_load_4d(v_tile, &p.map_v, bar.resident(), 0, kb * kTile, head, seq);
             int stage = 0;
             uint32_t phase = 0;
-            for (int it = 0; it < iterations; ++it) {
-                if (!sm100::mbar_wait(stage_empty(stage), phase ^ 1u, abort)) {
+            for (int h = 0; h < steps; ++h) {
+                if (!sm100::mbar_wait(bar.stage_empty(stage), phase ^ 1u, abort)) {
                     break;
                 }
-                const int qb = kb + it;
-                const uint32_t dst = ring + stage * 2 * kTileBytes;
-                sm100::mbar_expect_tx(stage_full(stage), 2 * kTileBytes);
-                tma_load_4d(dst, &p.map_q, stage_full(stage), 0, qb * kTile, head, seq);
-                tma_load_4d(dst + kTileBytes, &p.map_do, stage_full(stage), 0, qb * kTile, head,
-                            seq);
-                if (++stage == 2) {
+                const int q0 = kb * kTile + h * kSub;
+                const uint32_t dst = ring + stage * 2 * kSubBytes;
+                // Row statistics of the queries that exist (length is a multiple of 8, so
+                // the byte count is a multiple of 32); the rest of the slot is never used.
+                const int present = min(kSub, p.length - q0);
+                const uint32_t stat_bytes = present > 0 ? static_cast<uint32_t>(present) * 4u : 0u;
+                sm100::mbar_expect_tx(bar.stage_full(stage), 2 * kSubBytes + 2 * stat_bytes);
+                tma_load_4d(dst, &p.map_q64, bar.stage_full(stage), 0, q0, head, seq);
+                tma_load_4d(dst + kSubBytes, &p.map_do64, bar.stage_full(stage), 0, q0, head, seq);
+                if (stat_bytes != 0) {
+                    const size_t at = static_cast<size_t>(bh) * p.length + q0;
+                    const uint32_t slot = stats + stage * 2 * kStatBytes;
+                    bulk_load(slot, p.lse + at, stat_bytes, bar.stage_full(stage));
+                    bulk_load(slot + kStatBytes, p.delta + at, stat_bytes, bar.stage_full(stage));
+                }
+                if (++stage == kBwdStages) {
                     stage = 0;
                     phase ^= 1u;
                 }
@@ -491,111 +576,161 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            bool ok = sm100::mbar_wait(kv_full, 0, abort);
-            int stage = 0;
-            uint32_t phase = 0;
-            for (int it = 0; ok && it < iterations; ++it) {
-                if (!sm100::mbar_wait(stage_full(stage), phase, abort)) {
-                    break;
+            bool ok = sm100::mbar_wait(bar.resident(), 0, abort);
+            // S^T and dP^T of sub-step g into accumulator pair g & 1.
+            auto issue_scores = [&](int g) -> bool {
+                const int stage = g % kBwdStages;
+                if (!sm100::mbar_wait(bar.stage_full(stage), (g / kBwdStages) & 1, abort)) {
+                    return false;
                 }
                 sm100::tc_fence_after_sync();
-                const uint32_t q_tile = ring + stage * 2 * kTileBytes;
-                const uint32_t do_tile = q_tile + kTileBytes;
-                // S = Q K^T and dP = dO V^T; the compute warps have drained the
-                // previous pair (they signalled pds_ready before the last gradient MMAs).
+                const uint32_t q_sub = ring + stage * 2 * kSubBytes;
+                const uint32_t do_sub = q_sub + kSubBytes;
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {
-                    sm100::mma_f16_ss(tmem_s, desc_kmajor(q_tile, ks), desc_kmajor(k_tile, ks),
-                                      kIdescS, ks > 0);
+                    sm100::mma_f16_ss(tmem_st(g & 1), desc_kmajor(k_tile, ks),
+                                      desc_kmajor(q_sub, ks), kIdescSub, ks > 0);
                 }
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {
-                    sm100::mma_f16_ss(tmem_dp, desc_kmajor(do_tile, ks), desc_kmajor(v_tile, ks),
-                                      kIdescS, ks > 0);
+                    sm100::mma_f16_ss(tmem_dpt(g & 1), desc_kmajor(v_tile, ks),
+                                      desc_kmajor(do_sub, ks), kIdescSub, ks > 0);
                 }
-                sm100::mma_commit(sdp_full);
-                if (!sm100::mbar_wait(pds_ready, it & 1, abort)) {
+                sm100::mma_commit(bar.scores_full(g & 1));
+                return true;
+            };
+            FB_TRACE(1, 39, 0);
+            ok = ok && issue_scores(0);
+            FB_TRACE(1, 39, 1);
+            for (int h = 0; ok && h < steps; ++h) {
+                const int b = h & 1;
+                FB_TRACE(1, h, 0);
+                if (h + 1 < steps && !issue_scores(h + 1)) {
                     break;
                 }
+                FB_TRACE(1, h, 1);
+                if (!sm100::mbar_wait(bar.operands_ready(b), (h >> 1) & 1, abort)) {
+                    break;
+                }
+                FB_TRACE(1, h, 2);
                 sm100::tc_fence_after_sync();
-                // dV += P^T dO, dK += dS^T Q (K = the 128 queries of this tile).
+                const int stage = h % kBwdStages;
+                const uint32_t q_sub = ring + stage * 2 * kSubBytes;
+                const uint32_t do_sub = q_sub + kSubBytes;
+                const uint32_t pt = pt_tiles + b * kPanelBytes;
+                const uint32_t dst = dst_tiles + b * kPanelBytes;
+                // dV += P^T dO and dK += dS^T Q over this sub-step's 64 queries.
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    sm100::mma_f16_ss(tmem_dv, desc_mnmajor(p_tile, ks, kPanelBytes),
-                                      desc_mnmajor(do_tile, ks, 16), kIdescT, (it | ks) != 0);
+                for (int ks = 0; ks < 4; ++ks) {
+                    sm100::mma_f16_ss(tmem_dv, desc_kmajor(pt, ks), desc_mnmajor(do_sub, ks, 16),
+                                      kIdescPV, (h | ks) != 0);
                 }
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    sm100::mma_f16_ss(tmem_dk, desc_mnmajor(ds_tile, ks, kPanelBytes),
-                                      desc_mnmajor(q_tile, ks, 16), kIdescT, (it | ks) != 0);
+                for (int ks = 0; ks < 4; ++ks) {
+                    sm100::mma_f16_ss(tmem_dk, desc_kmajor(dst, ks), desc_mnmajor(q_sub, ks, 16),
+                                      kIdescPV, (h | ks) != 0);
                 }
-                sm100::mma_commit(stage_empty(stage));
-                if (it + 1 == iterations) {
-                    sm100::mma_commit(grads_done);
+                sm100::mma_commit(bar.stage_empty(stage));
+                sm100::mma_commit(bar.operands_free(b));
+                if (h + 1 == steps) {
+                    sm100::mma_commit(bar.done());
                 }
-                if (++stage == 2) {
-                    stage = 0;
-                    phase ^= 1u;
-                }
+                FB_TRACE(1, h, 3);
             }
         }
     } else {
         const int quadrant = warp % 4;
-        const int part = (warp - 2) / 4;                 // which 32 key columns
-        const int col = part * 32;
-        const int row = quadrant * 32 + lane;            // query row inside the tile
+        const int part = (warp - 2) / 4;                 // which 32 of the 64 query columns
+        const int row = quadrant * 32 + lane;            // key row inside the tile
+        const int k_index = kb * kTile + row;
         const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
         const float scale2 = p.scale * kLog2e;
         bool ok = true;
-        for (int it = 0; ok && it < iterations; ++it) {
-            const int qb = kb + it;
-            const int q_index = qb * kTile + row;
-            const bool row_valid = q_index < p.length;
-            // An invalid row gets lse = +inf, so its probabilities are exp2(-inf) = 0.
-            float lse2 = INFINITY;
-            float dlt = 0.0f;
-            if (row_valid) {
-                lse2 = p.lse[static_cast<size_t>(bh) * p.length + q_index] * kLog2e;
-                dlt = p.delta[static_cast<size_t>(bh) * p.length + q_index];
+        for (int h = 0; ok && h < steps; ++h) {
+            const int b = h & 1;
+            const int stage = h % kBwdStages;
+            const int q0 = kb * kTile + h * kSub + part * 32;  // first query of my columns
+            if (threadIdx.x == 64) {
+                FB_TRACE(0, h, 0);
             }
-            if (!sm100::mbar_wait(sdp_full, it & 1, abort)) {
+            // stage_full covers the statistics; scores_full the two accumulators.
+            if (!sm100::mbar_wait(bar.stage_full(stage), (h / kBwdStages) & 1, abort) ||
+                !sm100::mbar_wait(bar.scores_full(b), (h >> 1) & 1, abort) ||
+                !sm100::mbar_wait(bar.operands_free(b), ((h >> 1) & 1) ^ 1u, abort)) {
                 ok = false;
                 break;
+            }
+            if (threadIdx.x == 64) {
+                FB_TRACE(0, h, 1);
             }
             sm100::tc_fence_after_sync();
             uint32_t s_raw[32];
             uint32_t dp_raw[32];
-            sm100::tmem_ld_32x32(tmem_s + lane_base + col, s_raw);
-            sm100::tmem_ld_32x32(tmem_dp + lane_base + col, dp_raw);
+            sm100::tmem_ld_32x32(tmem_st(b) + lane_base + part * 32, s_raw);
+            sm100::tmem_ld_32x32(tmem_dpt(b) + lane_base + part * 32, dp_raw);
+            // My 32 queries' statistics: every lane reads the same addresses (broadcast).
+            const uint32_t stat = stats + stage * 2 * kStatBytes + part * 128;
+            float lse2[32];
+            float dlt[32];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                float a0, a1, a2, a3;
+                asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                             : "=f"(a0), "=f"(a1), "=f"(a2), "=f"(a3)
+                             : "r"(stat + c * 16));
+                lse2[4 * c] = a0 * kLog2e;
+                lse2[4 * c + 1] = a1 * kLog2e;
+                lse2[4 * c + 2] = a2 * kLog2e;
+                lse2[4 * c + 3] = a3 * kLog2e;
+                asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                             : "=f"(dlt[4 * c]), "=f"(dlt[4 * c + 1]), "=f"(dlt[4 * c + 2]),
+                               "=f"(dlt[4 * c + 3])
+                             : "r"(stat + kStatBytes + c * 16));
+            }
             sm100::tmem_ld_wait();
+            if (threadIdx.x == 64) {
+                FB_TRACE(0, h, 2);
+            }
             float pv[32];
             float dsv[32];
-            if (it == 0) {
-                // The diagonal tile: keys after the query are masked.
+            if (h < 2 || kb * kTile + (h + 1) * kSub > p.length) {
+                // The diagonal tile (a key is visible to the queries at or after it) or a
+                // sub-step with absent queries, whose statistics slots were not filled:
+                // both tests select rather than multiply.
+                const int first_visible = h < 2 ? k_index : 0;
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    const float e = fast_exp2(fmaf(__uint_as_float(s_raw[i]), scale2, -lse2));
-                    pv[i] = (col + i <= row) ? e : 0.0f;
-                    dsv[i] = pv[i] * (__uint_as_float(dp_raw[i]) - dlt);
+                    const bool visible = first_visible <= q0 + i && q0 + i < p.length;
+                    const float e = fast_exp2(fmaf(__uint_as_float(s_raw[i]), scale2, -lse2[i]));
+                    pv[i] = visible ? e : 0.0f;
+                    dsv[i] = visible ? e * (__uint_as_float(dp_raw[i]) - dlt[i]) : 0.0f;
                 }
             } else {
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    pv[i] = fast_exp2(fmaf(__uint_as_float(s_raw[i]), scale2, -lse2));
-                    dsv[i] = pv[i] * (__uint_as_float(dp_raw[i]) - dlt);
+                    pv[i] = fast_exp2(fmaf(__uint_as_float(s_raw[i]), scale2, -lse2[i]));
+                    dsv[i] = pv[i] * (__uint_as_float(dp_raw[i]) - dlt[i]);
                 }
             }
-            store_operand_row(p_tile, row, col, pv);
-            store_operand_row(ds_tile, row, col, dsv);
+            store_panel_row(pt_tiles + b * kPanelBytes, row, part * 32, pv);
+            store_panel_row(dst_tiles + b * kPanelBytes, row, part * 32, dsv);
             fence_async_shared();
             sm100::tc_fence_before_sync();
-            sm100::mbar_arrive(pds_ready);
+            sm100::mbar_arrive(bar.operands_ready(b));
+            if (threadIdx.x == 64) {
+                FB_TRACE(0, h, 3);
+            }
         }
-        if (ok && part < 2 && sm100::mbar_wait(grads_done, 0, abort)) {
+        if (threadIdx.x == 64) {
+            FB_TRACE(0, 39, 0);
+        }
+        if (ok && sm100::mbar_wait(bar.done(), 0, abort)) {
+            if (threadIdx.x == 64) {
+                FB_TRACE(0, 39, 1);
+            }
             sm100::tc_fence_after_sync();
             // Rows of dV/dK are keys; this warp writes 32 of the 64 columns. dS was kept
             // unscaled, so the score scale is applied to dK here.
-            const int k_index = kb * kTile + row;
             uint32_t dv_raw[32];
             uint32_t dk_raw[32];
             sm100::tmem_ld_32x32(tmem_dv + lane_base + part * 32, dv_raw);
@@ -609,26 +744,36 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     float a[8];
-                    float b[8];
+                    float bv[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         a[i] = __uint_as_float(dk_raw[c * 8 + i]) * p.scale;
-                        b[i] = __uint_as_float(dv_raw[c * 8 + i]);
+                        bv[i] = __uint_as_float(dv_raw[c * 8 + i]);
                     }
                     *reinterpret_cast<uint4*>(dk_out + c * 8) = fb::pack8(a);
-                    *reinterpret_cast<uint4*>(dv_out + c * 8) = fb::pack8(b);
+                    *reinterpret_cast<uint4*>(dv_out + c * 8) = fb::pack8(bv);
                 }
             }
             sm100::tc_fence_before_sync();
         }
     }
+    if (threadIdx.x == 64) {
+        FB_TRACE(0, 39, 2);
+    }
     finish(abort_flag, tmem, 512, warp);
+    if (threadIdx.x == 64) {
+        FB_TRACE(0, 39, 3);
+    }
 }
 
 // ---- backward: dQ ---------------------------------------------------------------------------------
+//
+// One CTA per (head, 128 queries), 64 keys per sub-step: S = Q K^T and dP = dO V^T
+// into double-buffered accumulators, dS (queries on the rows) to double-buffered
+// shared memory, dQ += dS K accumulated in TMEM.
 
-// Q, dO, 2 x (K, V), dS
-constexpr int kDqSmem = 1024 + kTileBytes * 6 + 2 * kPanelBytes + 128;
+// resident Q, dO (2 x 16 KB) + ring of (K_g, V_g) (4 x 16 KB) + two dS buffers (2 x 16 KB)
+constexpr int kDqSmem = 1024 + 2 * kTileBytes + kBwdStages * 2 * kSubBytes + 2 * kPanelBytes + 256;
 
 __global__ void __launch_bounds__(kBwdThreads, 1)
     fb_attention_dq(const __grid_constant__ AttnParams p) {
@@ -636,13 +781,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     const uint32_t base = (sm100::smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t q_tile = base;
     const uint32_t do_tile = base + kTileBytes;
-    const uint32_t ring = base + 2 * kTileBytes;            // stage s: K at +0, V at +16 KB
-    const uint32_t ds_tile = ring + 4 * kTileBytes;
-    const uint32_t bars = ds_tile + 2 * kPanelBytes;
-    const uint32_t qdo_full = bars, sdp_full = bars + 8, ds_ready = bars + 16,
-                   dq_done = bars + 24;
-    auto stage_full = [&](int s) { return bars + 32 + 8u * s; };
-    auto stage_empty = [&](int s) { return bars + 48 + 8u * s; };
+    const uint32_t ring = base + 2 * kTileBytes;                 // stage: K_g then V_g
+    const uint32_t ds_tiles = ring + kBwdStages * 2 * kSubBytes;  // dS[0], dS[1]
+    const BwdBarriers bar{ds_tiles + 2 * kPanelBytes};
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -653,19 +794,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     const int bh = static_cast<int>(blockIdx.x % bh_count);
     const int head = bh % p.heads;
     const int seq = bh / p.heads;
-    const int iterations = qb + 1;
+    const int steps = 2 * (qb + 1);  // 64-key sub-steps up to and including the diagonal tile
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
-        sm100::mbar_init(qdo_full, 1);
-        sm100::mbar_init(sdp_full, 1);
-        sm100::mbar_init(ds_ready, 512);
-        sm100::mbar_init(dq_done, 1);
-        for (int s = 0; s < 2; ++s) {
-            sm100::mbar_init(stage_full(s), 1);
-            sm100::mbar_init(stage_empty(s), 1);
-        }
-        sm100::mbar_fence_init();
+        init_bwd_barriers(bar, 256);
     }
     if (warp == 1) {
         sm100::tmem_alloc(sm100::smem_u32(&tmem_slot), 512);
@@ -674,25 +807,28 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     __syncthreads();
     sm100::tc_fence_after_sync();
     const uint32_t tmem = tmem_slot;
-    const uint32_t tmem_s = tmem, tmem_dp = tmem + 128, tmem_dq = tmem + 256;
+    auto tmem_s = [&](int b) { return tmem + 64u * b; };
+    auto tmem_dp = [&](int b) { return tmem + 128u + 64u * b; };
+    const uint32_t tmem_dq = tmem + 256;
     volatile int* abort = &abort_flag;
 
     if (warp == 0) {
         if (lane == 0) {
-            sm100::mbar_expect_tx(qdo_full, 2 * kTileBytes);
-            tma_load_4d(q_tile, &p.map_q, qdo_full, 0, qb * kTile, head, seq);
-            tma_load_4d(do_tile, &p.map_do, qdo_full, 0, qb * kTile, head, seq);
+            sm100::mbar_expect_tx(bar.resident(), 2 * kTileBytes);
+            tma_load_4d(q_tile, &p.map_q, bar.resident(), 0, qb * kTile, head, seq);
+            tma_load_4d(do_tile, &p.map_do, bar.resident(), 0, qb * kTile, head, seq);
             int stage = 0;
             uint32_t phase = 0;
-            for (int j = 0; j < iterations; ++j) {
-                if (!sm100::mbar_wait(stage_empty(stage), phase ^ 1u, abort)) {
+            for (int g = 0; g < steps; ++g) {
+                if (!sm100::mbar_wait(bar.stage_empty(stage), phase ^ 1u, abort)) {
                     break;
                 }
-                const uint32_t dst = ring + stage * 2 * kTileBytes;
-                sm100::mbar_expect_tx(stage_full(stage), 2 * kTileBytes);
-                tma_load_4d(dst, &p.map_k, stage_full(stage), 0, j * kTile, head, seq);
-                tma_load_4d(dst + kTileBytes, &p.map_v, stage_full(stage), 0, j * kTile, head, seq);
-                if (++stage == 2) {
+                const uint32_t dst = ring + stage * 2 * kSubBytes;
+                sm100::mbar_expect_tx(bar.stage_full(stage), 2 * kSubBytes);
+                tma_load_4d(dst, &p.map_k64, bar.stage_full(stage), 0, g * kSub, head, seq);
+                tma_load_4d(dst + kSubBytes, &p.map_v64, bar.stage_full(stage), 0, g * kSub, head,
+                            seq);
+                if (++stage == kBwdStages) {
                     stage = 0;
                     phase ^= 1u;
                 }
@@ -700,52 +836,58 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            bool ok = sm100::mbar_wait(qdo_full, 0, abort);
-            int stage = 0;
-            uint32_t phase = 0;
-            for (int j = 0; ok && j < iterations; ++j) {
-                if (!sm100::mbar_wait(stage_full(stage), phase, abort)) {
+            bool ok = sm100::mbar_wait(bar.resident(), 0, abort);
+            auto issue_scores = [&](int g) -> bool {
+                const int stage = g % kBwdStages;
+                if (!sm100::mbar_wait(bar.stage_full(stage), (g / kBwdStages) & 1, abort)) {
+                    return false;
+                }
+                sm100::tc_fence_after_sync();
+                const uint32_t k_sub = ring + stage * 2 * kSubBytes;
+                const uint32_t v_sub = k_sub + kSubBytes;
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    sm100::mma_f16_ss(tmem_s(g & 1), desc_kmajor(q_tile, ks),
+                                      desc_kmajor(k_sub, ks), kIdescSub, ks > 0);
+                }
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    sm100::mma_f16_ss(tmem_dp(g & 1), desc_kmajor(do_tile, ks),
+                                      desc_kmajor(v_sub, ks), kIdescSub, ks > 0);
+                }
+                sm100::mma_commit(bar.scores_full(g & 1));
+                return true;
+            };
+            ok = ok && issue_scores(0);
+            for (int g = 0; ok && g < steps; ++g) {
+                const int b = g & 1;
+                if (g + 1 < steps && !issue_scores(g + 1)) {
+                    break;
+                }
+                if (!sm100::mbar_wait(bar.operands_ready(b), (g >> 1) & 1, abort)) {
                     break;
                 }
                 sm100::tc_fence_after_sync();
-                const uint32_t k_tile = ring + stage * 2 * kTileBytes;
-                const uint32_t v_tile = k_tile + kTileBytes;
+                const int stage = g % kBwdStages;
+                const uint32_t k_sub = ring + stage * 2 * kSubBytes;
+                const uint32_t ds = ds_tiles + b * kPanelBytes;
+                // dQ += dS K over this sub-step's 64 keys (the K tile read MN-major).
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {
-                    sm100::mma_f16_ss(tmem_s, desc_kmajor(q_tile, ks), desc_kmajor(k_tile, ks),
-                                      kIdescS, ks > 0);
+                    sm100::mma_f16_ss(tmem_dq, desc_kmajor(ds, ks), desc_mnmajor(k_sub, ks, 16),
+                                      kIdescPV, (g | ks) != 0);
                 }
-#pragma unroll
-                for (int ks = 0; ks < 4; ++ks) {
-                    sm100::mma_f16_ss(tmem_dp, desc_kmajor(do_tile, ks), desc_kmajor(v_tile, ks),
-                                      kIdescS, ks > 0);
-                }
-                sm100::mma_commit(sdp_full);
-                if (!sm100::mbar_wait(ds_ready, j & 1, abort)) {
-                    break;
-                }
-                sm100::tc_fence_after_sync();
-                // dQ += dS K (K = the 128 keys of this tile; K tile read MN-major).
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    sm100::mma_f16_ss(tmem_dq, desc_kmajor_wide(ds_tile, ks),
-                                      desc_mnmajor(k_tile, ks, 16), kIdescPV, (j | ks) != 0);
-                }
-                sm100::mma_commit(stage_empty(stage));
-                if (j + 1 == iterations) {
-                    sm100::mma_commit(dq_done);
-                }
-                if (++stage == 2) {
-                    stage = 0;
-                    phase ^= 1u;
+                sm100::mma_commit(bar.stage_empty(stage));
+                sm100::mma_commit(bar.operands_free(b));
+                if (g + 1 == steps) {
+                    sm100::mma_commit(bar.done());
                 }
             }
         }
     } else {
         const int quadrant = warp % 4;
-        const int part = (warp - 2) / 4;
-        const int col = part * 32;
-        const int row = quadrant * 32 + lane;
+        const int part = (warp - 2) / 4;                 // which 32 of the 64 key columns
+        const int row = quadrant * 32 + lane;            // query row inside the tile
         const int q_index = qb * kTile + row;
         const bool row_valid = q_index < p.length;
         const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
@@ -757,23 +899,27 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             dlt = p.delta[static_cast<size_t>(bh) * p.length + q_index];
         }
         bool ok = true;
-        for (int j = 0; ok && j < iterations; ++j) {
-            if (!sm100::mbar_wait(sdp_full, j & 1, abort)) {
+        for (int g = 0; ok && g < steps; ++g) {
+            const int b = g & 1;
+            if (!sm100::mbar_wait(bar.scores_full(b), (g >> 1) & 1, abort) ||
+                !sm100::mbar_wait(bar.operands_free(b), ((g >> 1) & 1) ^ 1u, abort)) {
                 ok = false;
                 break;
             }
             sm100::tc_fence_after_sync();
             uint32_t s_raw[32];
             uint32_t dp_raw[32];
-            sm100::tmem_ld_32x32(tmem_s + lane_base + col, s_raw);
-            sm100::tmem_ld_32x32(tmem_dp + lane_base + col, dp_raw);
+            sm100::tmem_ld_32x32(tmem_s(b) + lane_base + part * 32, s_raw);
+            sm100::tmem_ld_32x32(tmem_dp(b) + lane_base + part * 32, dp_raw);
             sm100::tmem_ld_wait();
+            const int k0 = g * kSub + part * 32;  // first key of my columns
             float dsv[32];
-            if (j == qb) {
+            if (g + 2 >= steps) {
+                // The diagonal tile: keys after the query are masked.
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
                     const float e = fast_exp2(fmaf(__uint_as_float(s_raw[i]), scale2, -lse2));
-                    dsv[i] = (col + i <= row) ? e * (__uint_as_float(dp_raw[i]) - dlt) : 0.0f;
+                    dsv[i] = (k0 + i <= q_index) ? e * (__uint_as_float(dp_raw[i]) - dlt) : 0.0f;
                 }
             } else {
 #pragma unroll
@@ -782,12 +928,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                     dsv[i] = e * (__uint_as_float(dp_raw[i]) - dlt);
                 }
             }
-            store_operand_row(ds_tile, row, col, dsv);
+            store_panel_row(ds_tiles + b * kPanelBytes, row, part * 32, dsv);
             fence_async_shared();
             sm100::tc_fence_before_sync();
-            sm100::mbar_arrive(ds_ready);
+            sm100::mbar_arrive(bar.operands_ready(b));
         }
-        if (ok && part < 2 && sm100::mbar_wait(dq_done, 0, abort)) {
+        if (ok && sm100::mbar_wait(bar.done(), 0, abort)) {
             sm100::tc_fence_after_sync();
             uint32_t raw[32];
             sm100::tmem_ld_32x32(tmem_dq + lane_base + part * 32, raw);
@@ -838,7 +984,8 @@ cudaError_t encode_fn(EncodeTiled* out) {
 }
 
 // (column 0..63, row 0..length-1, head, sequence) view of an FP16 tensor.
-cudaError_t make_map(CUtensorMap* map, const AttentionView& v, const AttentionShape& s) {
+cudaError_t make_map(CUtensorMap* map, const AttentionView& v, const AttentionShape& s,
+                     int box_rows = kTile) {
     EncodeTiled encode = nullptr;
     const cudaError_t e = encode_fn(&encode);
     if (e != cudaSuccess) {
@@ -848,7 +995,7 @@ cudaError_t make_map(CUtensorMap* map, const AttentionView& v, const AttentionSh
     const cuuint64_t strides[3] = {static_cast<cuuint64_t>(v.row_stride) * 2,
                                    static_cast<cuuint64_t>(v.head_stride) * 2,
                                    static_cast<cuuint64_t>(v.sequence_stride) * 2};
-    const cuuint32_t box[4] = {kHead, kTile, 1, 1};
+    const cuuint32_t box[4] = {kHead, static_cast<cuuint32_t>(box_rows), 1, 1};
     const cuuint32_t elem[4] = {1, 1, 1, 1};
     const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(v.base),
                               dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -919,6 +1066,10 @@ cudaError_t attention_backward(const AttentionView& dq, const AttentionView& dk,
     if (e == cudaSuccess) e = make_map(&p.map_k, k, shape);
     if (e == cudaSuccess) e = make_map(&p.map_v, v, shape);
     if (e == cudaSuccess) e = make_map(&p.map_do, d_o, shape);
+    if (e == cudaSuccess) e = make_map(&p.map_q64, q, shape, kSub);
+    if (e == cudaSuccess) e = make_map(&p.map_k64, k, shape, kSub);
+    if (e == cudaSuccess) e = make_map(&p.map_v64, v, shape, kSub);
+    if (e == cudaSuccess) e = make_map(&p.map_do64, d_o, shape, kSub);
     if (e != cudaSuccess) {
         return e;
     }
@@ -1010,6 +1161,12 @@ fb::AttentionView heads_view(const void* base, size_t batches, size_t length) {
 }  // namespace
 
 extern "C" {
+
+#ifdef FB_ATTN_TRACE
+__attribute__((visibility("default"))) int flint_b200_debug_trace(void* host, size_t bytes) {
+    return static_cast<int>(cudaMemcpyFromSymbol(host, fb::g_trace, bytes));
+}
+#endif
 
 flint_status flint_b200_attention_forward(void* o, void* lse, const void* q, const void* k,
                                           const void* v, size_t batches, size_t length,
