@@ -45,7 +45,6 @@ constexpr int kTileBytes = kTile * kHead * 2;  // 16 KB: one Q/K/V/dO tile
 constexpr int kPanelBytes = kTile * 128;       // 16 KB: 64 FP16 columns of a 128-row P/dS tile
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
-constexpr flint_status kInvalid = FLINT_ERROR_INVALID_ARGUMENT;
 
 __device__ int g_attention_error = 0;
 
@@ -143,7 +142,6 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile, int kstep, uint3
 
 constexpr uint32_t kIdescS = sm100::instr_desc_f16(128, 128, false, false);   // Q K^T, dO V^T
 constexpr uint32_t kIdescPV = sm100::instr_desc_f16(128, 64, false, true);    // P V, dS K
-constexpr uint32_t kIdescT = sm100::instr_desc_f16(128, 64, true, true);      // P^T dO, dS^T Q
 
 __device__ __forceinline__ void finish(int abort_value, uint32_t tmem_base, uint32_t cols,
                                        int warp) {

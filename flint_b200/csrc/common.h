@@ -58,6 +58,10 @@ unsigned long long launch_count();
 // Number of SMs of the current device (cached per device index).
 cudaError_t sm_count(int* sms);
 
+// Device error word of the column-sum kernels: set when a bounded wait for a
+// staged row gave up (read, and cleared if asked, by flint_b200_kernel_fault).
+cudaError_t reductions_error_flag(int* value, bool reset);
+
 }  // namespace fb
 
 #define FB_CUDA(call)                                                  \

@@ -41,6 +41,69 @@ __device__ __forceinline__ void comp_add_product(Comp& acc, float a, float b) {
     comp_add(acc, p);
 }
 
+// Two independent compensated sums side by side, on Blackwell's packed FP32
+// instructions (add/sub/mul/fma.rn.f32x2): each half is rounded exactly like the
+// scalar instruction, so the bits equal comp_add / comp_add_product applied to
+// the halves separately, at half the instruction count.
+using F2 = unsigned long long;  // two floats in a 64-bit register pair (.x low)
+
+__device__ __forceinline__ F2 f2_pack(float lo, float hi) {
+    F2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void f2_unpack(F2 v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ F2 f2_add(F2 a, F2 b) {
+    F2 r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ F2 f2_sub(F2 a, F2 b) {
+    F2 r;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ F2 f2_mul(F2 a, F2 b) {
+    F2 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ F2 f2_fma(F2 a, F2 b, F2 c) {
+    F2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
+struct Comp2 {
+    F2 s = 0;  // (+0, +0)
+    F2 e = 0;
+};
+
+__device__ __forceinline__ void comp_add2(Comp2& a, F2 v) {
+    const F2 t = f2_add(a.s, v);
+    const F2 vp = f2_sub(t, a.s);
+    const F2 err = f2_add(f2_sub(a.s, f2_sub(t, vp)), f2_sub(v, vp));
+    a.e = f2_add(a.e, err);
+    a.s = t;
+}
+
+__device__ __forceinline__ void comp_add_product2(Comp2& acc, F2 a, F2 b) {
+    // The products are rounded by the scalar instruction: a packed multiply whose
+    // result feeds a packed add was seen fused into one fma (a single rounding),
+    // which an explicitly rounded scalar multiply never is.
+    float a0, a1, b0, b1;
+    f2_unpack(a, a0, a1);
+    f2_unpack(b, b0, b1);
+    const F2 p = f2_pack(__fmul_rn(a0, b0), __fmul_rn(a1, b1));
+    // fma(a, b, -p) is the product's rounding error, exactly; (-0) - p negates p
+    // exactly for every p, signed zeros included.
+    const F2 minus_p = f2_sub(f2_pack(-0.0f, -0.0f), p);
+    acc.e = f2_add(acc.e, f2_fma(a, b, minus_p));
+    comp_add2(acc, p);
+}
+
 // Merges (bs, be) into a: the errors are added first, b's sum goes through
 // TwoSum, then the errors are added back. Symmetric in its operands' bits.
 __device__ __forceinline__ void comp_merge(Comp& a, float bs, float be) {

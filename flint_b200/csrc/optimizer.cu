@@ -436,7 +436,9 @@ flint_status flint_b200_kernel_fault(int* raised) {
     int attention = 0;
     FB_CUDA(fb::gemm_error_flag(&gemm, true));
     FB_CUDA(fb::attention_error_flag(&attention, true));
-    *raised = (gemm != 0 || attention != 0) ? 1 : 0;
+    int reductions = 0;
+    FB_CUDA(fb::reductions_error_flag(&reductions, true));
+    *raised = (gemm != 0 || attention != 0 || reductions != 0) ? 1 : 0;
     return FLINT_OK;
 }
 

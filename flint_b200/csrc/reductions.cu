@@ -41,96 +41,272 @@ constexpr size_t column_sum_workspace(size_t rows, size_t cols) {
 
 enum class Source { kHalf, kHalfTimesXhat, kFloat };
 
-// First pass. CTA (chunk, tile) with 32 x 8 threads: thread (px, ly) owns the
-// 8 columns of piece tile*32+px and the row stream ly.
+// First pass. CTA (chunk, tile) with 32 x 9 threads: warps 0-7 add (thread
+// (px, ly) owns the 8 columns of piece tile*32+px and the row stream ly), warp 8
+// fetches.
+//
+// The chunk's rows reach the CTA through shared memory: lane l of the fetching
+// warp issues one bulk asynchronous copy per row segment (32 rows per stage, a
+// ring of stages, each completing on its own mbarrier), so whole stages are in
+// flight per CTA while every adding thread still takes its stream's rows
+// strictly in row order. (A thread that loaded its own rows would add each one as
+// it arrived, paying one memory latency per row.) The additions run on packed
+// FP32 pairs: columns (0,1), (2,3), (4,5), (6,7) of the piece.
 template <Source kSource>
-__global__ void __launch_bounds__(kTilePieces * kLaneRows)
+struct Staging {
+    static constexpr int kMainBytes = kSource == Source::kFloat ? 32 : 16;  // per piece and row
+    static constexpr int kXBytes = kSource == Source::kHalfTimesXhat ? 32 : 0;
+    static constexpr int kRows = 32;                                        // rows per stage
+    static constexpr int kMainStage = kRows * kTilePieces * kMainBytes;
+    static constexpr int kStage = kMainStage + kRows * kTilePieces * kXBytes;
+    static constexpr int kStages = kSource == Source::kHalf ? 3 : 2;
+    static constexpr int kBytes = kStages * kStage + 128;
+};
+// After the last stage the ring's memory holds the eight streams' sums for the merge.
+static_assert(Staging<Source::kHalf>::kStages * Staging<Source::kHalf>::kStage >=
+                  2 * kLaneRows * kTilePieces * 8 * 4,
+              "the merge buffers must fit in the ring");
+
+__device__ int g_reduction_error = 0;
+
+__device__ __forceinline__ uint32_t shared_address(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// Bounded mbarrier wait: false (and the flag set) after about a second of SM clocks.
+__device__ __forceinline__ bool staged_wait(uint32_t bar, uint32_t parity, volatile int* abort) {
+    const long long start = clock64();
+    for (uint32_t spin = 0;; ++spin) {
+        uint32_t done = 0;
+        asm volatile(
+            "{\n.reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done != 0) {
+            return true;
+        }
+        if ((spin & 63u) == 63u && (*abort != 0 || clock64() - start > 2000000000LL)) {
+            *abort = 1;
+            return false;
+        }
+    }
+}
+
+template <Source kSource>
+__global__ void __launch_bounds__(kTilePieces * (kLaneRows + 1))
     fb_column_partials(float4* __restrict__ partial, const void* __restrict__ src,
                        const float4* __restrict__ x, const float* __restrict__ mean,
                        const float* __restrict__ rstd, size_t rows, int pieces) {
-    __shared__ float sh_s[kLaneRows][kTilePieces][8];
-    __shared__ float sh_e[kLaneRows][kTilePieces][8];
+    using S = Staging<kSource>;
+    extern __shared__ unsigned char staging_raw[];
+    __shared__ float sh_mean[kSource == Source::kHalfTimesXhat ? kChunkRows : 1];
+    __shared__ float sh_rstd[kSource == Source::kHalfTimesXhat ? kChunkRows : 1];
+    __shared__ alignas(8) unsigned long long barriers[2 * S::kStages];
+    __shared__ int abort_flag;
     const int px = threadIdx.x;
-    const int ly = threadIdx.y;
-    const int piece = blockIdx.y * kTilePieces + px;
+    const int ly = threadIdx.y;  // 0-7 add, 8 fetches
+    const int first_piece = blockIdx.y * kTilePieces;
+    const int piece = first_piece + px;
+    const int width = min(kTilePieces, pieces - first_piece);  // pieces this tile holds
     const size_t first = size_t{blockIdx.x} * kChunkRows;
-    const size_t end = rows - first < kChunkRows ? rows : first + kChunkRows;
+    const int chunk_rows = static_cast<int>(rows - first < kChunkRows ? rows - first : kChunkRows);
+    const int stages_total = (chunk_rows + S::kRows - 1) / S::kRows;
+    const uint32_t staging = (shared_address(staging_raw) + 127u) & ~127u;
+    const uint32_t bar0 = shared_address(barriers);
+    auto full_bar = [&](int slot) { return bar0 + 8u * slot; };
+    auto empty_bar = [&](int slot) { return bar0 + 8u * (S::kStages + slot); };
 
-    Comp acc[8];
-    // One row of this thread's stream: 8 values added in column order.
-    auto add_row = [&](const float (&v)[8], const float (&xs)[8], size_t r) {
-        if constexpr (kSource == Source::kHalfTimesXhat) {
-            const float m = mean[r];
-            const float rs = rstd[r];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float xhat = __fmul_rn(__fsub_rn(xs[j], m), rs);
-                fb::comp_add_product(acc[j], v[j], xhat);
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                fb::comp_add(acc[j], v[j]);
-            }
+    if (ly == 0 && px == 0) {
+        abort_flag = 0;
+        for (int i = 0; i < S::kStages; ++i) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(full_bar(i)) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(empty_bar(i)),
+                         "r"(kLaneRows)
+                         : "memory");
         }
-    };
-    auto load_row = [&](float (&v)[8], float (&xs)[8], size_t r) {
-        const size_t at = r * pieces + piece;
-        if constexpr (kSource == Source::kFloat) {
-            fb::load8(v, static_cast<const float4*>(src) + at * 2);
-        } else {
-            fb::unpack8(v, static_cast<const uint4*>(src)[at]);
-            if constexpr (kSource == Source::kHalfTimesXhat) {
-                fb::load8(xs, x + at * 2);
-            }
-        }
-    };
-    if (piece < pieces) {
-        // The additions stay in row order; only the loads are issued ahead, kDepth rows
-        // at a time, so that their latencies overlap.
-        constexpr int kDepth = kSource == Source::kHalf ? 8 : 4;
-        size_t r = first + ly;
-        for (; r + (kDepth - 1) * kLaneRows < end; r += kDepth * kLaneRows) {
-            float v[kDepth][8];
-            float xs[kDepth][8];
-#pragma unroll
-            for (int d = 0; d < kDepth; ++d) {
-                load_row(v[d], xs[d], r + d * kLaneRows);
-            }
-#pragma unroll
-            for (int d = 0; d < kDepth; ++d) {
-                add_row(v[d], xs[d], r + d * kLaneRows);
-            }
-        }
-        for (; r < end; r += kLaneRows) {
-            float v[8];
-            float xs[8];
-            load_row(v, xs, r);
-            add_row(v, xs, r);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if constexpr (kSource == Source::kHalfTimesXhat) {
+        const int t = ly * kTilePieces + px;
+        if (t < chunk_rows) {
+            sh_mean[t] = mean[first + t];
+            sh_rstd[t] = rstd[first + t];
         }
     }
+    __syncthreads();
+    volatile int* abort = &abort_flag;
+    bool ok = true;
+    fb::Comp2 acc[4];
+
+    if (ly == kLaneRows) {
+        // ---- fetching warp: lane l copies row l of each stage (and its x segment) ----
+        const uint32_t main_bytes = static_cast<uint32_t>(width) * S::kMainBytes;
+        const uint32_t x_bytes = static_cast<uint32_t>(width) * S::kXBytes;
+        for (int k = 0; k < stages_total; ++k) {
+            const int slot = k % S::kStages;
+            if (k >= S::kStages &&
+                !staged_wait(empty_bar(slot), static_cast<uint32_t>(k / S::kStages - 1) & 1u,
+                             abort)) {
+                ok = false;
+                break;
+            }
+            const int here = min(S::kRows, chunk_rows - k * S::kRows);
+            if (px == 0) {
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
+                                 full_bar(slot)),
+                             "r"(static_cast<uint32_t>(here) * (main_bytes + x_bytes))
+                             : "memory");
+            }
+            if (px < here) {
+                const size_t at =
+                    (first + static_cast<size_t>(k) * S::kRows + px) * pieces + first_piece;
+                const uint32_t dst =
+                    staging + slot * S::kStage + px * (kTilePieces * S::kMainBytes);
+                asm volatile(
+                    "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                    ::"r"(dst), "l"(static_cast<const unsigned char*>(src) + at * S::kMainBytes),
+                      "r"(main_bytes), "r"(full_bar(slot))
+                    : "memory");
+                if constexpr (S::kXBytes != 0) {
+                    const uint32_t xdst = staging + slot * S::kStage + S::kMainStage +
+                                          px * (kTilePieces * S::kXBytes);
+                    asm volatile(
+                        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                        ::"r"(xdst),
+                          "l"(reinterpret_cast<const unsigned char*>(x) + at * S::kXBytes),
+                          "r"(x_bytes), "r"(full_bar(slot))
+                        : "memory");
+                }
+            }
+        }
+    } else {
+        // ---- adding warps ----
+        auto load16 = [](uint4& q, uint32_t at) {
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
+                         : "r"(at));
+        };
+        auto pair_of = [](uint32_t lo, uint32_t hi) {
+            return static_cast<fb::F2>(lo) | (static_cast<fb::F2>(hi) << 32);
+        };
+        for (int k = 0; k < stages_total; ++k) {
+            const int slot = k % S::kStages;
+            if (!staged_wait(full_bar(slot), static_cast<uint32_t>(k / S::kStages) & 1u, abort)) {
+                ok = false;
+                break;
+            }
+            const int here = min(S::kRows, chunk_rows - k * S::kRows);
+            const uint32_t stage = staging + slot * S::kStage;
+            if (px < width) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        sh_s[ly][px][j] = acc[j].s;
-        sh_e[ly][px][j] = acc[j].e;
+                for (int j = 0; j < S::kRows / kLaneRows; ++j) {
+                    const int row = ly + kLaneRows * j;  // row inside the stage
+                    if (row >= here) {
+                        break;
+                    }
+                    fb::F2 v[4];
+                    const uint32_t at =
+                        stage + row * (kTilePieces * S::kMainBytes) + px * S::kMainBytes;
+                    uint4 a;
+                    load16(a, at);
+                    if constexpr (kSource == Source::kFloat) {
+                        uint4 b;
+                        load16(b, at + 16);
+                        v[0] = pair_of(a.x, a.y);
+                        v[1] = pair_of(a.z, a.w);
+                        v[2] = pair_of(b.x, b.y);
+                        v[3] = pair_of(b.z, b.w);
+                    } else {
+                        float f[8];
+                        fb::unpack8(f, a);
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            v[c] = fb::f2_pack(f[2 * c], f[2 * c + 1]);
+                        }
+                    }
+                    if constexpr (kSource == Source::kHalfTimesXhat) {
+                        uint4 x0;
+                        uint4 x1;
+                        const uint32_t xat = stage + S::kMainStage +
+                                             row * (kTilePieces * S::kXBytes) + px * S::kXBytes;
+                        load16(x0, xat);
+                        load16(x1, xat + 16);
+                        const fb::F2 xs[4] = {pair_of(x0.x, x0.y), pair_of(x0.z, x0.w),
+                                              pair_of(x1.x, x1.y), pair_of(x1.z, x1.w)};
+                        const float m = sh_mean[k * S::kRows + row];
+                        const float rs = sh_rstd[k * S::kRows + row];
+                        const fb::F2 m2 = fb::f2_pack(m, m);
+                        const fb::F2 rs2 = fb::f2_pack(rs, rs);
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const fb::F2 xhat = fb::f2_mul(fb::f2_sub(xs[c], m2), rs2);
+                            fb::comp_add_product2(acc[c], v[c], xhat);
+                        }
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            fb::comp_add2(acc[c], v[c]);
+                        }
+                    }
+                }
+            }
+            // This warp is done with the slot; the fetching warp refills it once all eight are.
+            __syncwarp();
+            if (px == 0) {
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_bar(slot))
+                             : "memory");
+            }
+        }
+    }
+    if (!ok && px == 0) {
+        atomicExch(&g_reduction_error, 1);
+    }
+    // Every stage has been consumed (or the wait gave up): the ring's memory now
+    // carries the eight streams' (sum, error) pairs to stream 0, which merges them
+    // in stream order.
+    __syncthreads();
+    float* sh_s = reinterpret_cast<float*>(staging_raw + (staging - shared_address(staging_raw)));
+    float* sh_e = sh_s + kLaneRows * kTilePieces * 8;
+    if (ly < kLaneRows) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            float lo, hi;
+            fb::f2_unpack(acc[c].s, lo, hi);
+            sh_s[(ly * kTilePieces + px) * 8 + 2 * c] = lo;
+            sh_s[(ly * kTilePieces + px) * 8 + 2 * c + 1] = hi;
+            fb::f2_unpack(acc[c].e, lo, hi);
+            sh_e[(ly * kTilePieces + px) * 8 + 2 * c] = lo;
+            sh_e[(ly * kTilePieces + px) * 8 + 2 * c + 1] = hi;
+        }
     }
     __syncthreads();
     if (ly != 0 || piece >= pieces) {
         return;
     }
+    Comp total[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        total[j].s = sh_s[px * 8 + j];
+        total[j].e = sh_e[px * 8 + j];
+    }
     for (int other = 1; other < kLaneRows; ++other) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            fb::comp_merge(acc[j], sh_s[other][px][j], sh_e[other][px][j]);
+            fb::comp_merge(total[j], sh_s[(other * kTilePieces + px) * 8 + j],
+                           sh_e[(other * kTilePieces + px) * 8 + j]);
         }
     }
     // Chunk c occupies rows 2c (sums) and 2c+1 (errors) of a [2*chunks, cols] FP32 matrix.
     float4* out = partial + size_t{blockIdx.x} * pieces * 4 + size_t(piece) * 2;
-    out[0] = make_float4(acc[0].s, acc[1].s, acc[2].s, acc[3].s);
-    out[1] = make_float4(acc[4].s, acc[5].s, acc[6].s, acc[7].s);
+    out[0] = make_float4(total[0].s, total[1].s, total[2].s, total[3].s);
+    out[1] = make_float4(total[4].s, total[5].s, total[6].s, total[7].s);
     out += size_t(pieces) * 2;
-    out[0] = make_float4(acc[0].e, acc[1].e, acc[2].e, acc[3].e);
-    out[1] = make_float4(acc[4].e, acc[5].e, acc[6].e, acc[7].e);
+    out[0] = make_float4(total[0].e, total[1].e, total[2].e, total[3].e);
+    out[1] = make_float4(total[4].e, total[5].e, total[6].e, total[7].e);
 }
 
 // Second pass: a warp per 4 columns.
@@ -187,7 +363,25 @@ cudaError_t launch_partials(void* workspace, const void* src, const void* x, con
     const unsigned chunks = static_cast<unsigned>((rows + kChunkRows - 1) / kChunkRows);
     const int pieces = static_cast<int>(cols / 8);
     const unsigned tiles = static_cast<unsigned>((pieces + kTilePieces - 1) / kTilePieces);
-    fb_column_partials<kSource><<<dim3(chunks, tiles), dim3(kTilePieces, kLaneRows), 0, stream>>>(
+    constexpr int kDynamic = Staging<kSource>::kBytes;
+    static bool configured[64] = {};  // per instantiation and device
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) {
+        return e;
+    }
+    if (device >= 64 || !configured[device]) {
+        e = cudaFuncSetAttribute(fb_column_partials<kSource>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kDynamic);
+        if (e != cudaSuccess) {
+            return e;
+        }
+        if (device < 64) {
+            configured[device] = true;
+        }
+    }
+    fb_column_partials<kSource>
+        <<<dim3(chunks, tiles), dim3(kTilePieces, kLaneRows + 1), kDynamic, stream>>>(
         static_cast<float4*>(workspace), src, static_cast<const float4*>(x),
         static_cast<const float*>(mean), static_cast<const float*>(rstd), rows, pieces);
     return fb::after_launch();
@@ -603,6 +797,15 @@ flint_status check_embedding_dims(const char* name, size_t sequences, size_t len
 }  // namespace
 
 namespace fb {
+
+cudaError_t reductions_error_flag(int* value, bool reset) {
+    cudaError_t e = cudaMemcpyFromSymbol(value, g_reduction_error, sizeof(int));
+    if (e == cudaSuccess && reset && *value != 0) {
+        const int zero = 0;
+        e = cudaMemcpyToSymbol(g_reduction_error, &zero, sizeof(int));
+    }
+    return e;
+}
 
 // Internal launchers, also used by the model assembly.
 cudaError_t launch_bias_gradient(void* dbias, const void* dy, size_t rows, size_t cols,
