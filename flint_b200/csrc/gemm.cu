@@ -32,6 +32,7 @@
 #include <cuda_fp16.h>
 
 #include "common.h"
+#include "device_utils.cuh"
 #include "gemm.h"
 #include "sm100.cuh"
 
@@ -69,26 +70,79 @@ struct GemmParams {
 
 // ---- epilogue math ----------------------------------------------------------------
 
+// 2^x on the special-function unit (relative error about 2^-22; flushes denormals).
+__device__ __forceinline__ float exp2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ float rcp_fast(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // GPT-2's tanh GELU written as x * sigmoid(2u), u = sqrt(2/pi) (x + 0.044715 x^3):
 // the same function without the cancellation of 1 + tanh(u) for negative x.
+// e = exp(-2u) is taken as 2^(-2u log2 e) in one special-function instruction:
+// its error (a few FP32 ulps) is three orders below the FP16 result's rounding.
+// Two values at a time on the packed FP32 instructions; the scalar forms below
+// run the same instructions, so every path gives the same bits.
+__device__ __forceinline__ fb::F2 gelu_tanh2(fb::F2 x) {
+    constexpr float kScale = -2.302208198144325f;  // -2 sqrt(2/pi) log2(e)
+    const fb::F2 one = fb::f2_pack(1.0f, 1.0f);
+    const fb::F2 t = fb::f2_fma(fb::f2_pack(0.044715f, 0.044715f), fb::f2_mul(x, x), one);
+    const fb::F2 arg = fb::f2_mul(fb::f2_mul(fb::f2_pack(kScale, kScale), x), t);
+    float a0, a1;
+    fb::f2_unpack(arg, a0, a1);
+    const fb::F2 d = fb::f2_add(fb::f2_pack(exp2_fast(a0), exp2_fast(a1)), one);
+    float d0, d1;
+    fb::f2_unpack(d, d0, d1);
+    return fb::f2_mul(x, fb::f2_pack(rcp_fast(d0), rcp_fast(d1)));
+}
+
 __device__ __forceinline__ float gelu_tanh(float x) {
-    constexpr float kNeg2Rt2OverPi = -1.5957691216057308f;
-    const float e = expf(kNeg2Rt2OverPi * x * fmaf(0.044715f, x * x, 1.0f));
-    return __fdividef(x, 1.0f + e);
+    float lo, hi;
+    fb::f2_unpack(gelu_tanh2(fb::f2_pack(x, x)), lo, hi);
+    return lo;
 }
 
 // d/dx of the above: s + x s (1 - s) * 2u', s = sigmoid(2u). For x >= 0,
 // 1 - s is computed as e * s to keep its relative accuracy near s = 1.
-__device__ __forceinline__ float gelu_tanh_grad(float x) {
-    constexpr float kNeg2Rt2OverPi = -1.5957691216057308f;
+__device__ __forceinline__ fb::F2 gelu_tanh_grad2(fb::F2 x) {
+    constexpr float kScale = -2.302208198144325f;
     constexpr float k2Rt2OverPi = 1.5957691216057308f;
     constexpr float k6KappaRt2OverPi = 0.21406444946504453f;  // 2 sqrt(2/pi) * 3 * 0.044715
-    const float e = expf(kNeg2Rt2OverPi * x * fmaf(0.044715f, x * x, 1.0f));
-    const float s = __fdividef(1.0f, 1.0f + e);
-    const float one_minus_s = x < 0.0f ? 1.0f - s : e * s;
-    const float q = x * one_minus_s * fmaf(k6KappaRt2OverPi, x * x, k2Rt2OverPi);
-    const float g = fmaf(s, q, s);
-    return isinf(x) ? (x > 0.0f ? 1.0f : 0.0f) : g;
+    const fb::F2 one = fb::f2_pack(1.0f, 1.0f);
+    const fb::F2 x2 = fb::f2_mul(x, x);
+    const fb::F2 t = fb::f2_fma(fb::f2_pack(0.044715f, 0.044715f), x2, one);
+    const fb::F2 arg = fb::f2_mul(fb::f2_mul(fb::f2_pack(kScale, kScale), x), t);
+    float a0, a1, x0, x1;
+    fb::f2_unpack(arg, a0, a1);
+    fb::f2_unpack(x, x0, x1);
+    const fb::F2 e = fb::f2_pack(exp2_fast(a0), exp2_fast(a1));
+    float d0, d1;
+    fb::f2_unpack(fb::f2_add(e, one), d0, d1);
+    const fb::F2 s = fb::f2_pack(rcp_fast(d0), rcp_fast(d1));
+    float n0, n1, p0, p1;
+    fb::f2_unpack(fb::f2_sub(one, s), n0, n1);  // 1 - s, accurate for x < 0
+    fb::f2_unpack(fb::f2_mul(e, s), p0, p1);    // e s,   accurate for x >= 0
+    const fb::F2 one_minus_s = fb::f2_pack(x0 < 0.0f ? n0 : p0, x1 < 0.0f ? n1 : p1);
+    const fb::F2 slope = fb::f2_fma(fb::f2_pack(k6KappaRt2OverPi, k6KappaRt2OverPi), x2,
+                                    fb::f2_pack(k2Rt2OverPi, k2Rt2OverPi));
+    const fb::F2 q = fb::f2_mul(fb::f2_mul(x, one_minus_s), slope);
+    float g0, g1;
+    fb::f2_unpack(fb::f2_fma(s, q, s), g0, g1);
+    g0 = isinf(x0) ? (x0 > 0.0f ? 1.0f : 0.0f) : g0;
+    g1 = isinf(x1) ? (x1 > 0.0f ? 1.0f : 0.0f) : g1;
+    return fb::f2_pack(g0, g1);
+}
+
+__device__ __forceinline__ float gelu_tanh_grad(float x) {
+    float lo, hi;
+    fb::f2_unpack(gelu_tanh_grad2(fb::f2_pack(x, x)), lo, hi);
+    return lo;
 }
 
 __device__ __forceinline__ float half_bits_to_float(unsigned short h) {
@@ -292,13 +346,67 @@ __device__ __forceinline__ void flush_half_chunk(uint32_t stage, __half* out_chu
     }
 }
 
+// Second operands of a chunk, fetched in the coalesced layout before the
+// accumulators are needed: the residual (bias+residual), the old value (TN
+// store with accumulate) or the saved pre-activation (dGELU). The loads are
+// issued a chunk ahead of their use, so their latency hides behind the previous
+// chunk's work instead of stalling every store.
+template <Epilogue E>
+__host__ __device__ constexpr int aux_slots() {
+    return (E == Epilogue::kBiasResidual || E == Epilogue::kTnStore) ? 8
+           : E == Epilogue::kDGelu                                   ? 4
+                                                                      : 1;
+}
+
+template <Epilogue E>
+struct Aux {
+    uint4 q[aux_slots<E>()];
+};
+
+template <Epilogue E>
+__device__ __forceinline__ void load_aux(Aux<E>& aux, const GemmParams& p, size_t batch_offset,
+                                         size_t row0, int col, int valid, int lane) {
+    const size_t n = static_cast<size_t>(p.n);
+    const size_t at0 = batch_offset + row0 * n + col;
+    const long long rows_long = static_cast<long long>(p.m) - static_cast<long long>(row0);
+    const int rows_left = rows_long > 32 ? 32 : static_cast<int>(rows_long);
+    if constexpr (E == Epilogue::kBiasResidual || E == Epilogue::kTnStore) {
+        const bool add = E == Epilogue::kBiasResidual || p.accumulate;
+        const float* old = E == Epilogue::kBiasResidual
+                               ? static_cast<const float*>(p.aux_in) + at0
+                               : static_cast<const float*>(p.y) + at0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int logical = lane + 32 * i;
+            const int r = logical >> 3;
+            const int c = logical & 7;
+            aux.q[i] = make_uint4(0u, 0u, 0u, 0u);
+            if (add && r < rows_left && c * 4 < valid) {
+                aux.q[i] = *reinterpret_cast<const uint4*>(old + static_cast<size_t>(r) * n + c * 4);
+            }
+        }
+    } else if constexpr (E == Epilogue::kDGelu) {
+        // Each lane fetches its own row's 64 bytes (two whole sectors), so the saved
+        // pre-activations need no trip through shared memory.
+        const __half* pre = static_cast<const __half*>(p.aux_in) + at0 + static_cast<size_t>(lane) * n;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            aux.q[i] = make_uint4(0u, 0u, 0u, 0u);
+            if (lane < rows_left && i * 8 < valid) {
+                aux.q[i] = *reinterpret_cast<const uint4*>(pre + i * 8);
+            }
+        }
+    }
+}
+
 // The whole warp calls this for one 32 x 32 chunk whose top-left element is
 // (row0, col). acc holds this lane's row. Requires n % 8 == 0 (FP16 outputs) or
 // n % 4 == 0 (FP32 outputs).
 template <Epilogue E>
 __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t stage,
                                             size_t batch_offset, long long split, size_t row0,
-                                            int col, float (&acc)[32], int valid, int lane) {
+                                            int col, float (&acc)[32], int valid, int lane,
+                                            const Aux<E>& aux) {
     const size_t n = static_cast<size_t>(p.n);
     const size_t at0 = batch_offset + row0 * n + col;  // the chunk's first element
     const long long rows_long = static_cast<long long>(p.m) - static_cast<long long>(row0);
@@ -306,11 +414,16 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t stage,
 
     if constexpr (E == Epilogue::kBias || E == Epilogue::kBiasGelu ||
                   E == Epilogue::kBiasResidual) {
-        const float* bias = p.bias + col;
+        // n is a multiple of 4 on this path and col of 32: whole 16-byte groups.
+        const float4* bias = reinterpret_cast<const float4*>(p.bias + col);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-            if (j < valid) {
-                acc[j] = __fadd_rn(acc[j], bias[j]);
+        for (int g = 0; g < 8; ++g) {
+            if (g * 4 < valid) {
+                const float4 b = __ldg(bias + g);
+                acc[4 * g] = __fadd_rn(acc[4 * g], b.x);
+                acc[4 * g + 1] = __fadd_rn(acc[4 * g + 1], b.y);
+                acc[4 * g + 2] = __fadd_rn(acc[4 * g + 2], b.z);
+                acc[4 * g + 3] = __fadd_rn(acc[4 * g + 3], b.w);
             }
         }
     }
@@ -338,10 +451,10 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t stage,
         } else {
             out = static_cast<float*>(p.y) + at0;
         }
-        const float* old = E == Epilogue::kBiasResidual
-                               ? static_cast<const float*>(p.aux_in) + at0
-                               : out;
-        const bool add = E == Epilogue::kBiasResidual || (E == Epilogue::kTnStore && p.accumulate);
+        bool add = false;
+        if constexpr (E == Epilogue::kBiasResidual || E == Epilogue::kTnStore) {
+            add = E == Epilogue::kBiasResidual || p.accumulate;
+        }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const int logical = lane + 32 * i;
@@ -352,10 +465,14 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t stage,
                 float4 v = make_float4(__uint_as_float(q.x), __uint_as_float(q.y),
                                        __uint_as_float(q.z), __uint_as_float(q.w));
                 const size_t off = static_cast<size_t>(r) * n + c * 4;
-                if (add) {
-                    const float4 o = *reinterpret_cast<const float4*>(old + off);
-                    v = make_float4(__fadd_rn(o.x, v.x), __fadd_rn(o.y, v.y), __fadd_rn(o.z, v.z),
-                                    __fadd_rn(o.w, v.w));
+                if constexpr (E == Epilogue::kBiasResidual || E == Epilogue::kTnStore) {
+                    if (add) {
+                        const uint4 o = aux.q[i];
+                        v = make_float4(__fadd_rn(__uint_as_float(o.x), v.x),
+                                        __fadd_rn(__uint_as_float(o.y), v.y),
+                                        __fadd_rn(__uint_as_float(o.z), v.z),
+                                        __fadd_rn(__uint_as_float(o.w), v.w));
+                    }
                 }
                 *reinterpret_cast<float4*>(out + off) = v;
             }
@@ -365,48 +482,43 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t stage,
     } else {
         __half* out = static_cast<__half*>(p.y) + at0;
         if constexpr (E == Epilogue::kDGelu) {
-            // Fetch the pre-activations coalesced, then hand each lane its row.
-            const __half* pre = static_cast<const __half*>(p.aux_in) + at0;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int logical = lane + 32 * i;
-                const int r = logical >> 2;
-                const int c = logical & 3;
-                uint4 q = make_uint4(0u, 0u, 0u, 0u);
-                if (r < rows_left && c * 8 < valid) {
-                    q = *reinterpret_cast<const uint4*>(pre + static_cast<size_t>(r) * n + c * 8);
-                }
-                st_shared_v4(stage_slot(stage, logical), q);
-            }
-            __syncwarp();
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                const uint4 q = ld_shared_v4(stage_slot(stage, lane * 4 + c));
+                const uint4 q = aux.q[c];
                 const unsigned w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const float lo = half_bits_to_float(static_cast<unsigned short>(w[j]));
                     const float hi = half_bits_to_float(static_cast<unsigned short>(w[j] >> 16));
-                    acc[c * 8 + 2 * j] = __fmul_rn(acc[c * 8 + 2 * j], gelu_tanh_grad(lo));
-                    acc[c * 8 + 2 * j + 1] = __fmul_rn(acc[c * 8 + 2 * j + 1], gelu_tanh_grad(hi));
+                    float g0, g1;
+                    fb::f2_unpack(gelu_tanh_grad2(fb::f2_pack(lo, hi)), g0, g1);
+                    acc[c * 8 + 2 * j] = __fmul_rn(acc[c * 8 + 2 * j], g0);
+                    acc[c * 8 + 2 * j + 1] = __fmul_rn(acc[c * 8 + 2 * j + 1], g1);
                 }
             }
-            __syncwarp();
         }
         if constexpr (E == Epilogue::kBiasGelu) {
-            // The pre-activation first, then GELU of the unrounded sums.
+            // The pre-activation goes to the slot's first half, GELU of the unrounded
+            // sums to the second; one trip through shared memory serves both outputs.
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 st_shared_v4(stage_slot(stage, lane * 4 + c), pack_half8(acc + 8 * c));
             }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                fb::f2_unpack(gelu_tanh2(fb::f2_pack(acc[2 * j], acc[2 * j + 1])), acc[2 * j],
+                              acc[2 * j + 1]);
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                st_shared_v4(stage_slot(stage + 2048u, lane * 4 + c), pack_half8(acc + 8 * c));
+            }
             __syncwarp();
             flush_half_chunk(stage, static_cast<__half*>(p.aux_out) + at0, n, rows_left, valid,
                              lane);
+            flush_half_chunk(stage + 2048u, out, n, rows_left, valid, lane);
             __syncwarp();
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                acc[j] = gelu_tanh(acc[j]);
-            }
+            return;
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -636,22 +748,30 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int quadrant = warp % 4;      // the TMEM lanes this warp may read
         const int column_half = (warp - 2) / 4;  // which of the alternating 32-column chunks
         const bool coalesced = chunk_path_ok<E>(p);
+        const bool prefetch = coalesced && aux_slots<E>() > 1;
         const uint32_t stage = staging + static_cast<uint32_t>(warp - 2) * 4096u;
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
         for (long long id = blockIdx.x; ok && id < p.tiles_total; id += gridDim.x) {
             const TileCoord t = decode_tile(p, id);
-            if (!sm100::mbar_wait(acc_full_bar(acc), acc_phase, abort)) {
-                ok = false;
-                break;
-            }
-            sm100::tc_fence_after_sync();
             const size_t row = static_cast<size_t>(t.tm) * kBM + quadrant * 32 + lane;
             const bool row_ok = row < static_cast<size_t>(p.m);
             const int col0 = t.tn * BN;
             const size_t batch_offset =
                 p.batched ? static_cast<size_t>(t.z) * p.m * static_cast<size_t>(p.n) : 0;
+            // The first chunk's second operands are requested before the accumulator is
+            // awaited, each later chunk's while the one before it is processed.
+            Aux<E> aux;
+            if (prefetch && p.n - (col0 + column_half * 32) > 0) {
+                load_aux<E>(aux, p, batch_offset, row - lane, col0 + column_half * 32,
+                            min(32, p.n - (col0 + column_half * 32)), lane);
+            }
+            if (!sm100::mbar_wait(acc_full_bar(acc), acc_phase, abort)) {
+                ok = false;
+                break;
+            }
+            sm100::tc_fence_after_sync();
             const uint32_t t_addr = tmem_base + static_cast<uint32_t>(acc * BN) +
                                     (static_cast<uint32_t>(quadrant * 32) << 16);
 #pragma unroll 1
@@ -659,6 +779,11 @@ __global__ void __launch_bounds__(kThreads, 1)
                 const bool last = c + 64 >= BN;
                 const int col = col0 + c;
                 const int valid = min(32, p.n - col);  // warp-uniform
+                Aux<E> next = aux;
+                if (prefetch && !last && p.n - (col + 64) > 0) {
+                    load_aux<E>(next, p, batch_offset, row - lane, col + 64,
+                                min(32, p.n - (col + 64)), lane);
+                }
                 uint32_t raw[32];
                 if (valid > 0) {
                     sm100::tmem_ld_32x32(t_addr + c, raw);
@@ -680,11 +805,12 @@ __global__ void __launch_bounds__(kThreads, 1)
                     }
                     if (coalesced) {
                         store_chunk<E>(p, stage, batch_offset, t.z, row - lane, col, v, valid,
-                                       lane);
+                                       lane, aux);
                     } else if (row_ok) {
                         store_segment<E>(p, batch_offset, t.z, row, col, v, valid);
                     }
                 }
+                aux = next;
             }
             acc ^= 1;
             if (acc == 0) {
@@ -745,9 +871,20 @@ __device__ __forceinline__ TileCoord decode_pair_tile(const GemmParams& p, long 
     return c;
 }
 
+// Epilogue warps per CTA of the pair kernel: two per TMEM lane quadrant, 4 KB of
+// staging each. (Four per quadrant were measured for the element-wise FP16
+// epilogues and were slower: 96 registers per thread spill.)
+template <Epilogue E>
+__host__ __device__ constexpr int pair_epilogue_warps() {
+    return 8;
+}
+
 template <Layout L, Epilogue E>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + 32 * pair_epilogue_warps<E>(), 1)
     fb_gemm_pair(const __grid_constant__ GemmParams p) {
+    constexpr int kEpi = pair_epilogue_warps<E>();
+    constexpr int kColumnStep = 32 * (kEpi / 4);            // between a warp's chunks
+    constexpr uint32_t kSlotBytes = kEpilogueWarps * 4096 / kEpi;
     constexpr bool kAMn = L == Layout::kTN;
     constexpr bool kBMn = L != Layout::kNT;
     constexpr bool kIsTn = L == Layout::kTN;
@@ -780,7 +917,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         }
         for (int a = 0; a < 2; ++a) {
             sm100::mbar_init(acc_full_bar(a), 1);
-            sm100::mbar_init(acc_empty_bar(a), 2 * kEpilogueWarps);
+            sm100::mbar_init(acc_empty_bar(a), 2 * kEpi);
         }
         sm100::mbar_fence_init();
         sm100::tma_prefetch_descriptor(&p.map_a);
@@ -924,38 +1061,82 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     } else {
         // ---- epilogue warps (both CTAs) ----
         const int quadrant = warp % 4;
-        const int column_half = (warp - 2) / 4;
+        const int column_part = (warp - 2) / 4;
         const bool coalesced = chunk_path_ok<E>(p);
-        const uint32_t stage = staging + static_cast<uint32_t>(warp - 2) * 4096u;
+        const bool prefetch = coalesced && aux_slots<E>() > 1;
+        constexpr bool kAhead = kEpi == 8;  // room to keep the next chunk's operands too
+        const uint32_t stage = staging + static_cast<uint32_t>(warp - 2) * kSlotBytes;
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
         for (long long id = pair; ok && id < p.tiles_total; id += pairs) {
             const TileCoord t = decode_pair_tile(p, id);
-            if (!sm100::mbar_wait(acc_full_bar(acc), acc_phase, abort)) {
-                ok = false;
-                break;
-            }
-            sm100::tc_fence_after_sync();
             const size_t row = static_cast<size_t>(t.tm) * 256 + rank * 128 + quadrant * 32 + lane;
             const bool row_ok = row < static_cast<size_t>(p.m);
             const int col0 = t.tn * kPairBN;
             const size_t batch_offset =
                 p.batched ? static_cast<size_t>(t.z) * p.m * static_cast<size_t>(p.n) : 0;
+            // The first chunk's second operands are requested before the accumulator is
+            // awaited, each later chunk's while the one before it is processed.
+            Aux<E> aux;
+            if (prefetch && p.n - (col0 + column_part * 32) > 0) {
+                load_aux<E>(aux, p, batch_offset, row - lane, col0 + column_part * 32,
+                            min(32, p.n - (col0 + column_part * 32)), lane);
+            }
+            if (!sm100::mbar_wait(acc_full_bar(acc), acc_phase, abort)) {
+                ok = false;
+                break;
+            }
+            sm100::tc_fence_after_sync();
             const uint32_t t_addr = tmem_base + static_cast<uint32_t>(acc * kPairBN) +
                                     (static_cast<uint32_t>(quadrant * 32) << 16);
             const uint32_t leader_empty = sm100::map_to_cta(acc_empty_bar(acc), 0);
-#pragma unroll 1
-            for (int c = column_half * 32; c < kPairBN; c += 64) {
-                const bool last = c + 64 >= kPairBN;
+            // The warp's chunks, software-pipelined: chunk i+1's accumulators are being
+            // read from tensor memory into the other register set while chunk i is
+            // worked on.
+            constexpr int kChunks = kPairBN / kColumnStep;
+            // The epilogues with second operands already hold a chunk of those ahead; a
+            // second accumulator set in flight as well would not fit in registers.
+            constexpr bool kPipelined =
+                !(E == Epilogue::kBiasResidual || E == Epilogue::kTnStore ||
+                  E == Epilogue::kTnPartial || E == Epilogue::kDGelu);
+            uint32_t raw[2][32];
+            auto chunk_column = [&](int i) { return column_part * 32 + i * kColumnStep; };
+            auto chunk_valid = [&](int i) { return min(32, p.n - (col0 + chunk_column(i))); };
+            if (kPipelined && chunk_valid(0) > 0) {
+                sm100::tmem_ld_32x32(t_addr + chunk_column(0), raw[0]);
+            }
+#pragma unroll
+            for (int i = 0; i < kChunks; ++i) {
+                const bool last = i + 1 == kChunks;
+                const int c = chunk_column(i);
                 const int col = col0 + c;
-                const int valid = min(32, p.n - col);
-                uint32_t raw[32];
-                if (valid > 0) {
-                    sm100::tmem_ld_32x32(t_addr + c, raw);
-                    sm100::tmem_ld_wait();
+                const int valid = chunk_valid(i);
+                Aux<E> next = aux;
+                if (kAhead && prefetch && !last && chunk_valid(i + 1) > 0) {
+                    load_aux<E>(next, p, batch_offset, row - lane, col + kColumnStep,
+                                chunk_valid(i + 1), lane);
+                }
+                const int kSet = kPipelined ? (i & 1) : 0;  // static once unrolled
+                if (!kPipelined && valid > 0) {
+                    sm100::tmem_ld_32x32(t_addr + c, raw[0]);
+                }
+                sm100::tmem_ld_wait();
+                // The loaded registers are "rewritten" by empty volatile statements so
+                // that nothing reading them can be scheduled above the wait.
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                    asm volatile(""
+                                 : "+r"(raw[kSet][j]), "+r"(raw[kSet][j + 1]),
+                                   "+r"(raw[kSet][j + 2]), "+r"(raw[kSet][j + 3]),
+                                   "+r"(raw[kSet][j + 4]), "+r"(raw[kSet][j + 5]),
+                                   "+r"(raw[kSet][j + 6]), "+r"(raw[kSet][j + 7]));
+                }
+                if (kPipelined && !last && chunk_valid(i + 1) > 0) {
+                    sm100::tmem_ld_32x32(t_addr + chunk_column(i + 1), raw[(i + 1) & 1]);
                 }
                 if (last) {
+                    // Every read of this accumulator has completed: hand it back.
                     sm100::tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) {
@@ -966,14 +1147,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                     float v[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        v[j] = __uint_as_float(raw[j]);
+                        v[j] = __uint_as_float(raw[kSet][j]);
                     }
                     if (coalesced) {
                         store_chunk<E>(p, stage, batch_offset, t.z, row - lane, col, v, valid,
-                                       lane);
+                                       lane, aux);
                     } else if (row_ok) {
                         store_segment<E>(p, batch_offset, t.z, row, col, v, valid);
                     }
+                }
+                if (kAhead) {
+                    aux = next;
+                } else if (prefetch && !last && chunk_valid(i + 1) > 0) {
+                    load_aux<E>(aux, p, batch_offset, row - lane, col + kColumnStep,
+                                chunk_valid(i + 1), lane);
                 }
             }
             acc ^= 1;
@@ -1233,7 +1420,8 @@ cudaError_t launch_pair(GemmParams& p, const void* x, const void* w, int sms, cu
         configured = true;
     }
     const long long pairs = std::min<long long>(p.tiles_total, sms / 2);
-    kernel<<<static_cast<unsigned>(2 * pairs), kThreads, kPairSmemBytes, stream>>>(p);
+    kernel<<<static_cast<unsigned>(2 * pairs), 64 + 32 * pair_epilogue_warps<E>(), kPairSmemBytes,
+             stream>>>(p);
     return fb::after_launch();
 }
 
