@@ -368,6 +368,45 @@ __device__ __forceinline__ float ce_block_total(Comp a, float* scratch) {
     return __fadd_rn(total.s, total.e);
 }
 
+// e^x for two values x <= 0 at a time (x >= -64 after the clamp below):
+// n = round(x log2 e) by the magic-number add, r = x - n ln 2 in two fused steps
+// (n ln2_hi is exact), 2^(r log2 e) on the special-function unit with |r log2 e|
+// <= 1/2, and n added into the exponent. About 2 ulps, like expf.
+__device__ __forceinline__ void exp_pair(fb::F2 x, float& e0, float& e1) {
+    constexpr float kLog2e = 1.4426950408889634f;
+    constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
+    constexpr float kLn2Hi = 0.693145751953125f;
+    constexpr float kLn2Lo = 1.42860682030941723212e-6f;
+    const fb::F2 t = fb::f2_fma(x, fb::f2_pack(kLog2e, kLog2e), fb::f2_pack(kMagic, kMagic));
+    const fb::F2 n = fb::f2_sub(t, fb::f2_pack(kMagic, kMagic));
+    fb::F2 r = fb::f2_fma(n, fb::f2_pack(-kLn2Hi, -kLn2Hi), x);
+    r = fb::f2_fma(n, fb::f2_pack(-kLn2Lo, -kLn2Lo), r);
+    float y0, y1, t0, t1;
+    fb::f2_unpack(fb::f2_mul(r, fb::f2_pack(kLog2e, kLog2e)), y0, y1);
+    fb::f2_unpack(t, t0, t1);
+    float p0, p1;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(y0));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(y1));
+    // The low mantissa bits of t hold n (two's complement): 2^n is built from them
+    // and multiplied in, so a NaN stays a NaN.
+    const float s0 = __int_as_float((__float_as_int(t0) << 23) + 0x3f800000);
+    const float s1 = __int_as_float((__float_as_int(t1) << 23) + 0x3f800000);
+    fb::f2_unpack(fb::f2_mul(fb::f2_pack(p0, p1), fb::f2_pack(s0, s1)), e0, e1);
+}
+
+// The four pairs of a 16-byte word of logits as x = v - mx, with v first clamped
+// (as FP16) to mx - 64: e^-64 is far below what the sums or an FP16 gradient can
+// see, and the clamp keeps the exponent arithmetic above in range for any logits.
+__device__ __forceinline__ void gaps8(fb::F2 (&x)[4], const uint4& q, __half2 floor2, fb::F2 mx2) {
+    const unsigned w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __half2 h = __hmax2_nan(*reinterpret_cast<const __half2*>(&w[i]), floor2);
+        const float2 f = __half22float2(h);
+        x[i] = fb::f2_sub(fb::f2_pack(f.x, f.y), mx2);
+    }
+}
+
 __device__ __forceinline__ float half_max8(const uint4& q) {
     const __half2* h = reinterpret_cast<const __half2*>(&q);
     const __half2 m = __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
@@ -470,20 +509,56 @@ __global__ void __launch_bounds__(kCeThreads, 1)
         }
         mx = ce_block_max(mx, scratch);
 
-        Comp part;
-        for (int i = threadIdx.x; i < vocab_chunks; i += kCeThreads) {
-            float v[8];
-            fb::unpack8(v, in[i]);
-            const int count = min(vocab - i * 8, 8);
+        // mx is a maximum of FP16 values, so it is one itself; mx - 64 rounds to FP16
+        // within 16 for any finite mx (kept finite, so a -inf logit is clamped too).
+        const __half2 floor2 = __float2half2_rn(fmaxf(__fsub_rn(mx, 64.0f), -65504.0f));
+        const fb::F2 mx2 = fb::f2_pack(mx, mx);
+        const int full_chunks = vocab / 8;  // chunks whose 8 values all count
+
+        fb::Comp2 part[2];  // even and odd pairs of each word, merged in a fixed order below
+        for (int i = threadIdx.x; i < full_chunks; i += kCeThreads) {
+            fb::F2 x[4];
+            gaps8(x, in[i], floor2, mx2);
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                if (c < count) {
-                    fb::comp_add(part, expf(__fsub_rn(v[c], mx)));
+            for (int c = 0; c < 4; ++c) {
+                float e0, e1;
+                exp_pair(x[c], e0, e1);
+                fb::comp_add2(part[c & 1], fb::f2_pack(e0, e1));
+            }
+        }
+        Comp mine;
+        {
+            float s0, s1, e0, e1;
+            fb::f2_unpack(part[0].s, s0, s1);
+            fb::f2_unpack(part[0].e, e0, e1);
+            mine.s = s0;
+            mine.e = e0;
+            fb::comp_merge(mine, s1, e1);
+            fb::f2_unpack(part[1].s, s0, s1);
+            fb::f2_unpack(part[1].e, e0, e1);
+            fb::comp_merge(mine, s0, e0);
+            fb::comp_merge(mine, s1, e1);
+        }
+        if (full_chunks < vocab_chunks && threadIdx.x == (full_chunks % kCeThreads)) {
+            // The last, partly filled word: its counted values one by one.
+            fb::F2 x[4];
+            gaps8(x, in[full_chunks], floor2, mx2);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                float e0, e1;
+                exp_pair(x[c], e0, e1);
+                if (2 * c < last_count) {
+                    fb::comp_add(mine, e0);
+                }
+                if (2 * c + 1 < last_count) {
+                    fb::comp_add(mine, e1);
                 }
             }
         }
-        const float sum = ce_block_total(part, scratch);
+        const float sum = ce_block_total(mine, scratch);
         const float inv = __fdiv_rn(1.0f, sum);
+        const fb::F2 inv2 = fb::f2_pack(inv, inv);
+        const fb::F2 scale2 = fb::f2_pack(scale, scale);
 
         const int target = targets[row];
         const int target_chunk = target / 8;
@@ -493,20 +568,31 @@ __global__ void __launch_bounds__(kCeThreads, 1)
                 out[i] = make_uint4(0u, 0u, 0u, 0u);
                 continue;
             }
-            float v[8];
-            fb::unpack8(v, in[i]);
-            const int count = min(vocab - i * 8, 8);
+            fb::F2 x[4];
+            gaps8(x, in[i], floor2, mx2);
             float o[8];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const float gap = __fsub_rn(v[c], mx);
-                o[c] = c < count ? __fmul_rn(__fmul_rn(expf(gap), inv), scale) : 0.0f;
+            for (int c = 0; c < 4; ++c) {
+                float e0, e1;
+                exp_pair(x[c], e0, e1);
+                fb::f2_unpack(fb::f2_mul(fb::f2_mul(fb::f2_pack(e0, e1), inv2), scale2), o[2 * c],
+                              o[2 * c + 1]);
+            }
+            if (i >= full_chunks) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    o[c] = c < last_count ? o[c] : 0.0f;
+                }
             }
             if (i == target_chunk) {
+                // The target column: p - 1, and the row's loss, from the unclamped logit.
+                float v[8];
+                fb::unpack8(v, in[i]);
                 const float gap = __fsub_rn(v[target_slot], mx);
+                float e0, e1;
+                exp_pair(fb::f2_pack(fmaxf(gap, -64.0f), 0.0f), e0, e1);
                 row_loss[row] = __fsub_rn(logf(sum), gap);
-                o[target_slot] =
-                    __fmul_rn(__fsub_rn(__fmul_rn(expf(gap), inv), 1.0f), scale);
+                o[target_slot] = __fmul_rn(__fsub_rn(__fmul_rn(e0, inv), 1.0f), scale);
             }
             out[i] = fb::pack8(o);
         }
