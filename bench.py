@@ -93,40 +93,58 @@ class ClockSampler:
 
 
 def step_gemms(rows: int):
-    """(kind, m, n, k) of every GEMM launch of one training step."""
+    """(entry point, m, n, k) of every GEMM launch of one training step, in the model's order
+    (flint_b200/csrc/gpt2.cu, forward_block / backward_block and the head)."""
     w, v, layers = 768, 50304, 12
-    forward = [("nt", rows, 3 * w, w), ("nt", rows, w, w), ("nt", rows, 4 * w, w),
-               ("nt", rows, w, 4 * w)]
-    backward = [("tn", w, 4 * w, rows), ("nn", rows, 4 * w, w), ("tn", 4 * w, w, rows),
+    forward = [("nt_bias", rows, 3 * w, w), ("nt_bias_residual", rows, w, w),
+               ("nt_bias_gelu", rows, 4 * w, w), ("nt_bias_residual", rows, w, 4 * w)]
+    backward = [("tn", w, 4 * w, rows), ("nn_dgelu", rows, 4 * w, w), ("tn", 4 * w, w, rows),
                 ("nn", rows, w, 4 * w), ("tn", w, w, rows), ("nn", rows, w, w),
                 ("tn", 3 * w, w, rows), ("nn", rows, w, 3 * w)]
     return layers * (forward + backward) + [("nt", rows, v, w), ("tn", v, w, rows),
                                             ("nn", rows, w, v)]
 
 
-def gemm_roofline(flint, torch, rows: int):
-    """Replays one step's GEMM launches between CUDA events on the launch stream."""
+# DRAM bytes (read + write) per GEMM launch, averaged over the 147 launches of one step's
+# replay below: `dram__bytes_read.sum + dram__bytes_write.sum` from the ncu capture summarised
+# in profiles/gemm_step_replay_gpt2_124m.md. None until such a capture has been taken.
+GEMM_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def gemm_roofline(flint, torch, rows: int, reps: int = 3):
+    """Replays one step's GEMM launches, with the epilogues the model uses, between CUDA
+    events on the launch stream."""
     dev = "cuda"
     shapes = step_gemms(rows)
     a = torch.randn(rows * 50304, device=dev).half()      # big enough for every operand
-    b = torch.randn(50304 * 768 * 4, device=dev).half()
+    b = (torch.randn(50304 * 768, device=dev) * 0.02).half()
     y = torch.empty(rows * 50304, device=dev, dtype=torch.float16)
+    pre = torch.randn(rows * 3072, device=dev).half()
+    residual = torch.randn(rows * 768, device=dev)
     y32 = torch.zeros(50304 * 768, device=dev)
+    bias = torch.randn(3072, device=dev)
     workspace = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
     def replay():
         for kind, m, n, k in shapes:
             if kind == "nt":
                 flint.gemm_nt(y, a, b, m, n, k)
+            elif kind == "nt_bias":
+                flint.gemm_nt_bias(y, a, b, bias, m, n, k)
+            elif kind == "nt_bias_gelu":
+                flint.gemm_nt_bias_gelu(y, pre, a, b, bias, m, n, k)
+            elif kind == "nt_bias_residual":
+                flint.gemm_nt_bias_residual(y32, a, b, bias, residual, m, n, k)
             elif kind == "nn":
                 flint.gemm_nn(y, a, b, m, n, k)
+            elif kind == "nn_dgelu":
+                flint.gemm_nn_dgelu(y, a, b, pre, m, n, k)
             else:
                 flint.gemm_tn(y32, a, b, m, n, k, True, workspace)
 
     replay()
     torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    reps = 3
     start.record()
     for _ in range(reps):
         replay()
@@ -136,11 +154,13 @@ def gemm_roofline(flint, torch, rows: int):
     flops = sum(2.0 * m * n * k for _, m, n, k in shapes)
     peak, _, source = peaks()
     achieved = flops / seconds / 1e12
-    return {"bound": "tensor", "kernel": "fb_gemm_tc (all GEMM launches of one step)",
+    return {"bound": "tensor",
+            "kernel": "fb_gemm_pair / fb_gemm_tc / fb_gemm_tn_reduce (all 147 GEMM calls of one "
+                      "step, with their epilogues)",
             "achieved": round(achieved, 1), "peak": peak, "unit": "TFLOP/s",
             "frac": round(achieved / peak, 4), "peak_source": source + " (sustained bf16 GEMM)",
             "launches_per_step": len(shapes), "avg_launch_us": round(seconds / len(shapes) * 1e6, 2),
-            "traffic": None}
+            "traffic": GEMM_TRAFFIC_BYTES_PER_LAUNCH}
 
 
 def cpu_step_tokens_per_second(budget_seconds: float, threads=None):
@@ -326,10 +346,20 @@ def main():
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="flint", choices=["flint", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--gemm-replay", action="store_true",
+                        help="only replay one step's GEMM calls once after a warm-up replay and "
+                             "print the roofline object (the command profiled for its DRAM traffic)")
     args = parser.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    if args.impl == "reference":
+    if args.gemm_replay:
+        import torch
+
+        import flint_b200
+        torch.cuda.set_device(0)
+        print(json.dumps(gemm_roofline(flint_b200.Flint(), torch, SEQUENCES * LENGTH, reps=1)),
+              flush=True)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_flint(args)
