@@ -5,6 +5,8 @@
 #include <cstdarg>
 #include <cstdio>
 
+#include <cuda.h>
+
 #ifndef FLINT_VERSION
 #define FLINT_VERSION "0.1.0"
 #endif
@@ -92,6 +94,40 @@ cudaError_t sm_count(int* sms) {
     *sms = value;
     return cudaSuccess;
 }
+
+cudaError_t encode_rows_map(void* map, const void* base, size_t rows, size_t cols,
+                            int element_bytes, unsigned box_cols, unsigned box_rows) {
+    using Encode = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static Encode encode = nullptr;
+    if (encode == nullptr) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult status;
+        const cudaError_t e =
+            cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &status);
+        if (e != cudaSuccess) {
+            return e;
+        }
+        if (status != cudaDriverEntryPointSuccess || fn == nullptr) {
+            return cudaErrorNotSupported;
+        }
+        encode = reinterpret_cast<Encode>(fn);
+    }
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * static_cast<cuuint64_t>(element_bytes)};
+    const cuuint32_t box[2] = {box_cols, box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUtensorMapDataType type =
+        element_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    const CUresult r = encode(static_cast<CUtensorMap*>(map), type, 2, const_cast<void*>(base), dims,
+                              strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
 
 }  // namespace fb
 

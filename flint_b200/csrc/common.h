@@ -58,6 +58,12 @@ unsigned long long launch_count();
 // Number of SMs of the current device (cached per device index).
 cudaError_t sm_count(int* sms);
 
+// Tensor map over a row-major matrix [rows, cols] of 2- or 4-byte elements (no
+// swizzle, zero fill outside), for boxes of box_cols x box_rows. The row pitch
+// must be a multiple of 16 bytes and both extents below 2^32.
+cudaError_t encode_rows_map(void* map, const void* base, size_t rows, size_t cols,
+                            int element_bytes, unsigned box_cols, unsigned box_rows);
+
 // Device error word of the column-sum kernels: set when a bounded wait for a
 // staged row gave up (read, and cleared if asked, by flint_b200_kernel_fault).
 cudaError_t reductions_error_flag(int* value, bool reset);

@@ -518,15 +518,15 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t stage,
                              lane);
             flush_half_chunk(stage + 2048u, out, n, rows_left, valid, lane);
             __syncwarp();
-            return;
-        }
+        } else {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            st_shared_v4(stage_slot(stage, lane * 4 + c), pack_half8(acc + 8 * c));
+            for (int c = 0; c < 4; ++c) {
+                st_shared_v4(stage_slot(stage, lane * 4 + c), pack_half8(acc + 8 * c));
+            }
+            __syncwarp();
+            flush_half_chunk(stage, out, n, rows_left, valid, lane);
+            __syncwarp();
         }
-        __syncwarp();
-        flush_half_chunk(stage, out, n, rows_left, valid, lane);
-        __syncwarp();
     }
 }
 

@@ -18,6 +18,7 @@
 #include <algorithm>
 #include <cstdint>
 
+#include <cuda.h>
 #include <cuda_fp16.h>
 
 #include "common.h"
@@ -59,7 +60,7 @@ struct Staging {
     static constexpr int kRows = 32;                                        // rows per stage
     static constexpr int kMainStage = kRows * kTilePieces * kMainBytes;
     static constexpr int kStage = kMainStage + kRows * kTilePieces * kXBytes;
-    static constexpr int kStages = kSource == Source::kHalf ? 3 : 2;
+    static constexpr int kStages = kSource == Source::kHalf ? 4 : 2;
     static constexpr int kBytes = kStages * kStage + 128;
 };
 // After the last stage the ring's memory holds the eight streams' sums for the merge.
@@ -95,11 +96,21 @@ __device__ __forceinline__ bool staged_wait(uint32_t bar, uint32_t parity, volat
     }
 }
 
+// Tensor maps of the source (and of x for the dgamma sums): one TMA tensor load
+// then brings a whole 32-row stage. `use` is 0 for matrices whose row count does
+// not fit a tensor map; those stages are fetched row by row.
+struct ColumnMaps {
+    CUtensorMap main;
+    CUtensorMap x;
+    int use;
+};
+
 template <Source kSource>
 __global__ void __launch_bounds__(kTilePieces * (kLaneRows + 1))
-    fb_column_partials(float4* __restrict__ partial, const void* __restrict__ src,
-                       const float4* __restrict__ x, const float* __restrict__ mean,
-                       const float* __restrict__ rstd, size_t rows, int pieces) {
+    fb_column_partials(const __grid_constant__ ColumnMaps maps, float4* __restrict__ partial,
+                       const void* __restrict__ src, const float4* __restrict__ x,
+                       const float* __restrict__ mean, const float* __restrict__ rstd, size_t rows,
+                       int pieces) {
     using S = Staging<kSource>;
     extern __shared__ unsigned char staging_raw[];
     __shared__ float sh_mean[kSource == Source::kHalfTimesXhat ? kChunkRows : 1];
@@ -155,6 +166,34 @@ __global__ void __launch_bounds__(kTilePieces * (kLaneRows + 1))
                 break;
             }
             const int here = min(S::kRows, chunk_rows - k * S::kRows);
+            if (maps.use != 0) {
+                // One tensor load per operand: the box is always delivered whole (zeros
+                // past the matrix's edges, which the adding warps never read).
+                if (px == 0) {
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
+                                     full_bar(slot)),
+                                 "r"(static_cast<uint32_t>(S::kStage))
+                                 : "memory");
+                    const int column = first_piece * 8;
+                    const int row = static_cast<int>(first) + k * S::kRows;
+                    const uint32_t dst = staging + slot * S::kStage;
+                    asm volatile(
+                        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+                        " [%0], [%1, {%3, %4}], [%2];"
+                        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(&maps.main)),
+                          "r"(full_bar(slot)), "r"(column), "r"(row)
+                        : "memory");
+                    if constexpr (S::kXBytes != 0) {
+                        asm volatile(
+                            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+                            " [%0], [%1, {%3, %4}], [%2];"
+                            ::"r"(dst + S::kMainStage), "l"(reinterpret_cast<uint64_t>(&maps.x)),
+                              "r"(full_bar(slot)), "r"(column), "r"(row)
+                            : "memory");
+                    }
+                }
+                continue;
+            }
             if (px == 0) {
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(
                                  full_bar(slot)),
@@ -380,9 +419,22 @@ cudaError_t launch_partials(void* workspace, const void* src, const void* x, con
             configured[device] = true;
         }
     }
+    ColumnMaps maps;
+    maps.use = rows < (size_t{1} << 31) ? 1 : 0;
+    if (maps.use != 0) {
+        using S = Staging<kSource>;
+        e = fb::encode_rows_map(&maps.main, src, rows, cols, S::kMainBytes / 8, kTilePieces * 8,
+                                S::kRows);
+        if (e == cudaSuccess && S::kXBytes != 0) {
+            e = fb::encode_rows_map(&maps.x, x, rows, cols, 4, kTilePieces * 8, S::kRows);
+        }
+        if (e != cudaSuccess) {
+            return e;
+        }
+    }
     fb_column_partials<kSource>
         <<<dim3(chunks, tiles), dim3(kTilePieces, kLaneRows + 1), kDynamic, stream>>>(
-        static_cast<float4*>(workspace), src, static_cast<const float4*>(x),
+        maps, static_cast<float4*>(workspace), src, static_cast<const float4*>(x),
         static_cast<const float*>(mean), static_cast<const float*>(rstd), rows, pieces);
     return fb::after_launch();
 }
