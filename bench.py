@@ -105,10 +105,10 @@ def step_gemms(rows: int):
                                             ("nn", rows, w, v)]
 
 
-# DRAM bytes (read + write) per GEMM launch, averaged over the 147 launches of one step's
-# replay below: `dram__bytes_read.sum + dram__bytes_write.sum` from the ncu capture summarised
-# in profiles/gemm_step_replay_gpt2_124m.md. None until such a capture has been taken.
-GEMM_TRAFFIC_BYTES_PER_LAUNCH = None
+# DRAM bytes (read + write) per GEMM call, averaged over the 147 calls of one step's replay
+# below: `dram__bytes_read.sum + dram__bytes_write.sum` summed over the replay's kernels in the
+# ncu capture summarised in profiles/gemm_step_replay_gpt2_124m.md.
+GEMM_TRAFFIC_BYTES_PER_LAUNCH = 167.1e6
 
 
 def gemm_roofline(flint, torch, rows: int, reps: int = 3):

@@ -64,6 +64,15 @@ cudaError_t sm_count(int* sms);
 cudaError_t encode_rows_map(void* map, const void* base, size_t rows, size_t cols,
                             int element_bytes, unsigned box_cols, unsigned box_rows);
 
+// flint_layernorm_backward's kernels without the argument checks, for the model
+// assembly; dx_half, when not null, also receives dx rounded to FP16 (the next
+// GEMM's operand), which saves a separate conversion pass over dx.
+cudaError_t launch_layernorm_backward(void* dx, void* dgamma, void* dbeta, const void* dy,
+                                      const void* x, const void* mean, const void* rstd,
+                                      const void* gamma, size_t rows, size_t cols,
+                                      bool accumulate_dx, bool accumulate_params, void* workspace,
+                                      cudaStream_t stream, void* dx_half);
+
 // Device error word of the column-sum kernels: set when a bounded wait for a
 // staged row gave up (read, and cleared if asked, by flint_b200_kernel_fault).
 cudaError_t reductions_error_flag(int* value, bool reset);

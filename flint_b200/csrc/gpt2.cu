@@ -394,12 +394,17 @@ flint_status bias_gradient(const flint_gpt2& m, const Tensor* bias, const void* 
                                m.workspace_bytes, s);
 }
 
+// dres (+)= the gradient through a LayerNorm whose output gradient is dh. With
+// `half_copy` the kernel also leaves dres rounded to FP16 in dres_half, the operand of
+// the GEMMs that follow.
 flint_status layernorm_backward(const flint_gpt2& m, const Tensor* gain, const Tensor* bias,
                                 const void* x, const void* mean, const void* rstd,
-                                int accumulate_dx, int accumulate, flint_stream s) {
-    return flint_layernorm_backward(m.dres, gain->gradient, bias->gradient, m.dh, x, mean, rstd,
-                                    gain->data, m.rows, m.config.width, accumulate_dx, accumulate,
-                                    m.workspace, m.workspace_bytes, s);
+                                int accumulate_dx, int accumulate, bool half_copy, flint_stream s) {
+    FB_CUDA(fb::launch_layernorm_backward(m.dres, gain->gradient, bias->gradient, m.dh, x, mean,
+                                          rstd, gain->data, m.rows, m.config.width,
+                                          accumulate_dx != 0, accumulate != 0, m.workspace, s,
+                                          half_copy ? m.dres_half : nullptr));
+    return FLINT_OK;
 }
 
 // On entry dres is the gradient of the residual stream leaving block i; on
@@ -414,18 +419,17 @@ flint_status backward_block(const flint_gpt2& m, size_t i, int accumulate, flint
     const size_t hb = m.head_batches;
     const size_t len = c.length;
 
-    // MLP.
-    FB_TRY(flint_fp32_to_fp16(m.dres_half, m.dres, rows * w, s));
+    // MLP. dres_half already holds dres in FP16 (written by the LayerNorm backward before).
     FB_TRY(weight_gradient(m, wt.fcproj_w, m.dres_half, a.gelu, accumulate, s));
     FB_TRY(bias_gradient(m, wt.fcproj_b, m.dres_half, accumulate, s));
     FB_TRY(flint_gemm_nn_dgelu(m.dpre, m.dres_half, wt.fcproj_w->half, a.pre, rows, 4 * w, w, s));
     FB_TRY(weight_gradient(m, wt.fc_w, m.dpre, a.h2, accumulate, s));
     FB_TRY(bias_gradient(m, wt.fc_b, m.dpre, accumulate, s));
     FB_TRY(flint_gemm_nn(m.dh, m.dpre, wt.fc_w->half, rows, w, 4 * w, s));
-    FB_TRY(layernorm_backward(m, wt.ln2_w, wt.ln2_b, a.x_mid, a.mean2, a.rstd2, 1, accumulate, s));
+    FB_TRY(layernorm_backward(m, wt.ln2_w, wt.ln2_b, a.x_mid, a.mean2, a.rstd2, 1, accumulate, true,
+                              s));
 
     // Attention output projection.
-    FB_TRY(flint_fp32_to_fp16(m.dres_half, m.dres, rows * w, s));
     FB_TRY(weight_gradient(m, wt.proj_w, m.dres_half, a.attn, accumulate, s));
     FB_TRY(bias_gradient(m, wt.proj_b, m.dres_half, accumulate, s));
     FB_TRY(flint_gemm_nn(m.dh, m.dres_half, wt.proj_w->half, rows, w, w, s));
@@ -457,7 +461,9 @@ flint_status backward_block(const flint_gpt2& m, size_t i, int accumulate, flint
     FB_TRY(weight_gradient(m, wt.attn_w, m.qkv, a.h1, accumulate, s));
     FB_TRY(bias_gradient(m, wt.attn_b, m.qkv, accumulate, s));
     FB_TRY(flint_gemm_nn(m.dh, m.qkv, wt.attn_w->half, rows, w, 3 * w, s));
-    return layernorm_backward(m, wt.ln1_w, wt.ln1_b, a.x_in, a.mean1, a.rstd1, 1, accumulate, s);
+    // Block 0's result feeds the embedding backward, which reads FP32.
+    return layernorm_backward(m, wt.ln1_w, wt.ln1_b, a.x_in, a.mean1, a.rstd1, 1, accumulate, i > 0,
+                              s);
 }
 
 flint_status create(const char* name, const flint_gpt2_config* config, bool flash,
@@ -547,7 +553,7 @@ flint_status backward_impl(const char* name, flint_gpt2* model, const void* toke
     FB_TRY(weight_gradient(m, m.wte, m.dlogits, m.h_f, accumulate, stream));
     FB_TRY(flint_gemm_nn(m.dh, m.dlogits, m.wte->half, rows, w, c.padded_vocab, stream));
     FB_TRY(layernorm_backward(m, m.lnf_w, m.lnf_b, m.x_final, m.mean_f, m.rstd_f, 0, accumulate,
-                              stream));
+                              true, stream));
     int bucket = 0;
     notify(bucket++, m.lnf_w, m.lnf_b);
     for (size_t i = m.blocks.size(); i-- > 0;) {

@@ -463,7 +463,7 @@ __global__ void __launch_bounds__(32 * kWarpsPerBlock)
     fb_layernorm_backward_dx(float4* __restrict__ dx, const uint4* __restrict__ dy,
                              const float4* __restrict__ x, const float* __restrict__ mean,
                              const float* __restrict__ rstd, const float4* __restrict__ gamma,
-                             size_t rows, int pieces, bool accumulate) {
+                             size_t rows, int pieces, bool accumulate, uint4* __restrict__ dx_half) {
     const size_t row = size_t{blockIdx.x} * kWarpsPerBlock + threadIdx.x / 32;
     if (row >= rows) {
         return;
@@ -521,6 +521,9 @@ __global__ void __launch_bounds__(32 * kWarpsPerBlock)
                     }
                 }
                 fb::store8(dxr + 2 * i, o);
+                if (dx_half != nullptr) {
+                    dx_half[row * pieces + i] = fb::pack8(o);  // the same values, rounded once
+                }
             }
         }
     } else {
@@ -563,6 +566,9 @@ __global__ void __launch_bounds__(32 * kWarpsPerBlock)
                 }
             }
             fb::store8(dxr + 2 * i, o);
+            if (dx_half != nullptr) {
+                dx_half[row * pieces + i] = fb::pack8(o);
+            }
         }
     }
 }
@@ -874,7 +880,7 @@ cudaError_t launch_layernorm_backward(void* dx, void* dgamma, void* dbeta, const
                                       const void* x, const void* mean, const void* rstd,
                                       const void* gamma, size_t rows, size_t cols,
                                       bool accumulate_dx, bool accumulate_params, void* workspace,
-                                      cudaStream_t stream) {
+                                      cudaStream_t stream, void* dx_half) {
     // dbeta first; its second pass is done with the workspace before dgamma's
     // partial sums reuse it (stream order).
     cudaError_t e = launch_bias_gradient(dbeta, dy, rows, cols, accumulate_params, workspace,
@@ -900,16 +906,16 @@ cudaError_t launch_layernorm_backward(void* dx, void* dgamma, void* dbeta, const
     const auto* gq = static_cast<const float4*>(gamma);
     if (pieces <= 32) {
         fb_layernorm_backward_dx<1><<<blocks, 32 * kWarpsPerBlock, 0, stream>>>(
-            dxq, dyq, xq, mf, rf, gq, rows, pieces, accumulate_dx);
+            dxq, dyq, xq, mf, rf, gq, rows, pieces, accumulate_dx, static_cast<uint4*>(dx_half));
     } else if (pieces <= 96) {
         fb_layernorm_backward_dx<3><<<blocks, 32 * kWarpsPerBlock, 0, stream>>>(
-            dxq, dyq, xq, mf, rf, gq, rows, pieces, accumulate_dx);
+            dxq, dyq, xq, mf, rf, gq, rows, pieces, accumulate_dx, static_cast<uint4*>(dx_half));
     } else if (pieces <= 192) {
         fb_layernorm_backward_dx<6><<<blocks, 32 * kWarpsPerBlock, 0, stream>>>(
-            dxq, dyq, xq, mf, rf, gq, rows, pieces, accumulate_dx);
+            dxq, dyq, xq, mf, rf, gq, rows, pieces, accumulate_dx, static_cast<uint4*>(dx_half));
     } else {
         fb_layernorm_backward_dx<0><<<blocks, 32 * kWarpsPerBlock, 0, stream>>>(
-            dxq, dyq, xq, mf, rf, gq, rows, pieces, accumulate_dx);
+            dxq, dyq, xq, mf, rf, gq, rows, pieces, accumulate_dx, static_cast<uint4*>(dx_half));
     }
     return fb::after_launch();
 }
@@ -1116,7 +1122,7 @@ flint_status flint_layernorm_backward(void* dx, void* dgamma, void* dbeta, const
     FB_TRY(fb::check_spans(name, spans, 4));
     FB_CUDA(fb::launch_layernorm_backward(dx, dgamma, dbeta, dy, x, mean, rstd, gamma, rows, cols,
                                           accumulate_dx != 0, accumulate_params != 0, workspace,
-                                          stream));
+                                          stream, nullptr));
     return FLINT_OK;
 }
 
