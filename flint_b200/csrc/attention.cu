@@ -430,34 +430,33 @@ __global__ void __launch_bounds__(256)
     }
 }
 
-// ---- backward: dK and dV ------------------------------------------------------------------------
+// ---- backward: shared pieces --------------------------------------------------------------------
 //
-// One CTA per (head, 128 keys). Scores are formed transposed, S^T = K Q^T with
-// keys on the TMEM lanes, 64 queries at a time, so that P^T and dS^T leave the
-// compute warps directly in the K-major layout the gradient MMAs want as their
-// A operand (dV += P^T dO, dK += dS^T Q). The two S^T/dP^T accumulators and the
-// two P^T/dS^T shared-memory buffers are double-buffered: the MMA warp issues
-// sub-step h+1's score MMAs before it waits for sub-step h's probabilities, so
-// tensor work and exponentials overlap.
+// Both gradient kernels keep every A operand in tensor memory (TS-form MMAs): the
+// resident tile pair is copied there once per CTA, and the probabilities / score
+// gradients the compute warps produce are written back as FP16 pairs over the
+// accumulator columns they were read from. Shared memory then only feeds the B
+// operands (the streamed 64-row tiles): an SS-form MMA with N = 64 needs 6 KB of
+// operands per instruction and is bound by the shared-memory rate (measured 49
+// clocks against 32 of tensor work), and the P/dS stores shared the same banks.
 
 constexpr int kBwdThreads = 320;  // TMA warp, MMA warp, 8 compute warps
-constexpr int kSub = 64;          // queries (dK/dV) or keys (dQ) per sub-step
-constexpr int kSubBytes = kSub * kHead * 2;     // 8 KB: a 64-row Q/dO/K/V tile
+constexpr int kSub = 64;          // streamed rows (queries for dK/dV, keys for dQ) per sub-step
+constexpr int kSubBytes = kSub * kHead * 2;  // 8 KB: one streamed tile
 constexpr int kBwdStages = 4;
-// resident pair (2 x 16 KB) + ring (4 x 16 KB) + two P^T and two dS^T buffers (4 x 16 KB)
-// + per stage the sub-step's 64 log-sum-exp and 64 delta values
 constexpr int kStatBytes = kSub * 4;  // one sub-step's log-sum-exp or delta values
-constexpr int kDkvSmem = 1024 + 2 * kTileBytes + kBwdStages * 2 * kSubBytes + 4 * kPanelBytes +
+// resident pair (2 x 16 KB) + ring of tile pairs (4 x 16 KB) + row statistics + barriers
+constexpr int kBwdSmem = 1024 + 2 * kTileBytes + kBwdStages * 2 * kSubBytes +
                          kBwdStages * 2 * kStatBytes + 256;
-constexpr uint32_t kIdescSub = sm100::instr_desc_f16(128, 64, false, false);  // K Q^T, V dO^T
+constexpr uint32_t kIdescSub = sm100::instr_desc_f16(128, 64, false, false);  // A Bsub^T
 
 struct BwdBarriers {
     uint32_t base;
     __device__ uint32_t resident() const { return base; }
     __device__ uint32_t done() const { return base + 8; }
-    __device__ uint32_t scores_full(int b) const { return base + 16 + 8u * b; }
-    __device__ uint32_t operands_ready(int b) const { return base + 32 + 8u * b; }
-    __device__ uint32_t operands_free(int b) const { return base + 48 + 8u * b; }
+    __device__ uint32_t a_ready() const { return base + 16; }
+    __device__ uint32_t scores_full(int b) const { return base + 32 + 8u * b; }
+    __device__ uint32_t operands_ready(int b) const { return base + 48 + 8u * b; }
     __device__ uint32_t stage_full(int s) const { return base + 64 + 8u * s; }
     __device__ uint32_t stage_empty(int s) const { return base + 96 + 8u * s; }
 };
@@ -465,10 +464,10 @@ struct BwdBarriers {
 __device__ __forceinline__ void init_bwd_barriers(const BwdBarriers& b, int compute_threads) {
     sm100::mbar_init(b.resident(), 1);
     sm100::mbar_init(b.done(), 1);
+    sm100::mbar_init(b.a_ready(), compute_threads);
     for (int i = 0; i < 2; ++i) {
         sm100::mbar_init(b.scores_full(i), 1);
         sm100::mbar_init(b.operands_ready(i), compute_threads);
-        sm100::mbar_init(b.operands_free(i), 1);
     }
     for (int s = 0; s < kBwdStages; ++s) {
         sm100::mbar_init(b.stage_full(s), 1);
@@ -477,23 +476,44 @@ __device__ __forceinline__ void init_bwd_barriers(const BwdBarriers& b, int comp
     sm100::mbar_fence_init();
 }
 
-// Writes 32 FP16 values into columns [col, col + 32) of row `row` of a one-panel
-// (64-column) swizzled operand tile.
-__device__ __forceinline__ void store_panel_row(uint32_t tile, int row, int col,
-                                                const float (&v)[32]) {
-    const uint32_t line = tile + row * 128;
-    const int first_chunk = col >> 3;
+// Copies this thread's row of a resident 128 x 64 FP16 tile (swizzled as TMA wrote it)
+// into tensor memory as an A operand: the 32 head columns [32 part, 32 part + 32)
+// become 16 columns of FP16 pairs at `dst` + 16 part.
+__device__ __forceinline__ void tile_row_to_tmem(uint32_t dst, uint32_t tile, int row, int part) {
+    uint32_t r[16];
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-        const uint32_t at = line + (((first_chunk + c) ^ (row & 7)) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(at),
-                     "r"(fb::pack2(v[8 * c], v[8 * c + 1])),
-                     "r"(fb::pack2(v[8 * c + 2], v[8 * c + 3])),
-                     "r"(fb::pack2(v[8 * c + 4], v[8 * c + 5])),
-                     "r"(fb::pack2(v[8 * c + 6], v[8 * c + 7]))
-                     : "memory");
+    for (int i = 0; i < 4; ++i) {
+        const int chunk = part * 4 + i;
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(r[4 * i]), "=r"(r[4 * i + 1]), "=r"(r[4 * i + 2]), "=r"(r[4 * i + 3])
+                     : "r"(tile + row * 128 + ((chunk ^ (row & 7)) << 4)));
+    }
+    sm100::tmem_st_32x16(dst + 16 * part, r);
+}
+
+// 32 FP32 values -> 16 words of FP16 pairs (the lower-indexed value in the low half).
+__device__ __forceinline__ void pack_pairs(uint32_t (&w)[16], const float (&v)[32]) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        w[i] = fb::pack2(v[2 * i], v[2 * i + 1]);
     }
 }
+
+// The 64-bit descriptor of a 128-byte-swizzled tile moved by `bytes` (a multiple of
+// 16; shared memory is small enough that the address field never carries).
+__device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) {
+    return desc + (bytes >> 4);
+}
+
+// ---- backward: dK and dV ------------------------------------------------------------------------
+//
+// One CTA per (head, 128 keys), 64 queries per sub-step. Scores are formed
+// transposed, S^T = K Q^T and dP^T = V dO^T with keys on the TMEM lanes (A = K, V
+// from tensor memory), so P^T and dS^T are already the A operands of
+// dV += P^T dO and dK += dS^T Q. Accumulator pairs are double-buffered: the MMA
+// warp issues sub-step h+1's score MMAs before it waits for sub-step h's
+// probabilities. Tensor memory: S^T at 0/64, dP^T at 128/192 (P^T and dS^T overwrite
+// 16 + 16 columns of each), dV 256, dK 320, K 384, V 416.
 
 __global__ void __launch_bounds__(kBwdThreads, 1)
     fb_attention_dkv(const __grid_constant__ AttnParams p) {
@@ -501,10 +521,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     const uint32_t base = (sm100::smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t k_tile = base;
     const uint32_t v_tile = base + kTileBytes;
-    const uint32_t ring = base + 2 * kTileBytes;                 // stage: Q_h then dO_h
-    const uint32_t pt_tiles = ring + kBwdStages * 2 * kSubBytes;  // P^T[0], P^T[1]
-    const uint32_t dst_tiles = pt_tiles + 2 * kPanelBytes;        // dS^T[0], dS^T[1]
-    const uint32_t stats = dst_tiles + 2 * kPanelBytes;           // stage: lse[64] then delta[64]
+    const uint32_t ring = base + 2 * kTileBytes;                   // stage: Q_h then dO_h
+    const uint32_t stats = ring + kBwdStages * 2 * kSubBytes;      // stage: lse[64] then delta[64]
     const BwdBarriers bar{stats + kBwdStages * 2 * kStatBytes};
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
@@ -517,10 +535,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     const int head = bh % p.heads;
     const int seq = bh / p.heads;
     const int steps = 2 * (p.blocks - kb);  // 64-query sub-steps from the diagonal tile on
+    if (threadIdx.x == 64) { FB_TRACE(0, 38, 0); }
 
-    if (threadIdx.x == 64) {
-        FB_TRACE(0, 38, 0);
-    }
     if (threadIdx.x == 0) {
         abort_flag = 0;
         init_bwd_barriers(bar, 256);
@@ -535,10 +551,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     auto tmem_st = [&](int b) { return tmem + 64u * b; };
     auto tmem_dpt = [&](int b) { return tmem + 128u + 64u * b; };
     const uint32_t tmem_dv = tmem + 256, tmem_dk = tmem + 320;
+    const uint32_t tmem_k = tmem + 384, tmem_v = tmem + 416;
     volatile int* abort = &abort_flag;
-    if (threadIdx.x == 64) {
-        FB_TRACE(0, 38, 1);
-    }
 
     if (warp == 0) {
         if (lane == 0) {
@@ -574,7 +588,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            bool ok = sm100::mbar_wait(bar.resident(), 0, abort);
+            bool ok = sm100::mbar_wait(bar.a_ready(), 0, abort);
+            sm100::tc_fence_after_sync();
+            // Descriptors of stage 0's tiles; a stage is 16 KB further, a K-major k-step 32
+            // bytes, an MN-major one 2,048.
+            const uint64_t q_desc = sm100::smem_desc_sw128(ring, 16, 1024);
+            const uint64_t do_desc = sm100::smem_desc_sw128(ring + kSubBytes, 16, 1024);
             // S^T and dP^T of sub-step g into accumulator pair g & 1.
             auto issue_scores = [&](int g) -> bool {
                 const int stage = g % kBwdStages;
@@ -582,17 +601,17 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                     return false;
                 }
                 sm100::tc_fence_after_sync();
-                const uint32_t q_sub = ring + stage * 2 * kSubBytes;
-                const uint32_t do_sub = q_sub + kSubBytes;
+                const uint64_t q_sub = desc_advance(q_desc, stage * 2 * kSubBytes);
+                const uint64_t do_sub = desc_advance(do_desc, stage * 2 * kSubBytes);
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {
-                    sm100::mma_f16_ss(tmem_st(g & 1), desc_kmajor(k_tile, ks),
-                                      desc_kmajor(q_sub, ks), kIdescSub, ks > 0);
+                    sm100::mma_f16_ts(tmem_st(g & 1), tmem_k + ks * 8, desc_advance(q_sub, ks * 32),
+                                      kIdescSub, ks > 0);
                 }
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {
-                    sm100::mma_f16_ss(tmem_dpt(g & 1), desc_kmajor(v_tile, ks),
-                                      desc_kmajor(do_sub, ks), kIdescSub, ks > 0);
+                    sm100::mma_f16_ts(tmem_dpt(g & 1), tmem_v + ks * 8,
+                                      desc_advance(do_sub, ks * 32), kIdescSub, ks > 0);
                 }
                 sm100::mma_commit(bar.scores_full(g & 1));
                 return true;
@@ -613,23 +632,21 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                 FB_TRACE(1, h, 2);
                 sm100::tc_fence_after_sync();
                 const int stage = h % kBwdStages;
-                const uint32_t q_sub = ring + stage * 2 * kSubBytes;
-                const uint32_t do_sub = q_sub + kSubBytes;
-                const uint32_t pt = pt_tiles + b * kPanelBytes;
-                const uint32_t dst = dst_tiles + b * kPanelBytes;
-                // dV += P^T dO and dK += dS^T Q over this sub-step's 64 queries.
+                const uint64_t q_sub = desc_advance(q_desc, stage * 2 * kSubBytes);
+                const uint64_t do_sub = desc_advance(do_desc, stage * 2 * kSubBytes);
+                // dV += P^T dO and dK += dS^T Q over this sub-step's 64 queries; queries
+                // 32 part + [0, 32) sit in columns 32 part + [0, 16) of the accumulator.
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {
-                    sm100::mma_f16_ss(tmem_dv, desc_kmajor(pt, ks), desc_mnmajor(do_sub, ks, 16),
-                                      kIdescPV, (h | ks) != 0);
+                    sm100::mma_f16_ts(tmem_dv, tmem_st(b) + (ks >> 1) * 32 + (ks & 1) * 8,
+                                      desc_advance(do_sub, ks * 2048), kIdescPV, (h | ks) != 0);
                 }
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {
-                    sm100::mma_f16_ss(tmem_dk, desc_kmajor(dst, ks), desc_mnmajor(q_sub, ks, 16),
-                                      kIdescPV, (h | ks) != 0);
+                    sm100::mma_f16_ts(tmem_dk, tmem_dpt(b) + (ks >> 1) * 32 + (ks & 1) * 8,
+                                      desc_advance(q_sub, ks * 2048), kIdescPV, (h | ks) != 0);
                 }
                 sm100::mma_commit(bar.stage_empty(stage));
-                sm100::mma_commit(bar.operands_free(b));
                 if (h + 1 == steps) {
                     sm100::mma_commit(bar.done());
                 }
@@ -643,24 +660,29 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         const int k_index = kb * kTile + row;
         const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
         const float scale2 = p.scale * kLog2e;
-        bool ok = true;
+        bool ok = sm100::mbar_wait(bar.resident(), 0, abort);
+        if (ok) {
+            // K and V become the A operands of the score MMAs.
+            tile_row_to_tmem(tmem_k + lane_base, k_tile, row, part);
+            tile_row_to_tmem(tmem_v + lane_base, v_tile, row, part);
+            sm100::tmem_st_wait();
+            sm100::tc_fence_before_sync();
+            sm100::mbar_arrive(bar.a_ready());
+        }
         for (int h = 0; ok && h < steps; ++h) {
             const int b = h & 1;
             const int stage = h % kBwdStages;
             const int q0 = kb * kTile + h * kSub + part * 32;  // first query of my columns
-            if (threadIdx.x == 64) {
-                FB_TRACE(0, h, 0);
-            }
-            // stage_full covers the statistics; scores_full the two accumulators.
+            // stage_full covers the statistics; scores_full the two accumulators (and, the
+            // tensor pipe being in order, that the MMAs which read this pair's previous
+            // P^T and dS^T have finished).
+            if (threadIdx.x == 64) { FB_TRACE(0, h, 0); }
             if (!sm100::mbar_wait(bar.stage_full(stage), (h / kBwdStages) & 1, abort) ||
-                !sm100::mbar_wait(bar.scores_full(b), (h >> 1) & 1, abort) ||
-                !sm100::mbar_wait(bar.operands_free(b), ((h >> 1) & 1) ^ 1u, abort)) {
+                !sm100::mbar_wait(bar.scores_full(b), (h >> 1) & 1, abort)) {
                 ok = false;
                 break;
             }
-            if (threadIdx.x == 64) {
-                FB_TRACE(0, h, 1);
-            }
+            if (threadIdx.x == 64) { FB_TRACE(0, h, 1); }
             sm100::tc_fence_after_sync();
             uint32_t s_raw[32];
             uint32_t dp_raw[32];
@@ -686,9 +708,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                              : "r"(stat + kStatBytes + c * 16));
             }
             sm100::tmem_ld_wait();
-            if (threadIdx.x == 64) {
-                FB_TRACE(0, h, 2);
-            }
+            if (threadIdx.x == 64) { FB_TRACE(0, h, 2); }
             float pv[32];
             float dsv[32];
             if (h < 2 || kb * kTile + (h + 1) * kSub > p.length) {
@@ -710,22 +730,20 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                     dsv[i] = pv[i] * (__uint_as_float(dp_raw[i]) - dlt[i]);
                 }
             }
-            store_panel_row(pt_tiles + b * kPanelBytes, row, part * 32, pv);
-            store_panel_row(dst_tiles + b * kPanelBytes, row, part * 32, dsv);
-            fence_async_shared();
+            // P^T and dS^T go back over the first 16 of the 32 columns this warp just read.
+            uint32_t packed[16];
+            pack_pairs(packed, pv);
+            sm100::tmem_st_32x16(tmem_st(b) + lane_base + part * 32, packed);
+            pack_pairs(packed, dsv);
+            sm100::tmem_st_32x16(tmem_dpt(b) + lane_base + part * 32, packed);
+            sm100::tmem_st_wait();
             sm100::tc_fence_before_sync();
             sm100::mbar_arrive(bar.operands_ready(b));
-            if (threadIdx.x == 64) {
-                FB_TRACE(0, h, 3);
-            }
+            if (threadIdx.x == 64) { FB_TRACE(0, h, 3); }
         }
-        if (threadIdx.x == 64) {
-            FB_TRACE(0, 39, 0);
-        }
+        if (threadIdx.x == 64) { FB_TRACE(0, 39, 0); }
         if (ok && sm100::mbar_wait(bar.done(), 0, abort)) {
-            if (threadIdx.x == 64) {
-                FB_TRACE(0, 39, 1);
-            }
+            if (threadIdx.x == 64) { FB_TRACE(0, 39, 1); }
             sm100::tc_fence_after_sync();
             // Rows of dV/dK are keys; this warp writes 32 of the 64 columns. dS was kept
             // unscaled, so the score scale is applied to dK here.
@@ -755,23 +773,17 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             sm100::tc_fence_before_sync();
         }
     }
-    if (threadIdx.x == 64) {
-        FB_TRACE(0, 39, 2);
-    }
+    if (threadIdx.x == 64) { FB_TRACE(0, 39, 2); }
     finish(abort_flag, tmem, 512, warp);
-    if (threadIdx.x == 64) {
-        FB_TRACE(0, 39, 3);
-    }
+    if (threadIdx.x == 64) { FB_TRACE(0, 39, 3); }
 }
 
 // ---- backward: dQ ---------------------------------------------------------------------------------
 //
 // One CTA per (head, 128 queries), 64 keys per sub-step: S = Q K^T and dP = dO V^T
-// into double-buffered accumulators, dS (queries on the rows) to double-buffered
-// shared memory, dQ += dS K accumulated in TMEM.
-
-// resident Q, dO (2 x 16 KB) + ring of (K_g, V_g) (4 x 16 KB) + two dS buffers (2 x 16 KB)
-constexpr int kDqSmem = 1024 + 2 * kTileBytes + kBwdStages * 2 * kSubBytes + 2 * kPanelBytes + 256;
+// (A = Q, dO from tensor memory) into double-buffered accumulators, dS written back
+// over dP as FP16 pairs, dQ += dS K accumulated in TMEM. Tensor memory: S at 0/64,
+// dP at 128/192, dQ 256, Q 320, dO 352.
 
 __global__ void __launch_bounds__(kBwdThreads, 1)
     fb_attention_dq(const __grid_constant__ AttnParams p) {
@@ -779,9 +791,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     const uint32_t base = (sm100::smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t q_tile = base;
     const uint32_t do_tile = base + kTileBytes;
-    const uint32_t ring = base + 2 * kTileBytes;                 // stage: K_g then V_g
-    const uint32_t ds_tiles = ring + kBwdStages * 2 * kSubBytes;  // dS[0], dS[1]
-    const BwdBarriers bar{ds_tiles + 2 * kPanelBytes};
+    const uint32_t ring = base + 2 * kTileBytes;                   // stage: K_g then V_g
+    const uint32_t stats = ring + kBwdStages * 2 * kSubBytes;      // unused here
+    const BwdBarriers bar{stats + kBwdStages * 2 * kStatBytes};
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -808,6 +820,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     auto tmem_s = [&](int b) { return tmem + 64u * b; };
     auto tmem_dp = [&](int b) { return tmem + 128u + 64u * b; };
     const uint32_t tmem_dq = tmem + 256;
+    const uint32_t tmem_q = tmem + 320, tmem_do = tmem + 352;
     volatile int* abort = &abort_flag;
 
     if (warp == 0) {
@@ -834,24 +847,27 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            bool ok = sm100::mbar_wait(bar.resident(), 0, abort);
+            bool ok = sm100::mbar_wait(bar.a_ready(), 0, abort);
+            sm100::tc_fence_after_sync();
+            const uint64_t k_desc = sm100::smem_desc_sw128(ring, 16, 1024);
+            const uint64_t v_desc = sm100::smem_desc_sw128(ring + kSubBytes, 16, 1024);
             auto issue_scores = [&](int g) -> bool {
                 const int stage = g % kBwdStages;
                 if (!sm100::mbar_wait(bar.stage_full(stage), (g / kBwdStages) & 1, abort)) {
                     return false;
                 }
                 sm100::tc_fence_after_sync();
-                const uint32_t k_sub = ring + stage * 2 * kSubBytes;
-                const uint32_t v_sub = k_sub + kSubBytes;
+                const uint64_t k_sub = desc_advance(k_desc, stage * 2 * kSubBytes);
+                const uint64_t v_sub = desc_advance(v_desc, stage * 2 * kSubBytes);
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {
-                    sm100::mma_f16_ss(tmem_s(g & 1), desc_kmajor(q_tile, ks),
-                                      desc_kmajor(k_sub, ks), kIdescSub, ks > 0);
+                    sm100::mma_f16_ts(tmem_s(g & 1), tmem_q + ks * 8, desc_advance(k_sub, ks * 32),
+                                      kIdescSub, ks > 0);
                 }
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {
-                    sm100::mma_f16_ss(tmem_dp(g & 1), desc_kmajor(do_tile, ks),
-                                      desc_kmajor(v_sub, ks), kIdescSub, ks > 0);
+                    sm100::mma_f16_ts(tmem_dp(g & 1), tmem_do + ks * 8,
+                                      desc_advance(v_sub, ks * 32), kIdescSub, ks > 0);
                 }
                 sm100::mma_commit(bar.scores_full(g & 1));
                 return true;
@@ -867,16 +883,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                 }
                 sm100::tc_fence_after_sync();
                 const int stage = g % kBwdStages;
-                const uint32_t k_sub = ring + stage * 2 * kSubBytes;
-                const uint32_t ds = ds_tiles + b * kPanelBytes;
+                const uint64_t k_sub = desc_advance(k_desc, stage * 2 * kSubBytes);
                 // dQ += dS K over this sub-step's 64 keys (the K tile read MN-major).
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {
-                    sm100::mma_f16_ss(tmem_dq, desc_kmajor(ds, ks), desc_mnmajor(k_sub, ks, 16),
-                                      kIdescPV, (g | ks) != 0);
+                    sm100::mma_f16_ts(tmem_dq, tmem_dp(b) + (ks >> 1) * 32 + (ks & 1) * 8,
+                                      desc_advance(k_sub, ks * 2048), kIdescPV, (g | ks) != 0);
                 }
                 sm100::mma_commit(bar.stage_empty(stage));
-                sm100::mma_commit(bar.operands_free(b));
                 if (g + 1 == steps) {
                     sm100::mma_commit(bar.done());
                 }
@@ -896,11 +910,18 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             lse2 = p.lse[static_cast<size_t>(bh) * p.length + q_index] * kLog2e;
             dlt = p.delta[static_cast<size_t>(bh) * p.length + q_index];
         }
-        bool ok = true;
+        bool ok = sm100::mbar_wait(bar.resident(), 0, abort);
+        if (ok) {
+            // Q and dO become the A operands of the score MMAs.
+            tile_row_to_tmem(tmem_q + lane_base, q_tile, row, part);
+            tile_row_to_tmem(tmem_do + lane_base, do_tile, row, part);
+            sm100::tmem_st_wait();
+            sm100::tc_fence_before_sync();
+            sm100::mbar_arrive(bar.a_ready());
+        }
         for (int g = 0; ok && g < steps; ++g) {
             const int b = g & 1;
-            if (!sm100::mbar_wait(bar.scores_full(b), (g >> 1) & 1, abort) ||
-                !sm100::mbar_wait(bar.operands_free(b), ((g >> 1) & 1) ^ 1u, abort)) {
+            if (!sm100::mbar_wait(bar.scores_full(b), (g >> 1) & 1, abort)) {
                 ok = false;
                 break;
             }
@@ -926,8 +947,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                     dsv[i] = e * (__uint_as_float(dp_raw[i]) - dlt);
                 }
             }
-            store_panel_row(ds_tiles + b * kPanelBytes, row, part * 32, dsv);
-            fence_async_shared();
+            // dS goes back over the first 16 of the 32 dP columns this warp just read.
+            uint32_t packed[16];
+            pack_pairs(packed, dsv);
+            sm100::tmem_st_32x16(tmem_dp(b) + lane_base + part * 32, packed);
+            sm100::tmem_st_wait();
             sm100::tc_fence_before_sync();
             sm100::mbar_arrive(bar.operands_ready(b));
         }
@@ -1090,7 +1114,7 @@ cudaError_t attention_backward(const AttentionView& dq, const AttentionView& dk,
     const unsigned grid = static_cast<unsigned>(shape.sequences * shape.heads * p.blocks);
 
     static bool dkv_configured = false;
-    e = configure(fb_attention_dkv, kDkvSmem, &dkv_configured);
+    e = configure(fb_attention_dkv, kBwdSmem, &dkv_configured);
     if (e != cudaSuccess) {
         return e;
     }
@@ -1100,13 +1124,13 @@ cudaError_t attention_backward(const AttentionView& dq, const AttentionView& dk,
     p.out_row = dk.row_stride;
     p.out_head = dk.head_stride;
     p.out_seq = dk.sequence_stride;
-    fb_attention_dkv<<<grid, kBwdThreads, kDkvSmem, stream>>>(p);
+    fb_attention_dkv<<<grid, kBwdThreads, kBwdSmem, stream>>>(p);
     e = fb::after_launch();
     if (e != cudaSuccess) {
         return e;
     }
     static bool dq_configured = false;
-    e = configure(fb_attention_dq, kDqSmem, &dq_configured);
+    e = configure(fb_attention_dq, kBwdSmem, &dq_configured);
     if (e != cudaSuccess) {
         return e;
     }
@@ -1115,7 +1139,7 @@ cudaError_t attention_backward(const AttentionView& dq, const AttentionView& dk,
     p.out_row = dq.row_stride;
     p.out_head = dq.head_stride;
     p.out_seq = dq.sequence_stride;
-    fb_attention_dq<<<grid, kBwdThreads, kDqSmem, stream>>>(p);
+    fb_attention_dq<<<grid, kBwdThreads, kBwdSmem, stream>>>(p);
     return fb::after_launch();
 }
 
