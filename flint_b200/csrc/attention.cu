@@ -211,6 +211,10 @@ __global__ void __launch_bounds__(kFwdThreads, 2)
     const uint32_t tmem_s = tmem;
     const uint32_t tmem_o = tmem + 128;
     volatile int* abort = &abort_flag;
+    fb::dependency_wait();
+    if (threadIdx.x == 0) {
+        fb::dependency_release();
+    }
 
     if (warp == 0) {
         if (lane == 0) {
@@ -406,6 +410,8 @@ struct View {
 __global__ void __launch_bounds__(256)
     fb_attention_delta(float* __restrict__ delta, View d_o, View o, int length, int heads,
                        int seqs) {
+    fb::dependency_wait();
+    fb::dependency_release();
     const long long rows = static_cast<long long>(length) * heads * seqs;
     const int lane = threadIdx.x % 32;
     for (long long r = blockIdx.x * 8LL + threadIdx.x / 32; r < rows; r += gridDim.x * 8LL) {
@@ -553,6 +559,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     const uint32_t tmem_dv = tmem + 256, tmem_dk = tmem + 320;
     const uint32_t tmem_k = tmem + 384, tmem_v = tmem + 416;
     volatile int* abort = &abort_flag;
+    fb::dependency_wait();
+    if (threadIdx.x == 0) {
+        fb::dependency_release();
+    }
 
     if (warp == 0) {
         if (lane == 0) {
@@ -822,6 +832,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     const uint32_t tmem_dq = tmem + 256;
     const uint32_t tmem_q = tmem + 320, tmem_do = tmem + 352;
     volatile int* abort = &abort_flag;
+    fb::dependency_wait();
+    if (threadIdx.x == 0) {
+        fb::dependency_release();
+    }
 
     if (warp == 0) {
         if (lane == 0) {
@@ -1073,8 +1087,8 @@ cudaError_t attention_forward(const AttentionView& o, float* lse, const Attentio
         return e;
     }
     const unsigned grid = static_cast<unsigned>(shape.sequences * shape.heads * p.blocks);
-    fb_attention_forward<<<grid, kFwdThreads, kFwdSmem, stream>>>(p);
-    return fb::after_launch();
+    return fb::launch_dependent(fb_attention_forward, dim3(grid), dim3(kFwdThreads), kFwdSmem, stream,
+                                p);
 }
 
 cudaError_t attention_backward(const AttentionView& dq, const AttentionView& dk,
@@ -1104,8 +1118,8 @@ cudaError_t attention_backward(const AttentionView& dq, const AttentionView& dk,
                    d_o.sequence_stride};
     const View vo{static_cast<const __half*>(o.base), o.row_stride, o.head_stride,
                   o.sequence_stride};
-    fb_attention_delta<<<delta_grid, 256, 0, stream>>>(delta, vdo, vo, p.length, p.heads, p.seqs);
-    e = fb::after_launch();
+    e = fb::launch_dependent(fb_attention_delta, dim3(delta_grid), dim3(256), 0, stream, delta, vdo,
+                             vo, p.length, p.heads, p.seqs);
     if (e != cudaSuccess) {
         return e;
     }
@@ -1124,8 +1138,7 @@ cudaError_t attention_backward(const AttentionView& dq, const AttentionView& dk,
     p.out_row = dk.row_stride;
     p.out_head = dk.head_stride;
     p.out_seq = dk.sequence_stride;
-    fb_attention_dkv<<<grid, kBwdThreads, kBwdSmem, stream>>>(p);
-    e = fb::after_launch();
+    e = fb::launch_dependent(fb_attention_dkv, dim3(grid), dim3(kBwdThreads), kBwdSmem, stream, p);
     if (e != cudaSuccess) {
         return e;
     }
@@ -1139,8 +1152,7 @@ cudaError_t attention_backward(const AttentionView& dq, const AttentionView& dk,
     p.out_row = dq.row_stride;
     p.out_head = dq.head_stride;
     p.out_seq = dq.sequence_stride;
-    fb_attention_dq<<<grid, kBwdThreads, kBwdSmem, stream>>>(p);
-    return fb::after_launch();
+    return fb::launch_dependent(fb_attention_dq, dim3(grid), dim3(kBwdThreads), kBwdSmem, stream, p);
 }
 
 cudaError_t attention_error_flag(int* value, bool reset) {

@@ -4,6 +4,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 
 #include <cuda.h>
 
@@ -62,6 +63,14 @@ flint_status check_spans(const char* function, const Span* spans, size_t count, 
 
 namespace {
 std::atomic<unsigned long long> g_launches{0};
+}
+
+bool dependent_launch_enabled() {
+    static const bool enabled = [] {
+        const char* v = std::getenv("FLINT_B200_PDL");
+        return !(v != nullptr && v[0] == '0');
+    }();
+    return enabled;
 }
 
 cudaError_t after_launch() {

@@ -55,6 +55,33 @@ flint_status check_spans(const char* function, const Span (&spans)[N], size_t ou
 cudaError_t after_launch();
 unsigned long long launch_count();
 
+// Launches `kernel` so that it may begin while the kernel before it in the stream
+// is still draining (programmatic dependent launch): its CTAs become resident as the
+// earlier kernel's CTAs retire, and its set-up (barrier initialisation, tensor-memory
+// allocation, index arithmetic) overlaps that tail. Every kernel launched this way
+// calls fb::dependency_wait() before its first access to global memory; the earlier
+// kernel allows the early start with fb::dependency_release(). FLINT_B200_PDL=0 in the
+// environment turns the attribute off (plain stream order). Counts the launch.
+bool dependent_launch_enabled();
+
+template <typename... Params, typename... Args>
+cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                             cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = dependent_launch_enabled() ? 1 : 0;
+    const cudaError_t e = cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+    const cudaError_t last = after_launch();
+    return e != cudaSuccess ? e : last;
+}
+
 // Number of SMs of the current device (cached per device index).
 cudaError_t sm_count(int* sms);
 

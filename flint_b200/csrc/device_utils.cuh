@@ -18,6 +18,18 @@ namespace fb {
 
 constexpr unsigned kFullMask = 0xffffffffu;
 
+// Programmatic dependent launch (see fb::launch_dependent): dependency_wait() returns
+// once every kernel this one depends on has completed and its writes are visible; it
+// costs nothing in a kernel launched the ordinary way. dependency_release() lets the
+// next kernel in the stream start its set-up early (it still waits, in its own
+// dependency_wait(), for this kernel to finish).
+__device__ __forceinline__ void dependency_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void dependency_release() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 struct Comp {
     float s = 0.0f;  // rounded sum
     float e = 0.0f;  // sum of the rounding errors

@@ -619,6 +619,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     sm100::tc_fence_after_sync();
     const uint32_t tmem_base = tmem_base_slot;
     volatile int* abort = &abort_flag;
+    // Everything above ran while the previous kernel in the stream may still have been
+    // finishing; global memory is touched only from here on.
+    fb::dependency_wait();
+    if (threadIdx.x == 0) {
+        fb::dependency_release();
+    }
 
     if (warp == 0) {
         // ---- TMA producer ----
@@ -933,6 +939,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + 32 * pair_epilo
     sm100::tc_fence_after_sync();
     const uint32_t tmem_base = tmem_base_slot;
     volatile int* abort = &abort_flag;
+    // Everything above ran while the previous kernel in the stream may still have been
+    // finishing; global memory is touched only from here on.
+    fb::dependency_wait();
+    if (threadIdx.x == 0) {
+        fb::dependency_release();
+    }
 
     if (warp == 0) {
         // ---- TMA producer (both CTAs) ----
@@ -1248,6 +1260,8 @@ __global__ void __launch_bounds__(256)
 __global__ void __launch_bounds__(256)
     fb_gemm_tn_reduce(float4* __restrict__ y, const float4* __restrict__ partials, size_t quads,
                       int splits, int accumulate) {
+    fb::dependency_wait();
+    fb::dependency_release();
     for (size_t i = size_t{blockIdx.x} * 256 + threadIdx.x; i < quads;
          i += size_t{gridDim.x} * 256) {
         float4 s = partials[i];
@@ -1363,8 +1377,7 @@ cudaError_t launch_tc(GemmParams& p, const void* x, const void* w, int sms, cuda
         configured = true;
     }
     const unsigned grid = static_cast<unsigned>(std::min<long long>(p.tiles_total, sms));
-    kernel<<<grid, kThreads, R::kSmemBytes, stream>>>(p);
-    return fb::after_launch();
+    return fb::launch_dependent(kernel, dim3(grid), dim3(kThreads), R::kSmemBytes, stream, p);
 }
 
 bool pair_disabled() {
@@ -1420,9 +1433,8 @@ cudaError_t launch_pair(GemmParams& p, const void* x, const void* w, int sms, cu
         configured = true;
     }
     const long long pairs = std::min<long long>(p.tiles_total, sms / 2);
-    kernel<<<static_cast<unsigned>(2 * pairs), 64 + 32 * pair_epilogue_warps<E>(), kPairSmemBytes,
-             stream>>>(p);
-    return fb::after_launch();
+    return fb::launch_dependent(kernel, dim3(static_cast<unsigned>(2 * pairs)),
+                                dim3(64 + 32 * pair_epilogue_warps<E>()), kPairSmemBytes, stream, p);
 }
 
 template <Layout L, Epilogue E>
@@ -1557,10 +1569,9 @@ cudaError_t gemm_tn(void* y, const void* x, const void* w, size_t m, size_t n, s
     const size_t quads = m * n / 4;
     const unsigned grid =
         static_cast<unsigned>(std::min<size_t>((quads + 255) / 256, static_cast<size_t>(sms) * 8));
-    fb_gemm_tn_reduce<<<grid, 256, 0, stream>>>(static_cast<float4*>(y),
-                                                static_cast<const float4*>(workspace), quads,
-                                                s.count, p.accumulate);
-    return fb::after_launch();
+    return fb::launch_dependent(fb_gemm_tn_reduce, dim3(grid), dim3(256), 0, stream,
+                                static_cast<float4*>(y), static_cast<const float4*>(workspace),
+                                quads, s.count, p.accumulate);
 }
 
 cudaError_t gemm_batched(Layout l, void* y, const void* x, const void* w, size_t batches,

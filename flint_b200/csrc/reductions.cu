@@ -141,6 +141,10 @@ __global__ void __launch_bounds__(kTilePieces * (kLaneRows + 1))
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    fb::dependency_wait();
+    if (ly == 0 && px == 0) {
+        fb::dependency_release();
+    }
     if constexpr (kSource == Source::kHalfTimesXhat) {
         const int t = ly * kTilePieces + px;
         if (t < chunk_rows) {
@@ -354,6 +358,8 @@ constexpr int kFinishWarps = 8;
 __global__ void __launch_bounds__(32 * kFinishWarps)
     fb_column_finish(float4* __restrict__ out, const float4* __restrict__ partial, size_t chunks,
                      int quads, bool accumulate) {
+    fb::dependency_wait();
+    fb::dependency_release();
     const int quad = blockIdx.x * kFinishWarps + threadIdx.x / 32;
     if (quad >= quads) {
         return;
@@ -432,11 +438,11 @@ cudaError_t launch_partials(void* workspace, const void* src, const void* x, con
             return e;
         }
     }
-    fb_column_partials<kSource>
-        <<<dim3(chunks, tiles), dim3(kTilePieces, kLaneRows + 1), kDynamic, stream>>>(
-        maps, static_cast<float4*>(workspace), src, static_cast<const float4*>(x),
-        static_cast<const float*>(mean), static_cast<const float*>(rstd), rows, pieces);
-    return fb::after_launch();
+    return fb::launch_dependent(fb_column_partials<kSource>, dim3(chunks, tiles),
+                                dim3(kTilePieces, kLaneRows + 1), kDynamic, stream, maps,
+                                static_cast<float4*>(workspace), src, static_cast<const float4*>(x),
+                                static_cast<const float*>(mean), static_cast<const float*>(rstd),
+                                rows, pieces);
 }
 
 cudaError_t launch_finish(void* out, const void* workspace, size_t rows, size_t cols,
@@ -444,10 +450,9 @@ cudaError_t launch_finish(void* out, const void* workspace, size_t rows, size_t 
     const size_t chunks = (rows + kChunkRows - 1) / kChunkRows;
     const int quads = static_cast<int>(cols / 4);
     const unsigned blocks = static_cast<unsigned>((quads + kFinishWarps - 1) / kFinishWarps);
-    fb_column_finish<<<blocks, 32 * kFinishWarps, 0, stream>>>(
-        static_cast<float4*>(out), static_cast<const float4*>(workspace), chunks, quads,
-        accumulate);
-    return fb::after_launch();
+    return fb::launch_dependent(fb_column_finish, dim3(blocks), dim3(32 * kFinishWarps), 0, stream,
+                                static_cast<float4*>(out), static_cast<const float4*>(workspace),
+                                chunks, quads, accumulate);
 }
 
 // ---- LayerNorm backward: dx -----------------------------------------------------
@@ -464,6 +469,8 @@ __global__ void __launch_bounds__(32 * kWarpsPerBlock)
                              const float4* __restrict__ x, const float* __restrict__ mean,
                              const float* __restrict__ rstd, const float4* __restrict__ gamma,
                              size_t rows, int pieces, bool accumulate, uint4* __restrict__ dx_half) {
+    fb::dependency_wait();
+    fb::dependency_release();
     const size_t row = size_t{blockIdx.x} * kWarpsPerBlock + threadIdx.x / 32;
     if (row >= rows) {
         return;
@@ -905,19 +912,23 @@ cudaError_t launch_layernorm_backward(void* dx, void* dgamma, void* dbeta, const
     const auto* rf = static_cast<const float*>(rstd);
     const auto* gq = static_cast<const float4*>(gamma);
     if (pieces <= 32) {
-        fb_layernorm_backward_dx<1><<<blocks, 32 * kWarpsPerBlock, 0, stream>>>(
-            dxq, dyq, xq, mf, rf, gq, rows, pieces, accumulate_dx, static_cast<uint4*>(dx_half));
+        e = fb::launch_dependent(fb_layernorm_backward_dx<1>, dim3(blocks), dim3(32 * kWarpsPerBlock), 0,
+                                 stream, dxq, dyq, xq, mf, rf, gq, rows, pieces, accumulate_dx,
+                                 static_cast<uint4*>(dx_half));
     } else if (pieces <= 96) {
-        fb_layernorm_backward_dx<3><<<blocks, 32 * kWarpsPerBlock, 0, stream>>>(
-            dxq, dyq, xq, mf, rf, gq, rows, pieces, accumulate_dx, static_cast<uint4*>(dx_half));
+        e = fb::launch_dependent(fb_layernorm_backward_dx<3>, dim3(blocks), dim3(32 * kWarpsPerBlock), 0,
+                                 stream, dxq, dyq, xq, mf, rf, gq, rows, pieces, accumulate_dx,
+                                 static_cast<uint4*>(dx_half));
     } else if (pieces <= 192) {
-        fb_layernorm_backward_dx<6><<<blocks, 32 * kWarpsPerBlock, 0, stream>>>(
-            dxq, dyq, xq, mf, rf, gq, rows, pieces, accumulate_dx, static_cast<uint4*>(dx_half));
+        e = fb::launch_dependent(fb_layernorm_backward_dx<6>, dim3(blocks), dim3(32 * kWarpsPerBlock), 0,
+                                 stream, dxq, dyq, xq, mf, rf, gq, rows, pieces, accumulate_dx,
+                                 static_cast<uint4*>(dx_half));
     } else {
-        fb_layernorm_backward_dx<0><<<blocks, 32 * kWarpsPerBlock, 0, stream>>>(
-            dxq, dyq, xq, mf, rf, gq, rows, pieces, accumulate_dx, static_cast<uint4*>(dx_half));
+        e = fb::launch_dependent(fb_layernorm_backward_dx<0>, dim3(blocks), dim3(32 * kWarpsPerBlock), 0,
+                                 stream, dxq, dyq, xq, mf, rf, gq, rows, pieces, accumulate_dx,
+                                 static_cast<uint4*>(dx_half));
     }
-    return fb::after_launch();
+    return e;
 }
 
 cudaError_t launch_embedding_backward(void* dwte, void* dwpe, const void* dx, const void* tokens,

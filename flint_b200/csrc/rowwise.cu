@@ -39,6 +39,8 @@ __global__ void __launch_bounds__(kThreads)
                               float* __restrict__ rstd, const float* __restrict__ x,
                               const float* __restrict__ gamma, const float* __restrict__ beta,
                               size_t rows, int cols, float eps) {
+    fb::dependency_wait();
+    fb::dependency_release();
     const size_t row = size_t{blockIdx.x} * kWarpsPerBlock + threadIdx.x / 32;
     if (row >= rows) {
         return;
@@ -451,6 +453,10 @@ __global__ void __launch_bounds__(kCeThreads, 1)
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar0 + 8u) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    fb::dependency_wait();
+    if (threadIdx.x == 0) {
+        fb::dependency_release();
         if (blockIdx.x < rows) {
             issue(blockIdx.x, 0);
         }
@@ -646,22 +652,23 @@ flint_status flint_layernorm_forward(void* y, void* mean, void* rstd, const void
     const auto* bf = static_cast<const float*>(beta);
     const int c = static_cast<int>(cols);
     if (cols % 4 == 0 && cols <= 128 * 2) {
-        fb_layernorm_forward_regs<2><<<blocks, kThreads, 0, stream>>>(yh, mf, rf, xf, gf, bf,
-                                                                       rows, c, eps);
+        FB_CUDA(fb::launch_dependent(fb_layernorm_forward_regs<2>, dim3(blocks), dim3(kThreads), 0,
+                                     stream, yh, mf, rf, xf, gf, bf, rows, c, eps));
     } else if (cols % 4 == 0 && cols <= 128 * 6) {
-        fb_layernorm_forward_regs<6><<<blocks, kThreads, 0, stream>>>(yh, mf, rf, xf, gf, bf,
-                                                                       rows, c, eps);
+        FB_CUDA(fb::launch_dependent(fb_layernorm_forward_regs<6>, dim3(blocks), dim3(kThreads), 0,
+                                     stream, yh, mf, rf, xf, gf, bf, rows, c, eps));
     } else if (cols % 4 == 0 && cols <= 128 * 12) {
-        fb_layernorm_forward_regs<12><<<blocks, kThreads, 0, stream>>>(yh, mf, rf, xf, gf, bf,
-                                                                        rows, c, eps);
+        FB_CUDA(fb::launch_dependent(fb_layernorm_forward_regs<12>, dim3(blocks), dim3(kThreads), 0,
+                                     stream, yh, mf, rf, xf, gf, bf, rows, c, eps));
     } else if (cols % 4 == 0) {
         fb_layernorm_forward_stream<4><<<blocks, kThreads, 0, stream>>>(yh, mf, rf, xf, gf, bf,
                                                                          rows, c, eps);
+        FB_CUDA(fb::after_launch());
     } else {
         fb_layernorm_forward_stream<1><<<blocks, kThreads, 0, stream>>>(yh, mf, rf, xf, gf, bf,
                                                                          rows, c, eps);
+        FB_CUDA(fb::after_launch());
     }
-    FB_CUDA(fb::after_launch());
     return FLINT_OK;
 }
 
@@ -778,11 +785,11 @@ flint_status flint_softmax_cross_entropy(void* dlogits, void* row_loss, const vo
     int sms = 148;
     FB_CUDA(fb::sm_count(&sms));
     const unsigned blocks = static_cast<unsigned>(std::min<size_t>(rows, static_cast<size_t>(sms)));
-    fb_softmax_cross_entropy<<<blocks, kCeThreads, buffers * row_bytes, stream>>>(
-        static_cast<uint4*>(dlogits), static_cast<float*>(row_loss),
-        static_cast<const uint4*>(logits), static_cast<const uint16_t*>(targets), scale, rows,
-        static_cast<int>(vocab), static_cast<int>(cols), buffers);
-    FB_CUDA(fb::after_launch());
+    FB_CUDA(fb::launch_dependent(fb_softmax_cross_entropy, dim3(blocks), dim3(kCeThreads),
+                                 buffers * row_bytes, stream, static_cast<uint4*>(dlogits),
+                                 static_cast<float*>(row_loss), static_cast<const uint4*>(logits),
+                                 static_cast<const uint16_t*>(targets), scale, rows,
+                                 static_cast<int>(vocab), static_cast<int>(cols), buffers));
     return FLINT_OK;
 }
 
