@@ -48,16 +48,6 @@ constexpr float kLn2 = 0.6931471805599453f;
 
 __device__ int g_attention_error = 0;
 
-#ifdef FB_ATTN_TRACE
-__device__ long long g_trace[8][2][40][4];
-#define FB_TRACE(who, h, k)                                   \
-    if (blockIdx.x < 8 && (h) < 40) {                         \
-        g_trace[blockIdx.x][who][h][k] = clock64();           \
-    }
-#else
-#define FB_TRACE(who, h, k)
-#endif
-
 struct AttnParams {
     CUtensorMap map_q, map_k, map_v, map_do;          // 128-row boxes
     CUtensorMap map_q64, map_k64, map_v64, map_do64;  // 64-row boxes (backward sub-steps)
@@ -452,8 +442,13 @@ constexpr int kSubBytes = kSub * kHead * 2;  // 8 KB: one streamed tile
 constexpr int kBwdStages = 4;
 constexpr int kStatBytes = kSub * 4;  // one sub-step's log-sum-exp or delta values
 // resident pair (2 x 16 KB) + ring of tile pairs (4 x 16 KB) + row statistics + barriers
-constexpr int kBwdSmem = 1024 + 2 * kTileBytes + kBwdStages * 2 * kSubBytes +
+constexpr int kBwdUsed = 1024 + 2 * kTileBytes + kBwdStages * 2 * kSubBytes +
                          kBwdStages * 2 * kStatBytes + 256;
+// The kernels are persistent, one CTA per SM, and each CTA wants all of tensor memory:
+// asking for more than half an SM's shared memory keeps two from landing on one SM
+// (which happens when CTAs become resident one SM at a time, behind an earlier kernel,
+// and leaves other SMs idle while the pair takes turns).
+constexpr int kBwdSmem = kBwdUsed > 120 * 1024 ? kBwdUsed : 120 * 1024;
 constexpr uint32_t kIdescSub = sm100::instr_desc_f16(128, 64, false, false);  // A Bsub^T
 
 struct BwdBarriers {
@@ -513,13 +508,19 @@ __device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) 
 
 // ---- backward: dK and dV ------------------------------------------------------------------------
 //
-// One CTA per (head, 128 keys), 64 queries per sub-step. Scores are formed
-// transposed, S^T = K Q^T and dP^T = V dO^T with keys on the TMEM lanes (A = K, V
-// from tensor memory), so P^T and dS^T are already the A operands of
-// dV += P^T dO and dK += dS^T Q. Accumulator pairs are double-buffered: the MMA
-// warp issues sub-step h+1's score MMAs before it waits for sub-step h's
-// probabilities. Tensor memory: S^T at 0/64, dP^T at 128/192 (P^T and dS^T overwrite
-// 16 + 16 columns of each), dV 256, dK 320, K 384, V 416.
+// Persistent CTAs, one per SM, each taking (head, 128 keys) items round-robin from a
+// list ordered by work (key tile 0 first); an item is 64 queries per sub-step from the
+// diagonal on. Scores are formed transposed, S^T = K Q^T and dP^T = V dO^T with keys on
+// the TMEM lanes (A = K, V from tensor memory), so P^T and dS^T are already the A
+// operands of dV += P^T dO and dK += dS^T Q. Accumulator pairs are double-buffered: the
+// MMA warp issues sub-step h+1's score MMAs before it waits for sub-step h's
+// probabilities. Items overlap too: the producer fetches the next item's K/V as soon as
+// this item's were copied to tensor memory, the compute warps install them right after
+// their last sub-step, and the MMA warp issues the next item's first score MMAs while the
+// compute warps write this item's dK/dV out. Barrier phases and the tile ring simply
+// continue from item to item (an item has an even number of sub-steps).
+// Tensor memory: S^T at 0/64, dP^T at 128/192 (P^T and dS^T overwrite 16 + 16 columns of
+// each), dV 256, dK 320, K 384, V 416.
 
 __global__ void __launch_bounds__(kBwdThreads, 1)
     fb_attention_dkv(const __grid_constant__ AttnParams p) {
@@ -536,12 +537,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     const int warp = threadIdx.x / 32;
     const int lane = threadIdx.x % 32;
     const int bh_count = p.heads * p.seqs;
-    const int kb = static_cast<int>(blockIdx.x / bh_count);  // key tile 0 has the most work
-    const int bh = static_cast<int>(blockIdx.x % bh_count);
-    const int head = bh % p.heads;
-    const int seq = bh / p.heads;
-    const int steps = 2 * (p.blocks - kb);  // 64-query sub-steps from the diagonal tile on
-    if (threadIdx.x == 64) { FB_TRACE(0, 38, 0); }
+    const int items = bh_count * p.blocks;
+    const int first_item = static_cast<int>(blockIdx.x);
+    const int stride = static_cast<int>(gridDim.x);
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -560,200 +558,243 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     const uint32_t tmem_k = tmem + 384, tmem_v = tmem + 416;
     volatile int* abort = &abort_flag;
     fb::dependency_wait();
-    if (threadIdx.x == 0) {
-        fb::dependency_release();
-    }
 
     if (warp == 0) {
         if (lane == 0) {
-            sm100::mbar_expect_tx(bar.resident(), 2 * kTileBytes);
-            tma_load_4d(k_tile, &p.map_k, bar.resident(), 0, kb * kTile, head, seq);
-            tma_load_4d(v_tile, &p.map_v, bar.resident(), 0, kb * kTile, head, seq);
             int stage = 0;
             uint32_t phase = 0;
-            for (int h = 0; h < steps; ++h) {
-                if (!sm100::mbar_wait(bar.stage_empty(stage), phase ^ 1u, abort)) {
+            bool ok = true;
+            int round = 0;
+            for (int item = first_item; ok && item < items; item += stride, ++round) {
+                const int kb = item / bh_count;
+                const int bh = item % bh_count;
+                const int head = bh % p.heads;
+                const int seq = bh / p.heads;
+                const int steps = 2 * (p.blocks - kb);
+                // The K/V buffers are free once the item before was copied to tensor memory.
+                if (round > 0 && !sm100::mbar_wait(bar.a_ready(), (round - 1) & 1, abort)) {
                     break;
                 }
-                const int q0 = kb * kTile + h * kSub;
-                const uint32_t dst = ring + stage * 2 * kSubBytes;
-                // Row statistics of the queries that exist (length is a multiple of 8, so
-                // the byte count is a multiple of 32); the rest of the slot is never used.
-                const int present = min(kSub, p.length - q0);
-                const uint32_t stat_bytes = present > 0 ? static_cast<uint32_t>(present) * 4u : 0u;
-                sm100::mbar_expect_tx(bar.stage_full(stage), 2 * kSubBytes + 2 * stat_bytes);
-                tma_load_4d(dst, &p.map_q64, bar.stage_full(stage), 0, q0, head, seq);
-                tma_load_4d(dst + kSubBytes, &p.map_do64, bar.stage_full(stage), 0, q0, head, seq);
-                if (stat_bytes != 0) {
-                    const size_t at = static_cast<size_t>(bh) * p.length + q0;
-                    const uint32_t slot = stats + stage * 2 * kStatBytes;
-                    bulk_load(slot, p.lse + at, stat_bytes, bar.stage_full(stage));
-                    bulk_load(slot + kStatBytes, p.delta + at, stat_bytes, bar.stage_full(stage));
-                }
-                if (++stage == kBwdStages) {
-                    stage = 0;
-                    phase ^= 1u;
+                sm100::mbar_expect_tx(bar.resident(), 2 * kTileBytes);
+                tma_load_4d(k_tile, &p.map_k, bar.resident(), 0, kb * kTile, head, seq);
+                tma_load_4d(v_tile, &p.map_v, bar.resident(), 0, kb * kTile, head, seq);
+                for (int h = 0; h < steps; ++h) {
+                    if (!sm100::mbar_wait(bar.stage_empty(stage), phase ^ 1u, abort)) {
+                        ok = false;
+                        break;
+                    }
+                    const int q0 = kb * kTile + h * kSub;
+                    const uint32_t dst = ring + stage * 2 * kSubBytes;
+                    // Row statistics of the queries that exist (length is a multiple of 8,
+                    // so the byte count is a multiple of 32); the rest of the slot is never
+                    // used.
+                    const int present = min(kSub, p.length - q0);
+                    const uint32_t stat_bytes =
+                        present > 0 ? static_cast<uint32_t>(present) * 4u : 0u;
+                    sm100::mbar_expect_tx(bar.stage_full(stage), 2 * kSubBytes + 2 * stat_bytes);
+                    tma_load_4d(dst, &p.map_q64, bar.stage_full(stage), 0, q0, head, seq);
+                    tma_load_4d(dst + kSubBytes, &p.map_do64, bar.stage_full(stage), 0, q0, head,
+                                seq);
+                    if (stat_bytes != 0) {
+                        const size_t at = static_cast<size_t>(bh) * p.length + q0;
+                        const uint32_t slot = stats + stage * 2 * kStatBytes;
+                        bulk_load(slot, p.lse + at, stat_bytes, bar.stage_full(stage));
+                        bulk_load(slot + kStatBytes, p.delta + at, stat_bytes,
+                                  bar.stage_full(stage));
+                    }
+                    if (++stage == kBwdStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            bool ok = sm100::mbar_wait(bar.a_ready(), 0, abort);
-            sm100::tc_fence_after_sync();
             // Descriptors of stage 0's tiles; a stage is 16 KB further, a K-major k-step 32
             // bytes, an MN-major one 2,048.
             const uint64_t q_desc = sm100::smem_desc_sw128(ring, 16, 1024);
             const uint64_t do_desc = sm100::smem_desc_sw128(ring + kSubBytes, 16, 1024);
-            // S^T and dP^T of sub-step g into accumulator pair g & 1.
-            auto issue_scores = [&](int g) -> bool {
-                const int stage = g % kBwdStages;
-                if (!sm100::mbar_wait(bar.stage_full(stage), (g / kBwdStages) & 1, abort)) {
-                    return false;
-                }
+            uint32_t before = 0;  // sub-steps of earlier items (always even)
+            bool ok = true;
+            int round = 0;
+            for (int item = first_item; ok && item < items; item += stride, ++round) {
+                const int steps = 2 * (p.blocks - item / bh_count);
+                ok = sm100::mbar_wait(bar.a_ready(), round & 1, abort);
                 sm100::tc_fence_after_sync();
-                const uint64_t q_sub = desc_advance(q_desc, stage * 2 * kSubBytes);
-                const uint64_t do_sub = desc_advance(do_desc, stage * 2 * kSubBytes);
+                // S^T and dP^T of sub-step g into accumulator pair g & 1.
+                auto issue_scores = [&](int g) -> bool {
+                    const uint32_t count = before + g;
+                    const int stage = count % kBwdStages;
+                    if (!sm100::mbar_wait(bar.stage_full(stage), (count / kBwdStages) & 1, abort)) {
+                        return false;
+                    }
+                    sm100::tc_fence_after_sync();
+                    const uint64_t q_sub = desc_advance(q_desc, stage * 2 * kSubBytes);
+                    const uint64_t do_sub = desc_advance(do_desc, stage * 2 * kSubBytes);
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks) {
-                    sm100::mma_f16_ts(tmem_st(g & 1), tmem_k + ks * 8, desc_advance(q_sub, ks * 32),
-                                      kIdescSub, ks > 0);
-                }
+                    for (int ks = 0; ks < 4; ++ks) {
+                        sm100::mma_f16_ts(tmem_st(g & 1), tmem_k + ks * 8,
+                                          desc_advance(q_sub, ks * 32), kIdescSub, ks > 0);
+                    }
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks) {
-                    sm100::mma_f16_ts(tmem_dpt(g & 1), tmem_v + ks * 8,
-                                      desc_advance(do_sub, ks * 32), kIdescSub, ks > 0);
-                }
-                sm100::mma_commit(bar.scores_full(g & 1));
-                return true;
-            };
-            FB_TRACE(1, 39, 0);
-            ok = ok && issue_scores(0);
-            FB_TRACE(1, 39, 1);
-            for (int h = 0; ok && h < steps; ++h) {
-                const int b = h & 1;
-                FB_TRACE(1, h, 0);
-                if (h + 1 < steps && !issue_scores(h + 1)) {
-                    break;
-                }
-                FB_TRACE(1, h, 1);
-                if (!sm100::mbar_wait(bar.operands_ready(b), (h >> 1) & 1, abort)) {
-                    break;
-                }
-                FB_TRACE(1, h, 2);
-                sm100::tc_fence_after_sync();
-                const int stage = h % kBwdStages;
-                const uint64_t q_sub = desc_advance(q_desc, stage * 2 * kSubBytes);
-                const uint64_t do_sub = desc_advance(do_desc, stage * 2 * kSubBytes);
-                // dV += P^T dO and dK += dS^T Q over this sub-step's 64 queries; queries
-                // 32 part + [0, 32) sit in columns 32 part + [0, 16) of the accumulator.
+                    for (int ks = 0; ks < 4; ++ks) {
+                        sm100::mma_f16_ts(tmem_dpt(g & 1), tmem_v + ks * 8,
+                                          desc_advance(do_sub, ks * 32), kIdescSub, ks > 0);
+                    }
+                    sm100::mma_commit(bar.scores_full(g & 1));
+                    return true;
+                };
+                ok = ok && issue_scores(0);
+                for (int h = 0; ok && h < steps; ++h) {
+                    const int b = h & 1;
+                    const uint32_t count = before + h;
+                    if (h + 1 < steps && !issue_scores(h + 1)) {
+                        ok = false;
+                        break;
+                    }
+                    if (!sm100::mbar_wait(bar.operands_ready(b), (count >> 1) & 1, abort)) {
+                        ok = false;
+                        break;
+                    }
+                    sm100::tc_fence_after_sync();
+                    const int stage = count % kBwdStages;
+                    const uint64_t q_sub = desc_advance(q_desc, stage * 2 * kSubBytes);
+                    const uint64_t do_sub = desc_advance(do_desc, stage * 2 * kSubBytes);
+                    // dV += P^T dO and dK += dS^T Q over this sub-step's 64 queries; queries
+                    // 32 part + [0, 32) sit in columns 32 part + [0, 16) of the accumulator.
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks) {
-                    sm100::mma_f16_ts(tmem_dv, tmem_st(b) + (ks >> 1) * 32 + (ks & 1) * 8,
-                                      desc_advance(do_sub, ks * 2048), kIdescPV, (h | ks) != 0);
-                }
+                    for (int ks = 0; ks < 4; ++ks) {
+                        sm100::mma_f16_ts(tmem_dv, tmem_st(b) + (ks >> 1) * 32 + (ks & 1) * 8,
+                                          desc_advance(do_sub, ks * 2048), kIdescPV,
+                                          (h | ks) != 0);
+                    }
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks) {
-                    sm100::mma_f16_ts(tmem_dk, tmem_dpt(b) + (ks >> 1) * 32 + (ks & 1) * 8,
-                                      desc_advance(q_sub, ks * 2048), kIdescPV, (h | ks) != 0);
+                    for (int ks = 0; ks < 4; ++ks) {
+                        sm100::mma_f16_ts(tmem_dk, tmem_dpt(b) + (ks >> 1) * 32 + (ks & 1) * 8,
+                                          desc_advance(q_sub, ks * 2048), kIdescPV, (h | ks) != 0);
+                    }
+                    sm100::mma_commit(bar.stage_empty(stage));
+                    if (h + 1 == steps) {
+                        sm100::mma_commit(bar.done());
+                    }
                 }
-                sm100::mma_commit(bar.stage_empty(stage));
-                if (h + 1 == steps) {
-                    sm100::mma_commit(bar.done());
-                }
-                FB_TRACE(1, h, 3);
+                before += steps;
             }
         }
     } else {
         const int quadrant = warp % 4;
         const int part = (warp - 2) / 4;                 // which 32 of the 64 query columns
         const int row = quadrant * 32 + lane;            // key row inside the tile
-        const int k_index = kb * kTile + row;
         const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
         const float scale2 = p.scale * kLog2e;
-        bool ok = sm100::mbar_wait(bar.resident(), 0, abort);
-        if (ok) {
-            // K and V become the A operands of the score MMAs.
+        // K and V of an item become the A operands of its score MMAs. Called when every
+        // score MMA of the item before has completed (its last scores_full was awaited).
+        auto install = [&](int round) -> bool {
+            if (!sm100::mbar_wait(bar.resident(), round & 1, abort)) {
+                return false;
+            }
             tile_row_to_tmem(tmem_k + lane_base, k_tile, row, part);
             tile_row_to_tmem(tmem_v + lane_base, v_tile, row, part);
             sm100::tmem_st_wait();
             sm100::tc_fence_before_sync();
             sm100::mbar_arrive(bar.a_ready());
-        }
-        for (int h = 0; ok && h < steps; ++h) {
-            const int b = h & 1;
-            const int stage = h % kBwdStages;
-            const int q0 = kb * kTile + h * kSub + part * 32;  // first query of my columns
-            // stage_full covers the statistics; scores_full the two accumulators (and, the
-            // tensor pipe being in order, that the MMAs which read this pair's previous
-            // P^T and dS^T have finished).
-            if (threadIdx.x == 64) { FB_TRACE(0, h, 0); }
-            if (!sm100::mbar_wait(bar.stage_full(stage), (h / kBwdStages) & 1, abort) ||
-                !sm100::mbar_wait(bar.scores_full(b), (h >> 1) & 1, abort)) {
+            return true;
+        };
+        uint32_t before = 0;
+        int round = 0;
+        bool ok = first_item < items && install(0);
+        for (int item = first_item; ok && item < items; item += stride, ++round) {
+            const int kb = item / bh_count;
+            const int bh = item % bh_count;
+            const int head = bh % p.heads;
+            const int seq = bh / p.heads;
+            const int steps = 2 * (p.blocks - kb);
+            const int k_index = kb * kTile + row;
+            for (int h = 0; ok && h < steps; ++h) {
+                const int b = h & 1;
+                const uint32_t count = before + h;
+                const int stage = count % kBwdStages;
+                const int q0 = kb * kTile + h * kSub + part * 32;  // first query of my columns
+                // stage_full covers the statistics; scores_full the two accumulators (and,
+                // the tensor pipe being in order, that the MMAs which read this pair's
+                // previous P^T and dS^T have finished).
+                if (!sm100::mbar_wait(bar.stage_full(stage), (count / kBwdStages) & 1, abort) ||
+                    !sm100::mbar_wait(bar.scores_full(b), (count >> 1) & 1, abort)) {
+                    ok = false;
+                    break;
+                }
+                sm100::tc_fence_after_sync();
+                uint32_t s_raw[32];
+                uint32_t dp_raw[32];
+                sm100::tmem_ld_32x32(tmem_st(b) + lane_base + part * 32, s_raw);
+                sm100::tmem_ld_32x32(tmem_dpt(b) + lane_base + part * 32, dp_raw);
+                // My 32 queries' statistics: every lane reads the same addresses (broadcast).
+                const uint32_t stat = stats + stage * 2 * kStatBytes + part * 128;
+                float lse2[32];
+                float dlt[32];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    float a0, a1, a2, a3;
+                    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                 : "=f"(a0), "=f"(a1), "=f"(a2), "=f"(a3)
+                                 : "r"(stat + c * 16));
+                    lse2[4 * c] = a0 * kLog2e;
+                    lse2[4 * c + 1] = a1 * kLog2e;
+                    lse2[4 * c + 2] = a2 * kLog2e;
+                    lse2[4 * c + 3] = a3 * kLog2e;
+                    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                 : "=f"(dlt[4 * c]), "=f"(dlt[4 * c + 1]), "=f"(dlt[4 * c + 2]),
+                                   "=f"(dlt[4 * c + 3])
+                                 : "r"(stat + kStatBytes + c * 16));
+                }
+                sm100::tmem_ld_wait();
+                float pv[32];
+                float dsv[32];
+                if (h < 2 || kb * kTile + (h + 1) * kSub > p.length) {
+                    // The diagonal tile (a key is visible to the queries at or after it) or
+                    // a sub-step with absent queries, whose statistics slots were not
+                    // filled: both tests select rather than multiply.
+                    const int first_visible = h < 2 ? k_index : 0;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const bool visible = first_visible <= q0 + i && q0 + i < p.length;
+                        const float e =
+                            fast_exp2(fmaf(__uint_as_float(s_raw[i]), scale2, -lse2[i]));
+                        pv[i] = visible ? e : 0.0f;
+                        dsv[i] = visible ? e * (__uint_as_float(dp_raw[i]) - dlt[i]) : 0.0f;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        pv[i] = fast_exp2(fmaf(__uint_as_float(s_raw[i]), scale2, -lse2[i]));
+                        dsv[i] = pv[i] * (__uint_as_float(dp_raw[i]) - dlt[i]);
+                    }
+                }
+                // P^T and dS^T go back over the first 16 of the 32 columns this warp read.
+                uint32_t packed[16];
+                pack_pairs(packed, pv);
+                sm100::tmem_st_32x16(tmem_st(b) + lane_base + part * 32, packed);
+                pack_pairs(packed, dsv);
+                sm100::tmem_st_32x16(tmem_dpt(b) + lane_base + part * 32, packed);
+                sm100::tmem_st_wait();
+                sm100::tc_fence_before_sync();
+                sm100::mbar_arrive(bar.operands_ready(b));
+            }
+            before += steps;
+            if (!ok) {
+                break;
+            }
+            // The next item's K/V go in now, so that its first score MMAs run while this
+            // item's gradients are written out.
+            if (item + stride < items && !install(round + 1)) {
                 ok = false;
                 break;
             }
-            if (threadIdx.x == 64) { FB_TRACE(0, h, 1); }
-            sm100::tc_fence_after_sync();
-            uint32_t s_raw[32];
-            uint32_t dp_raw[32];
-            sm100::tmem_ld_32x32(tmem_st(b) + lane_base + part * 32, s_raw);
-            sm100::tmem_ld_32x32(tmem_dpt(b) + lane_base + part * 32, dp_raw);
-            // My 32 queries' statistics: every lane reads the same addresses (broadcast).
-            const uint32_t stat = stats + stage * 2 * kStatBytes + part * 128;
-            float lse2[32];
-            float dlt[32];
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                float a0, a1, a2, a3;
-                asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                             : "=f"(a0), "=f"(a1), "=f"(a2), "=f"(a3)
-                             : "r"(stat + c * 16));
-                lse2[4 * c] = a0 * kLog2e;
-                lse2[4 * c + 1] = a1 * kLog2e;
-                lse2[4 * c + 2] = a2 * kLog2e;
-                lse2[4 * c + 3] = a3 * kLog2e;
-                asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                             : "=f"(dlt[4 * c]), "=f"(dlt[4 * c + 1]), "=f"(dlt[4 * c + 2]),
-                               "=f"(dlt[4 * c + 3])
-                             : "r"(stat + kStatBytes + c * 16));
+            if (!sm100::mbar_wait(bar.done(), round & 1, abort)) {
+                ok = false;
+                break;
             }
-            sm100::tmem_ld_wait();
-            if (threadIdx.x == 64) { FB_TRACE(0, h, 2); }
-            float pv[32];
-            float dsv[32];
-            if (h < 2 || kb * kTile + (h + 1) * kSub > p.length) {
-                // The diagonal tile (a key is visible to the queries at or after it) or a
-                // sub-step with absent queries, whose statistics slots were not filled:
-                // both tests select rather than multiply.
-                const int first_visible = h < 2 ? k_index : 0;
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const bool visible = first_visible <= q0 + i && q0 + i < p.length;
-                    const float e = fast_exp2(fmaf(__uint_as_float(s_raw[i]), scale2, -lse2[i]));
-                    pv[i] = visible ? e : 0.0f;
-                    dsv[i] = visible ? e * (__uint_as_float(dp_raw[i]) - dlt[i]) : 0.0f;
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    pv[i] = fast_exp2(fmaf(__uint_as_float(s_raw[i]), scale2, -lse2[i]));
-                    dsv[i] = pv[i] * (__uint_as_float(dp_raw[i]) - dlt[i]);
-                }
-            }
-            // P^T and dS^T go back over the first 16 of the 32 columns this warp just read.
-            uint32_t packed[16];
-            pack_pairs(packed, pv);
-            sm100::tmem_st_32x16(tmem_st(b) + lane_base + part * 32, packed);
-            pack_pairs(packed, dsv);
-            sm100::tmem_st_32x16(tmem_dpt(b) + lane_base + part * 32, packed);
-            sm100::tmem_st_wait();
-            sm100::tc_fence_before_sync();
-            sm100::mbar_arrive(bar.operands_ready(b));
-            if (threadIdx.x == 64) { FB_TRACE(0, h, 3); }
-        }
-        if (threadIdx.x == 64) { FB_TRACE(0, 39, 0); }
-        if (ok && sm100::mbar_wait(bar.done(), 0, abort)) {
-            if (threadIdx.x == 64) { FB_TRACE(0, 39, 1); }
             sm100::tc_fence_after_sync();
             // Rows of dV/dK are keys; this warp writes 32 of the 64 columns. dS was kept
             // unscaled, so the score scale is applied to dK here.
@@ -783,17 +824,21 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             sm100::tc_fence_before_sync();
         }
     }
-    if (threadIdx.x == 64) { FB_TRACE(0, 39, 2); }
+    // A persistent CTA lets the next kernel in only when its own work is done: a
+    // dependent that became resident earlier was measured to slow this kernel down.
+    if (threadIdx.x == 0) {
+        fb::dependency_release();
+    }
     finish(abort_flag, tmem, 512, warp);
-    if (threadIdx.x == 64) { FB_TRACE(0, 39, 3); }
 }
 
 // ---- backward: dQ ---------------------------------------------------------------------------------
 //
-// One CTA per (head, 128 queries), 64 keys per sub-step: S = Q K^T and dP = dO V^T
-// (A = Q, dO from tensor memory) into double-buffered accumulators, dS written back
-// over dP as FP16 pairs, dQ += dS K accumulated in TMEM. Tensor memory: S at 0/64,
-// dP at 128/192, dQ 256, Q 320, dO 352.
+// Persistent CTAs over (head, 128 queries) items, the last query tile (most keys)
+// first; 64 keys per sub-step: S = Q K^T and dP = dO V^T (A = Q, dO from tensor
+// memory) into double-buffered accumulators, dS written back over dP as FP16 pairs,
+// dQ += dS K accumulated in TMEM. Items overlap as in the dK/dV kernel.
+// Tensor memory: S at 0/64, dP at 128/192, dQ 256, Q 320, dO 352.
 
 __global__ void __launch_bounds__(kBwdThreads, 1)
     fb_attention_dq(const __grid_constant__ AttnParams p) {
@@ -810,11 +855,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     const int warp = threadIdx.x / 32;
     const int lane = threadIdx.x % 32;
     const int bh_count = p.heads * p.seqs;
-    const int qb = p.blocks - 1 - static_cast<int>(blockIdx.x / bh_count);
-    const int bh = static_cast<int>(blockIdx.x % bh_count);
-    const int head = bh % p.heads;
-    const int seq = bh / p.heads;
-    const int steps = 2 * (qb + 1);  // 64-key sub-steps up to and including the diagonal tile
+    const int items = bh_count * p.blocks;
+    const int first_item = static_cast<int>(blockIdx.x);
+    const int stride = static_cast<int>(gridDim.x);
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -833,143 +876,190 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     const uint32_t tmem_q = tmem + 320, tmem_do = tmem + 352;
     volatile int* abort = &abort_flag;
     fb::dependency_wait();
-    if (threadIdx.x == 0) {
-        fb::dependency_release();
-    }
 
     if (warp == 0) {
         if (lane == 0) {
-            sm100::mbar_expect_tx(bar.resident(), 2 * kTileBytes);
-            tma_load_4d(q_tile, &p.map_q, bar.resident(), 0, qb * kTile, head, seq);
-            tma_load_4d(do_tile, &p.map_do, bar.resident(), 0, qb * kTile, head, seq);
             int stage = 0;
             uint32_t phase = 0;
-            for (int g = 0; g < steps; ++g) {
-                if (!sm100::mbar_wait(bar.stage_empty(stage), phase ^ 1u, abort)) {
+            bool ok = true;
+            int round = 0;
+            for (int item = first_item; ok && item < items; item += stride, ++round) {
+                const int qb = p.blocks - 1 - item / bh_count;
+                const int bh = item % bh_count;
+                const int head = bh % p.heads;
+                const int seq = bh / p.heads;
+                const int steps = 2 * (qb + 1);
+                // The Q/dO buffers are free once the item before was copied to tensor memory.
+                if (round > 0 && !sm100::mbar_wait(bar.a_ready(), (round - 1) & 1, abort)) {
                     break;
                 }
-                const uint32_t dst = ring + stage * 2 * kSubBytes;
-                sm100::mbar_expect_tx(bar.stage_full(stage), 2 * kSubBytes);
-                tma_load_4d(dst, &p.map_k64, bar.stage_full(stage), 0, g * kSub, head, seq);
-                tma_load_4d(dst + kSubBytes, &p.map_v64, bar.stage_full(stage), 0, g * kSub, head,
-                            seq);
-                if (++stage == kBwdStages) {
-                    stage = 0;
-                    phase ^= 1u;
+                sm100::mbar_expect_tx(bar.resident(), 2 * kTileBytes);
+                tma_load_4d(q_tile, &p.map_q, bar.resident(), 0, qb * kTile, head, seq);
+                tma_load_4d(do_tile, &p.map_do, bar.resident(), 0, qb * kTile, head, seq);
+                for (int g = 0; g < steps; ++g) {
+                    if (!sm100::mbar_wait(bar.stage_empty(stage), phase ^ 1u, abort)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t dst = ring + stage * 2 * kSubBytes;
+                    sm100::mbar_expect_tx(bar.stage_full(stage), 2 * kSubBytes);
+                    tma_load_4d(dst, &p.map_k64, bar.stage_full(stage), 0, g * kSub, head, seq);
+                    tma_load_4d(dst + kSubBytes, &p.map_v64, bar.stage_full(stage), 0, g * kSub,
+                                head, seq);
+                    if (++stage == kBwdStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            bool ok = sm100::mbar_wait(bar.a_ready(), 0, abort);
-            sm100::tc_fence_after_sync();
             const uint64_t k_desc = sm100::smem_desc_sw128(ring, 16, 1024);
             const uint64_t v_desc = sm100::smem_desc_sw128(ring + kSubBytes, 16, 1024);
-            auto issue_scores = [&](int g) -> bool {
-                const int stage = g % kBwdStages;
-                if (!sm100::mbar_wait(bar.stage_full(stage), (g / kBwdStages) & 1, abort)) {
-                    return false;
-                }
+            uint32_t before = 0;  // sub-steps of earlier items (always even)
+            bool ok = true;
+            int round = 0;
+            for (int item = first_item; ok && item < items; item += stride, ++round) {
+                const int steps = 2 * (p.blocks - item / bh_count);
+                ok = sm100::mbar_wait(bar.a_ready(), round & 1, abort);
                 sm100::tc_fence_after_sync();
-                const uint64_t k_sub = desc_advance(k_desc, stage * 2 * kSubBytes);
-                const uint64_t v_sub = desc_advance(v_desc, stage * 2 * kSubBytes);
+                auto issue_scores = [&](int g) -> bool {
+                    const uint32_t count = before + g;
+                    const int stage = count % kBwdStages;
+                    if (!sm100::mbar_wait(bar.stage_full(stage), (count / kBwdStages) & 1, abort)) {
+                        return false;
+                    }
+                    sm100::tc_fence_after_sync();
+                    const uint64_t k_sub = desc_advance(k_desc, stage * 2 * kSubBytes);
+                    const uint64_t v_sub = desc_advance(v_desc, stage * 2 * kSubBytes);
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks) {
-                    sm100::mma_f16_ts(tmem_s(g & 1), tmem_q + ks * 8, desc_advance(k_sub, ks * 32),
-                                      kIdescSub, ks > 0);
-                }
+                    for (int ks = 0; ks < 4; ++ks) {
+                        sm100::mma_f16_ts(tmem_s(g & 1), tmem_q + ks * 8,
+                                          desc_advance(k_sub, ks * 32), kIdescSub, ks > 0);
+                    }
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks) {
-                    sm100::mma_f16_ts(tmem_dp(g & 1), tmem_do + ks * 8,
-                                      desc_advance(v_sub, ks * 32), kIdescSub, ks > 0);
-                }
-                sm100::mma_commit(bar.scores_full(g & 1));
-                return true;
-            };
-            ok = ok && issue_scores(0);
-            for (int g = 0; ok && g < steps; ++g) {
-                const int b = g & 1;
-                if (g + 1 < steps && !issue_scores(g + 1)) {
-                    break;
-                }
-                if (!sm100::mbar_wait(bar.operands_ready(b), (g >> 1) & 1, abort)) {
-                    break;
-                }
-                sm100::tc_fence_after_sync();
-                const int stage = g % kBwdStages;
-                const uint64_t k_sub = desc_advance(k_desc, stage * 2 * kSubBytes);
-                // dQ += dS K over this sub-step's 64 keys (the K tile read MN-major).
+                    for (int ks = 0; ks < 4; ++ks) {
+                        sm100::mma_f16_ts(tmem_dp(g & 1), tmem_do + ks * 8,
+                                          desc_advance(v_sub, ks * 32), kIdescSub, ks > 0);
+                    }
+                    sm100::mma_commit(bar.scores_full(g & 1));
+                    return true;
+                };
+                ok = ok && issue_scores(0);
+                for (int g = 0; ok && g < steps; ++g) {
+                    const int b = g & 1;
+                    const uint32_t count = before + g;
+                    if (g + 1 < steps && !issue_scores(g + 1)) {
+                        ok = false;
+                        break;
+                    }
+                    if (!sm100::mbar_wait(bar.operands_ready(b), (count >> 1) & 1, abort)) {
+                        ok = false;
+                        break;
+                    }
+                    sm100::tc_fence_after_sync();
+                    const int stage = count % kBwdStages;
+                    const uint64_t k_sub = desc_advance(k_desc, stage * 2 * kSubBytes);
+                    // dQ += dS K over this sub-step's 64 keys (the K tile read MN-major).
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks) {
-                    sm100::mma_f16_ts(tmem_dq, tmem_dp(b) + (ks >> 1) * 32 + (ks & 1) * 8,
-                                      desc_advance(k_sub, ks * 2048), kIdescPV, (g | ks) != 0);
+                    for (int ks = 0; ks < 4; ++ks) {
+                        sm100::mma_f16_ts(tmem_dq, tmem_dp(b) + (ks >> 1) * 32 + (ks & 1) * 8,
+                                          desc_advance(k_sub, ks * 2048), kIdescPV, (g | ks) != 0);
+                    }
+                    sm100::mma_commit(bar.stage_empty(stage));
+                    if (g + 1 == steps) {
+                        sm100::mma_commit(bar.done());
+                    }
                 }
-                sm100::mma_commit(bar.stage_empty(stage));
-                if (g + 1 == steps) {
-                    sm100::mma_commit(bar.done());
-                }
+                before += steps;
             }
         }
     } else {
         const int quadrant = warp % 4;
         const int part = (warp - 2) / 4;                 // which 32 of the 64 key columns
         const int row = quadrant * 32 + lane;            // query row inside the tile
-        const int q_index = qb * kTile + row;
-        const bool row_valid = q_index < p.length;
         const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
         const float scale2 = p.scale * kLog2e;
-        float lse2 = INFINITY;
-        float dlt = 0.0f;
-        if (row_valid) {
-            lse2 = p.lse[static_cast<size_t>(bh) * p.length + q_index] * kLog2e;
-            dlt = p.delta[static_cast<size_t>(bh) * p.length + q_index];
-        }
-        bool ok = sm100::mbar_wait(bar.resident(), 0, abort);
-        if (ok) {
-            // Q and dO become the A operands of the score MMAs.
+        // Q and dO of an item become the A operands of its score MMAs.
+        auto install = [&](int round) -> bool {
+            if (!sm100::mbar_wait(bar.resident(), round & 1, abort)) {
+                return false;
+            }
             tile_row_to_tmem(tmem_q + lane_base, q_tile, row, part);
             tile_row_to_tmem(tmem_do + lane_base, do_tile, row, part);
             sm100::tmem_st_wait();
             sm100::tc_fence_before_sync();
             sm100::mbar_arrive(bar.a_ready());
-        }
-        for (int g = 0; ok && g < steps; ++g) {
-            const int b = g & 1;
-            if (!sm100::mbar_wait(bar.scores_full(b), (g >> 1) & 1, abort)) {
+            return true;
+        };
+        uint32_t before = 0;
+        int round = 0;
+        bool ok = first_item < items && install(0);
+        for (int item = first_item; ok && item < items; item += stride, ++round) {
+            const int qb = p.blocks - 1 - item / bh_count;
+            const int bh = item % bh_count;
+            const int head = bh % p.heads;
+            const int seq = bh / p.heads;
+            const int steps = 2 * (qb + 1);  // 64-key sub-steps up to and including the diagonal
+            const int q_index = qb * kTile + row;
+            const bool row_valid = q_index < p.length;
+            float lse2 = INFINITY;
+            float dlt = 0.0f;
+            if (row_valid) {
+                lse2 = p.lse[static_cast<size_t>(bh) * p.length + q_index] * kLog2e;
+                dlt = p.delta[static_cast<size_t>(bh) * p.length + q_index];
+            }
+            for (int g = 0; ok && g < steps; ++g) {
+                const int b = g & 1;
+                const uint32_t count = before + g;
+                if (!sm100::mbar_wait(bar.scores_full(b), (count >> 1) & 1, abort)) {
+                    ok = false;
+                    break;
+                }
+                sm100::tc_fence_after_sync();
+                uint32_t s_raw[32];
+                uint32_t dp_raw[32];
+                sm100::tmem_ld_32x32(tmem_s(b) + lane_base + part * 32, s_raw);
+                sm100::tmem_ld_32x32(tmem_dp(b) + lane_base + part * 32, dp_raw);
+                sm100::tmem_ld_wait();
+                const int k0 = g * kSub + part * 32;  // first key of my columns
+                float dsv[32];
+                if (g + 2 >= steps) {
+                    // The diagonal tile: keys after the query are masked.
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const float e = fast_exp2(fmaf(__uint_as_float(s_raw[i]), scale2, -lse2));
+                        dsv[i] =
+                            (k0 + i <= q_index) ? e * (__uint_as_float(dp_raw[i]) - dlt) : 0.0f;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const float e = fast_exp2(fmaf(__uint_as_float(s_raw[i]), scale2, -lse2));
+                        dsv[i] = e * (__uint_as_float(dp_raw[i]) - dlt);
+                    }
+                }
+                // dS goes back over the first 16 of the 32 dP columns this warp just read.
+                uint32_t packed[16];
+                pack_pairs(packed, dsv);
+                sm100::tmem_st_32x16(tmem_dp(b) + lane_base + part * 32, packed);
+                sm100::tmem_st_wait();
+                sm100::tc_fence_before_sync();
+                sm100::mbar_arrive(bar.operands_ready(b));
+            }
+            before += steps;
+            if (!ok) {
+                break;
+            }
+            if (item + stride < items && !install(round + 1)) {
                 ok = false;
                 break;
             }
-            sm100::tc_fence_after_sync();
-            uint32_t s_raw[32];
-            uint32_t dp_raw[32];
-            sm100::tmem_ld_32x32(tmem_s(b) + lane_base + part * 32, s_raw);
-            sm100::tmem_ld_32x32(tmem_dp(b) + lane_base + part * 32, dp_raw);
-            sm100::tmem_ld_wait();
-            const int k0 = g * kSub + part * 32;  // first key of my columns
-            float dsv[32];
-            if (g + 2 >= steps) {
-                // The diagonal tile: keys after the query are masked.
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float e = fast_exp2(fmaf(__uint_as_float(s_raw[i]), scale2, -lse2));
-                    dsv[i] = (k0 + i <= q_index) ? e * (__uint_as_float(dp_raw[i]) - dlt) : 0.0f;
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float e = fast_exp2(fmaf(__uint_as_float(s_raw[i]), scale2, -lse2));
-                    dsv[i] = e * (__uint_as_float(dp_raw[i]) - dlt);
-                }
+            if (!sm100::mbar_wait(bar.done(), round & 1, abort)) {
+                ok = false;
+                break;
             }
-            // dS goes back over the first 16 of the 32 dP columns this warp just read.
-            uint32_t packed[16];
-            pack_pairs(packed, dsv);
-            sm100::tmem_st_32x16(tmem_dp(b) + lane_base + part * 32, packed);
-            sm100::tmem_st_wait();
-            sm100::tc_fence_before_sync();
-            sm100::mbar_arrive(bar.operands_ready(b));
-        }
-        if (ok && sm100::mbar_wait(bar.done(), 0, abort)) {
             sm100::tc_fence_after_sync();
             uint32_t raw[32];
             sm100::tmem_ld_32x32(tmem_dq + lane_base + part * 32, raw);
@@ -989,6 +1079,11 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             }
             sm100::tc_fence_before_sync();
         }
+    }
+    // A persistent CTA lets the next kernel in only when its own work is done: a
+    // dependent that became resident earlier was measured to slow this kernel down.
+    if (threadIdx.x == 0) {
+        fb::dependency_release();
     }
     finish(abort_flag, tmem, 512, warp);
 }
@@ -1125,7 +1220,9 @@ cudaError_t attention_backward(const AttentionView& dq, const AttentionView& dk,
     }
     p.lse = const_cast<float*>(lse);
     p.delta = delta;
-    const unsigned grid = static_cast<unsigned>(shape.sequences * shape.heads * p.blocks);
+    // One persistent CTA per SM (fewer when there are fewer items).
+    const unsigned items = static_cast<unsigned>(shape.sequences * shape.heads * p.blocks);
+    const unsigned bwd_grid = std::min(items, static_cast<unsigned>(sms));
 
     static bool dkv_configured = false;
     e = configure(fb_attention_dkv, kBwdSmem, &dkv_configured);
@@ -1138,7 +1235,8 @@ cudaError_t attention_backward(const AttentionView& dq, const AttentionView& dk,
     p.out_row = dk.row_stride;
     p.out_head = dk.head_stride;
     p.out_seq = dk.sequence_stride;
-    e = fb::launch_dependent(fb_attention_dkv, dim3(grid), dim3(kBwdThreads), kBwdSmem, stream, p);
+    e = fb::launch_dependent(fb_attention_dkv, dim3(bwd_grid), dim3(kBwdThreads), kBwdSmem, stream,
+                             p);
     if (e != cudaSuccess) {
         return e;
     }
@@ -1152,7 +1250,8 @@ cudaError_t attention_backward(const AttentionView& dq, const AttentionView& dk,
     p.out_row = dq.row_stride;
     p.out_head = dq.head_stride;
     p.out_seq = dq.sequence_stride;
-    return fb::launch_dependent(fb_attention_dq, dim3(grid), dim3(kBwdThreads), kBwdSmem, stream, p);
+    return fb::launch_dependent(fb_attention_dq, dim3(bwd_grid), dim3(kBwdThreads), kBwdSmem, stream,
+                                p);
 }
 
 cudaError_t attention_error_flag(int* value, bool reset) {
@@ -1195,12 +1294,6 @@ fb::AttentionView heads_view(const void* base, size_t batches, size_t length) {
 }  // namespace
 
 extern "C" {
-
-#ifdef FB_ATTN_TRACE
-__attribute__((visibility("default"))) int flint_b200_debug_trace(void* host, size_t bytes) {
-    return static_cast<int>(cudaMemcpyFromSymbol(host, fb::g_trace, bytes));
-}
-#endif
 
 flint_status flint_b200_attention_forward(void* o, void* lse, const void* q, const void* k,
                                           const void* v, size_t batches, size_t length,
