@@ -540,6 +540,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     const int items = bh_count * p.blocks;
     const int first_item = static_cast<int>(blockIdx.x);
     const int stride = static_cast<int>(gridDim.x);
+    // Items are dealt in rounds of gridDim.x, alternately in ascending and descending CTA
+    // order (the list is sorted by work, so this evens the CTAs' totals out); a result
+    // >= items ends the list, and only the last round can be short.
+    auto item_of = [&](int round) {
+        const int slot = (round & 1) != 0 ? stride - 1 - first_item : first_item;
+        return round * stride + slot;
+    };
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -565,7 +572,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             uint32_t phase = 0;
             bool ok = true;
             int round = 0;
-            for (int item = first_item; ok && item < items; item += stride, ++round) {
+            for (int item = item_of(0); ok && item < items; item = item_of(++round)) {
                 const int kb = item / bh_count;
                 const int bh = item % bh_count;
                 const int head = bh % p.heads;
@@ -618,7 +625,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             uint32_t before = 0;  // sub-steps of earlier items (always even)
             bool ok = true;
             int round = 0;
-            for (int item = first_item; ok && item < items; item += stride, ++round) {
+            for (int item = item_of(0); ok && item < items; item = item_of(++round)) {
                 const int steps = 2 * (p.blocks - item / bh_count);
                 ok = sm100::mbar_wait(bar.a_ready(), round & 1, abort);
                 sm100::tc_fence_after_sync();
@@ -704,7 +711,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         uint32_t before = 0;
         int round = 0;
         bool ok = first_item < items && install(0);
-        for (int item = first_item; ok && item < items; item += stride, ++round) {
+        for (int item = item_of(0); ok && item < items; item = item_of(++round)) {
             const int kb = item / bh_count;
             const int bh = item % bh_count;
             const int head = bh % p.heads;
@@ -787,7 +794,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             }
             // The next item's K/V go in now, so that its first score MMAs run while this
             // item's gradients are written out.
-            if (item + stride < items && !install(round + 1)) {
+            if (item_of(round + 1) < items && !install(round + 1)) {
                 ok = false;
                 break;
             }
@@ -858,6 +865,13 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     const int items = bh_count * p.blocks;
     const int first_item = static_cast<int>(blockIdx.x);
     const int stride = static_cast<int>(gridDim.x);
+    // Items are dealt in rounds of gridDim.x, alternately in ascending and descending CTA
+    // order (the list is sorted by work, so this evens the CTAs' totals out); a result
+    // >= items ends the list, and only the last round can be short.
+    auto item_of = [&](int round) {
+        const int slot = (round & 1) != 0 ? stride - 1 - first_item : first_item;
+        return round * stride + slot;
+    };
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -883,7 +897,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             uint32_t phase = 0;
             bool ok = true;
             int round = 0;
-            for (int item = first_item; ok && item < items; item += stride, ++round) {
+            for (int item = item_of(0); ok && item < items; item = item_of(++round)) {
                 const int qb = p.blocks - 1 - item / bh_count;
                 const int bh = item % bh_count;
                 const int head = bh % p.heads;
@@ -920,7 +934,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             uint32_t before = 0;  // sub-steps of earlier items (always even)
             bool ok = true;
             int round = 0;
-            for (int item = first_item; ok && item < items; item += stride, ++round) {
+            for (int item = item_of(0); ok && item < items; item = item_of(++round)) {
                 const int steps = 2 * (p.blocks - item / bh_count);
                 ok = sm100::mbar_wait(bar.a_ready(), round & 1, abort);
                 sm100::tc_fence_after_sync();
@@ -996,7 +1010,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         uint32_t before = 0;
         int round = 0;
         bool ok = first_item < items && install(0);
-        for (int item = first_item; ok && item < items; item += stride, ++round) {
+        for (int item = item_of(0); ok && item < items; item = item_of(++round)) {
             const int qb = p.blocks - 1 - item / bh_count;
             const int bh = item % bh_count;
             const int head = bh % p.heads;
@@ -1052,7 +1066,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             if (!ok) {
                 break;
             }
-            if (item + stride < items && !install(round + 1)) {
+            if (item_of(round + 1) < items && !install(round + 1)) {
                 ok = false;
                 break;
             }
