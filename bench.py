@@ -234,9 +234,6 @@ def run_flint(args):
     group = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # The gradient all-reduce needs ~40 GB/s to hide behind backward; a few NCCL CTAs
-        # give that and leave the persistent GEMM and attention kernels their SMs.
-        os.environ.setdefault("NCCL_MAX_CTAS", "4")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         group = dist.group.WORLD
 
