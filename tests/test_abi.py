@@ -142,3 +142,11 @@ def test_forward_only_memory_plan_needs_no_gpu(flint):
     assert status == flint_b200.ERROR_INVALID_ARGUMENT
     assert "layers (0) must be from 1 to 1024" in flint.last_error()
     assert flint.lib.flint_gpt2_parameter_count(None) == 0
+
+
+def test_the_kernel_bench_module_lists_its_groups():
+    """python -m flint_b200.kernel_bench is the per-kernel counterpart of the reference's C++
+    bench harness; importing it needs no GPU."""
+    from flint_b200 import kernel_bench
+
+    assert set(kernel_bench.GROUPS) == {"gemm", "attention", "rowwise", "reductions"}

@@ -22,8 +22,10 @@ def rel_error(got, want):
     return ((got - want).norm() / want.norm().clamp_min(1e-300)).item()
 
 
+# The last two cases give the backward kernels more items than a B200 has SMs (39 x 8 = 312 and
+# 101 x 3 = 303 items for 148 persistent CTAs): two full rounds and a short third one.
 @pytest.mark.parametrize("batches, length", [(4, 128), (3, 256), (2, 1024), (5, 40), (2, 136),
-                                             (1, 8), (7, 520)])
+                                             (1, 8), (7, 520), (39, 1024), (101, 328)])
 def test_attention_forward_and_backward(flint, batches, length):
     g = torch.Generator().manual_seed(length)
     q, k, v, d_o = (torch.randn(batches, length, 64, generator=g).half() for _ in range(4))
@@ -60,3 +62,25 @@ def test_attention_is_deterministic_and_row_zero_copies_v(flint):
     torch.cuda.synchronize()
     assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
     assert torch.equal(outs[0][:, 0].view(torch.int16), v[:, 0].view(torch.int16))
+
+
+def test_attention_backward_is_deterministic_over_many_items(flint):
+    """Persistent CTAs take several items each; every output element still comes from one
+    CTA in a fixed order, so two runs agree bit for bit."""
+    batches, length = 60, 1024
+    g = torch.Generator().manual_seed(5)
+    q, k, v, d_o = (torch.randn(batches, length, 64, generator=g).half().to(DEV) for _ in range(4))
+    o = torch.zeros(batches, length, 64, dtype=torch.half, device=DEV)
+    lse = torch.zeros(batches, length, device=DEV)
+    flint.attention_forward(o, lse, q, k, v, batches, length, 64, 0.125)
+    runs = []
+    for fill in (2.0, -5.0):
+        grads = [torch.full((batches, length, 64), fill, dtype=torch.half, device=DEV)
+                 for _ in range(3)]
+        delta = torch.full((batches, length), fill, device=DEV)
+        flint.attention_backward(*grads, d_o, o, lse, delta, q, k, v, batches, length, 64, 0.125)
+        runs.append(grads)
+    torch.cuda.synchronize()
+    assert not flint.kernel_fault()
+    for a, b in zip(*runs):
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16))

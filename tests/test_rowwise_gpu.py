@@ -372,3 +372,45 @@ def test_embedding_backward_matches_the_oracle_at_gpt2_size(flint):
     want_wte, want_wpe, *_ = oracle.embedding_backward(dx, tokens, seqs, length, vocab)
     assert same_bits(dwte, want_wte)
     assert same_bits(dwpe, want_wpe)
+
+
+def test_cross_entropy_with_extreme_and_non_finite_logits(flint):
+    """The exponential's clamp and NaN handling: logits spanning FP16's range, -inf entries
+    (probability 0), and rows with +inf or NaN (every output of such a row is NaN, as in the
+    float64 reference)."""
+    rows, vocab, cols = 6, 1003, 1008
+    g = torch.Generator().manual_seed(3)
+    logits = (torch.randn(rows, cols, generator=g) * 3).half()
+    logits[0, :50] = -65504.0           # far below the row maximum
+    logits[0, 60] = 65504.0
+    logits[1] = -65504.0                # a very negative maximum
+    logits[1, 7] = -65000.0
+    logits[2, 100:200] = float("-inf")
+    logits[3, 5] = float("inf")
+    logits[4, 9] = float("nan")
+    targets = torch.tensor([60, 7, 3, 1, 2, 500])
+    scale = 4.0
+    dl = torch.full((rows, cols), 9.0, dtype=torch.half, device=DEV)
+    loss = torch.zeros(rows, device=DEV)
+    flint.softmax_cross_entropy(dl, loss, logits.to(DEV), tokens16(targets.numpy()), scale, rows,
+                                vocab, cols)
+    torch.cuda.synchronize()
+    got = dl.cpu().numpy().astype(np.float64)
+    got_loss = loss.cpu().numpy()
+    finite_rows = [0, 1, 2, 5]
+    x = logits.numpy().astype(np.float64)[:, :vocab]
+    for r in finite_rows:
+        m = x[r].max()
+        e = np.exp(x[r] - m)
+        p = e / e.sum()
+        want = p * scale
+        want[targets[r]] = (p[targets[r]] - 1.0) * scale
+        ulp16 = np.spacing(np.abs(want).astype(np.float16)).astype(np.float64)
+        assert (np.abs(got[r, :vocab] - want) <= ulp16 + 2.0 ** -23 * scale).all(), r
+        want_loss = np.log(e.sum()) - (x[r, targets[r]] - m)
+        assert abs(got_loss[r] - want_loss) <= 4e-6 * max(1.0, abs(want_loss)), r
+        assert (got[r, vocab:] == 0).all()
+    assert (got[2, 100:200] == 0).all()
+    for r in (3, 4):
+        assert np.isnan(got[r, :vocab]).all(), r
+        assert np.isnan(got_loss[r]), r
