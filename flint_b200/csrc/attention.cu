@@ -397,6 +397,7 @@ struct View {
     long long row, head, seq;
 };
 
+// Eight lanes per row (16 bytes of dO and of O each), four rows per warp and step.
 __global__ void __launch_bounds__(256)
     fb_attention_delta(float* __restrict__ delta, View d_o, View o, int length, int heads,
                        int seqs) {
@@ -404,23 +405,33 @@ __global__ void __launch_bounds__(256)
     fb::dependency_release();
     const long long rows = static_cast<long long>(length) * heads * seqs;
     const int lane = threadIdx.x % 32;
-    for (long long r = blockIdx.x * 8LL + threadIdx.x / 32; r < rows; r += gridDim.x * 8LL) {
+    const int piece = lane % 8;  // which 8 of the row's 64 values
+    const long long first = (blockIdx.x * 8LL + threadIdx.x / 32) * 4 + lane / 8;
+    const long long stride = gridDim.x * 8LL * 4;
+    for (long long r0 = first; r0 - lane / 8 < rows; r0 += stride) {
+        const bool valid = r0 < rows;
+        const long long r = valid ? r0 : rows - 1;
         const int t = static_cast<int>(r % length);
         const long long bh = r / length;
         const int head = static_cast<int>(bh % heads);
         const long long seq = bh / heads;
-        const __half2 a = *reinterpret_cast<const __half2*>(
-            d_o.base + seq * d_o.seq + head * d_o.head + t * d_o.row + 2 * lane);
-        const __half2 b = *reinterpret_cast<const __half2*>(
-            o.base + seq * o.seq + head * o.head + t * o.row + 2 * lane);
-        const float2 fa = __half22float2(a);
-        const float2 fb2 = __half22float2(b);
-        float s = fa.x * fb2.x + fa.y * fb2.y;
+        const uint4 a = *reinterpret_cast<const uint4*>(d_o.base + seq * d_o.seq + head * d_o.head +
+                                                        t * d_o.row + 8 * piece);
+        const uint4 b = *reinterpret_cast<const uint4*>(o.base + seq * o.seq + head * o.head +
+                                                        t * o.row + 8 * piece);
+        float fa[8];
+        float fo[8];
+        fb::unpack8(fa, a);
+        fb::unpack8(fo, b);
+        float s = 0.0f;
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) {
-            s += __shfl_xor_sync(fb::kFullMask, s, off);
+        for (int i = 0; i < 8; ++i) {
+            s = fmaf(fa[i], fo[i], s);
         }
-        if (lane == 0) {
+        s += __shfl_xor_sync(fb::kFullMask, s, 4);
+        s += __shfl_xor_sync(fb::kFullMask, s, 2);
+        s += __shfl_xor_sync(fb::kFullMask, s, 1);
+        if (valid && piece == 0) {
             delta[r] = s;
         }
     }
@@ -1222,7 +1233,7 @@ cudaError_t attention_backward(const AttentionView& dq, const AttentionView& dk,
     int sms = 148;
     sm_count(&sms);
     const unsigned delta_grid =
-        static_cast<unsigned>(std::min<long long>((rows + 7) / 8, sms * 16LL));
+        static_cast<unsigned>(std::min<long long>((rows + 31) / 32, sms * 16LL));
     const View vdo{static_cast<const __half*>(d_o.base), d_o.row_stride, d_o.head_stride,
                    d_o.sequence_stride};
     const View vo{static_cast<const __half*>(o.base), o.row_stride, o.head_stride,
