@@ -238,7 +238,8 @@ def run_flint(args):
         group = dist.group.WORLD
 
     flint = flint_b200.Flint()
-    config = TrainerConfig(sequences=SEQUENCES, length=LENGTH)
+    config = TrainerConfig(sequences=SEQUENCES, length=LENGTH,
+                           overlap_update=os.environ.get("FLINT_B200_OVERLAP_UPDATE", "1") != "0")
     trainer = Trainer(flint, config, group=group, seed=1234)
     rows = SEQUENCES * LENGTH
 

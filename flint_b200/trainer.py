@@ -46,6 +46,7 @@ class TrainerConfig:
     growth_interval: int = 2000
     max_grad_norm: float = 0.0   # 0 disables clipping
     flash_attention: bool = True
+    overlap_update: bool = True  # ranks > 1: update most of the model under the last all-reduce
 
 
 class _DeviceView:
@@ -169,6 +170,13 @@ class Trainer:
             tensors.append((address, self.m.data_ptr() + offset, self.v.data_ptr() + offset, grad,
                             half.get(name), rows * cols, decay))
         self.plan, self.plan_items = flint.adamw_plan(tensors)
+        # With more than one rank the update is pipelined with the last all-reduce (see
+        # step()): one plan for the embeddings (the last bucket, the first two tensors of
+        # the arena) and one for everything else.
+        self.body_offset = (gradients[2][1] - arena) // 4  # first float after wte and wpe
+        self.split_plans = None
+        if self.world > 1:
+            self.split_plans = (flint.adamw_plan(tensors[:2]), flint.adamw_plan(tensors[2:]))
         self.found = torch.zeros(1, dtype=torch.int32, device="cuda")
         self.norm_squared = torch.zeros(1, dtype=torch.float64, device="cuda")
         self.scaler = LossScaler(config.loss_scale, config.growth_interval)
@@ -199,14 +207,31 @@ class Trainer:
 
     # -- one optimizer step ---------------------------------------------------------------
 
+    def _pipelined(self) -> bool:
+        """Whether the update overlaps the last all-reduce: more than one rank, and no
+        gradient clipping (the clip coefficient needs the norm of all reduced gradients)."""
+        return self.world > 1 and self.config.overlap_update and self.config.max_grad_norm <= 0
+
     def _on_bucket(self, bucket: int, address: int, nbytes: int) -> None:
         import torch.distributed as dist
 
+        last = bucket == self.config.layers + 1  # ln_f, the blocks, then the embeddings
+        view = device_tensor(address, nbytes // 4)
+        if last and self._pipelined():
+            # This rank's embedding gradients are checked before they are summed: a
+            # non-finite value on any rank makes the sum non-finite, so the maximum of the
+            # ranks' flags (a four-byte all-reduce, ahead of the big one) is the flag the
+            # summed gradients would raise.
+            self.flint.check_gradients(view, nbytes // 4, 1.0 / self.scaler.scale, self.found,
+                                       None)
         ready = torch.cuda.Event()
         ready.record(self.stream)
         self.comm_stream.wait_event(ready)
-        view = device_tensor(address, nbytes // 4)
         with torch.cuda.stream(self.comm_stream):
+            if last and self._pipelined():
+                dist.all_reduce(self.found, op=dist.ReduceOp.MAX, group=self.group)
+                self._flag_ready = torch.cuda.Event()
+                self._flag_ready.record(self.comm_stream)
             dist.all_reduce(view, op=dist.ReduceOp.SUM, group=self.group)
 
     def step(self, tokens: torch.Tensor, targets: torch.Tensor) -> None:
@@ -215,6 +240,28 @@ class Trainer:
         c = self.config
         scale = cross_entropy_scale(self.scaler.scale, self.rows, self.world)
         self.model.forward(tokens, targets, scale)
+        inverse = 1.0 / self.scaler.scale
+        if self._pipelined():
+            # Every bucket but the last is summed while backward runs; the last one (the
+            # embeddings, a third of the bytes) would otherwise be waited for with nothing
+            # to do. Its non-finite flag is settled early (see _on_bucket), so the rest of
+            # the model is checked and updated while that all-reduce is in flight.
+            self.found.zero_()
+            self.model.backward(tokens, False, callback=self._on_bucket)
+            done = torch.cuda.Event()
+            done.record(self.comm_stream)
+            self.stream.wait_event(self._flag_ready)
+            body = self.gradients[self.body_offset:]
+            self.flint.check_gradients(body, body.numel(), inverse, self.found, None)
+            self.step_count += 1
+            (embed_plan, embed_items), (body_plan, body_items) = self.split_plans
+            step = self.step_count - self.skipped
+            self.flint.adamw_run(body_plan, body_items, c.lr, c.beta1, c.beta2, c.eps, inverse, step,
+                                 self.found)
+            self.stream.wait_event(done)
+            self.flint.adamw_run(embed_plan, embed_items, c.lr, c.beta1, c.beta2, c.eps, inverse,
+                                 step, self.found)
+            return
         if self.world > 1:
             self.model.backward(tokens, False, callback=self._on_bucket)
             done = torch.cuda.Event()
@@ -226,7 +273,6 @@ class Trainer:
         clip = c.max_grad_norm > 0
         if clip:
             self.norm_squared.zero_()
-        inverse = 1.0 / self.scaler.scale
         self.flint.check_gradients(self.gradients, self.gradient_count, inverse, self.found,
                                    self.norm_squared if clip else None)
         grad_scale = inverse
