@@ -105,7 +105,8 @@ cudaError_t sm_count(int* sms) {
 }
 
 cudaError_t encode_rows_map(void* map, const void* base, size_t rows, size_t cols,
-                            int element_bytes, unsigned box_cols, unsigned box_rows) {
+                            int element_bytes, unsigned box_cols, unsigned box_rows,
+                            int swizzle_bytes) {
     using Encode = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                 const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -132,7 +133,9 @@ cudaError_t encode_rows_map(void* map, const void* base, size_t rows, size_t col
         element_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
     const CUresult r = encode(static_cast<CUtensorMap*>(map), type, 2, const_cast<void*>(base), dims,
                               strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                                  : CU_TENSOR_MAP_SWIZZLE_NONE,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }

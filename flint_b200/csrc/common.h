@@ -85,11 +85,12 @@ cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, s
 // Number of SMs of the current device (cached per device index).
 cudaError_t sm_count(int* sms);
 
-// Tensor map over a row-major matrix [rows, cols] of 2- or 4-byte elements (no
-// swizzle, zero fill outside), for boxes of box_cols x box_rows. The row pitch
-// must be a multiple of 16 bytes and both extents below 2^32.
+// Tensor map over a row-major matrix [rows, cols] of 2- or 4-byte elements (zero
+// fill outside; swizzle_bytes 0 or 64), for boxes of box_cols x box_rows. The row
+// pitch must be a multiple of 16 bytes and both extents below 2^32.
 cudaError_t encode_rows_map(void* map, const void* base, size_t rows, size_t cols,
-                            int element_bytes, unsigned box_cols, unsigned box_rows);
+                            int element_bytes, unsigned box_cols, unsigned box_rows,
+                            int swizzle_bytes = 0);
 
 // flint_layernorm_backward's kernels without the argument checks, for the model
 // assembly; dx_half, when not null, also receives dx rounded to FP16 (the next

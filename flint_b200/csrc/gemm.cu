@@ -52,6 +52,9 @@ __device__ int g_gemm_error = 0;
 struct GemmParams {
     CUtensorMap map_a;
     CUtensorMap map_b;
+    CUtensorMap map_y;    // FP16 outputs of the pair kernel leave through TMA stores
+    CUtensorMap map_pre;  // bias+GELU: the pre-activation output
+    int tma_out;          // the two maps above are valid
     void* y;
     void* aux_out;        // bias+GELU: the pre-activation output
     const void* aux_in;   // dGELU: pre-activations; residual: the FP32 residual
@@ -331,6 +334,36 @@ __device__ __forceinline__ uint4 pack_half8(const float* v) {
     return q;
 }
 
+// FP16 chunks that leave by a TMA store are staged row-major, 64 bytes per row, in
+// the tensor map's 64-byte swizzle (16-byte piece c of row r at c ^ ((r >> 1) & 3)):
+// lane = row stores are conflict-free and the copy engine undoes the swizzle. The
+// store is asynchronous: the warp goes on to its next chunk and only waits, before it
+// overwrites the slot, for the engine to have read it.
+__device__ __forceinline__ void stage_row_for_store(uint32_t slot, int row, const float* v) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        st_shared_v4(slot + row * 64 + ((c ^ ((row >> 1) & 3)) << 4), pack_half8(v + 8 * c));
+    }
+}
+
+__device__ __forceinline__ void store_wait_slots_read() {
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
+__device__ __forceinline__ void store_wait_all() {
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
+// One lane: the staged 32 x 32 chunk to rows [row, row + 32), columns [col, col + 32);
+// parts outside the matrix are clipped by the copy engine.
+__device__ __forceinline__ void store_chunk_async(const CUtensorMap* map, uint32_t slot, int col,
+                                                  int row) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+        ::"l"(reinterpret_cast<uint64_t>(map)), "r"(slot), "r"(col), "r"(row)
+        : "memory");
+}
+
 // Moves the warp's staged FP16 chunk (4 slots per row) to `out` (row-major, ld = n).
 __device__ __forceinline__ void flush_half_chunk(uint32_t stage, __half* out_chunk, size_t n,
                                                  int rows_left, int valid, int lane) {
@@ -399,6 +432,18 @@ __device__ __forceinline__ void load_aux(Aux<E>& aux, const GemmParams& p, size_
     }
 }
 
+// This lane's bias value for a chunk starting at column `col` (0 for the other
+// epilogues and past the last column).
+template <Epilogue E>
+__device__ __forceinline__ float load_bias_lane(const GemmParams& p, int col, int lane) {
+    if constexpr (E == Epilogue::kBias || E == Epilogue::kBiasGelu ||
+                  E == Epilogue::kBiasResidual) {
+        return col + lane < p.n ? __ldg(p.bias + col + lane) : 0.0f;
+    } else {
+        return 0.0f;
+    }
+}
+
 // The whole warp calls this for one 32 x 32 chunk whose top-left element is
 // (row0, col). acc holds this lane's row. Requires n % 8 == 0 (FP16 outputs) or
 // n % 4 == 0 (FP32 outputs).
@@ -406,7 +451,7 @@ template <Epilogue E>
 __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t stage,
                                             size_t batch_offset, long long split, size_t row0,
                                             int col, float (&acc)[32], int valid, int lane,
-                                            const Aux<E>& aux) {
+                                            const Aux<E>& aux, float bias_lane) {
     const size_t n = static_cast<size_t>(p.n);
     const size_t at0 = batch_offset + row0 * n + col;  // the chunk's first element
     const long long rows_long = static_cast<long long>(p.m) - static_cast<long long>(row0);
@@ -414,17 +459,12 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t stage,
 
     if constexpr (E == Epilogue::kBias || E == Epilogue::kBiasGelu ||
                   E == Epilogue::kBiasResidual) {
-        // n is a multiple of 4 on this path and col of 32: whole 16-byte groups.
-        const float4* bias = reinterpret_cast<const float4*>(p.bias + col);
+        // Lane j holds bias[col + j] (fetched by the caller a chunk ahead, zero past the
+        // matrix's edge); every lane needs all 32, so they are passed round by shuffles
+        // instead of each lane waiting on its own loads.
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-            if (g * 4 < valid) {
-                const float4 b = __ldg(bias + g);
-                acc[4 * g] = __fadd_rn(acc[4 * g], b.x);
-                acc[4 * g + 1] = __fadd_rn(acc[4 * g + 1], b.y);
-                acc[4 * g + 2] = __fadd_rn(acc[4 * g + 2], b.z);
-                acc[4 * g + 3] = __fadd_rn(acc[4 * g + 3], b.w);
-            }
+        for (int j = 0; j < 32; ++j) {
+            acc[j] = __fadd_rn(acc[j], __shfl_sync(0xffffffffu, bias_lane, j));
         }
     }
     if constexpr (E == Epilogue::kScale) {
@@ -496,6 +536,36 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t stage,
                     acc[c * 8 + 2 * j + 1] = __fmul_rn(acc[c * 8 + 2 * j + 1], g1);
                 }
             }
+        }
+        if (p.tma_out != 0) {
+            // Asynchronous stores: wait until the copy engine has read what this slot held.
+            if (lane == 0) {
+                store_wait_slots_read();
+            }
+            __syncwarp();
+            if constexpr (E == Epilogue::kBiasGelu) {
+                stage_row_for_store(stage, lane, acc);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    fb::f2_unpack(gelu_tanh2(fb::f2_pack(acc[2 * j], acc[2 * j + 1])), acc[2 * j],
+                                  acc[2 * j + 1]);
+                }
+                stage_row_for_store(stage + 2048u, lane, acc);
+            } else {
+                stage_row_for_store(stage, lane, acc);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                if constexpr (E == Epilogue::kBiasGelu) {
+                    store_chunk_async(&p.map_pre, stage, col, static_cast<int>(row0));
+                    store_chunk_async(&p.map_y, stage + 2048u, col, static_cast<int>(row0));
+                } else {
+                    store_chunk_async(&p.map_y, stage, col, static_cast<int>(row0));
+                }
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+            return;
         }
         if constexpr (E == Epilogue::kBiasGelu) {
             // The pre-activation goes to the slot's first half, GELU of the unrounded
@@ -790,6 +860,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     load_aux<E>(next, p, batch_offset, row - lane, col + 64,
                                 min(32, p.n - (col + 64)), lane);
                 }
+                const float bias_lane = load_bias_lane<E>(p, col, lane);
                 uint32_t raw[32];
                 if (valid > 0) {
                     sm100::tmem_ld_32x32(t_addr + c, raw);
@@ -811,7 +882,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     }
                     if (coalesced) {
                         store_chunk<E>(p, stage, batch_offset, t.z, row - lane, col, v, valid,
-                                       lane, aux);
+                                       lane, aux, bias_lane);
                     } else if (row_ok) {
                         store_segment<E>(p, batch_offset, t.z, row, col, v, valid);
                     }
@@ -1095,6 +1166,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + 32 * pair_epilo
                 load_aux<E>(aux, p, batch_offset, row - lane, col0 + column_part * 32,
                             min(32, p.n - (col0 + column_part * 32)), lane);
             }
+            float bias_next = load_bias_lane<E>(p, col0 + column_part * 32, lane);
             if (!sm100::mbar_wait(acc_full_bar(acc), acc_phase, abort)) {
                 ok = false;
                 break;
@@ -1124,6 +1196,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + 32 * pair_epilo
                 const int c = chunk_column(i);
                 const int col = col0 + c;
                 const int valid = chunk_valid(i);
+                const float bias_lane = bias_next;
+                if (!last) {
+                    bias_next = load_bias_lane<E>(p, col + kColumnStep, lane);
+                }
                 Aux<E> next = aux;
                 if (kAhead && prefetch && !last && chunk_valid(i + 1) > 0) {
                     load_aux<E>(next, p, batch_offset, row - lane, col + kColumnStep,
@@ -1163,7 +1239,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + 32 * pair_epilo
                     }
                     if (coalesced) {
                         store_chunk<E>(p, stage, batch_offset, t.z, row - lane, col, v, valid,
-                                       lane, aux);
+                                       lane, aux, bias_lane);
                     } else if (row_ok) {
                         store_segment<E>(p, batch_offset, t.z, row, col, v, valid);
                     }
@@ -1179,6 +1255,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + 32 * pair_epilo
             if (acc == 0) {
                 acc_phase ^= 1u;
             }
+        }
+        // Asynchronous output stores must have landed before the kernel is over.
+        if (p.tma_out != 0 && lane == 0) {
+            store_wait_all();
         }
     }
 
@@ -1416,6 +1496,22 @@ cudaError_t launch_pair(GemmParams& p, const void* x, const void* w, int sms, cu
     }
     if (e != cudaSuccess) {
         return e;
+    }
+    // FP16 outputs of unbatched calls leave through TMA stores when the rows are 16-byte
+    // multiples (the tensor map's requirement; the same rule as the coalesced path).
+    constexpr bool kHalfOut = E == Epilogue::kNone || E == Epilogue::kBias ||
+                              E == Epilogue::kBiasGelu || E == Epilogue::kDGelu ||
+                              E == Epilogue::kScale;
+    p.tma_out = 0;
+    if (kHalfOut && L != Layout::kTN && !batched && p.n % 8 == 0) {
+        e = fb::encode_rows_map(&p.map_y, p.y, p.m, p.n, 2, 32, 32, 64);
+        if (e == cudaSuccess && E == Epilogue::kBiasGelu) {
+            e = fb::encode_rows_map(&p.map_pre, p.aux_out, p.m, p.n, 2, 32, 32, 64);
+        }
+        if (e != cudaSuccess) {
+            return e;
+        }
+        p.tma_out = 1;
     }
     p.tiles_m = (p.m + 255) / 256;
     p.tiles_n = (p.n + kPairBN - 1) / kPairBN;

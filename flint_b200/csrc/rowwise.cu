@@ -521,7 +521,11 @@ __global__ void __launch_bounds__(kCeThreads, 1)
         const fb::F2 mx2 = fb::f2_pack(mx, mx);
         const int full_chunks = vocab / 8;  // chunks whose 8 values all count
 
-        fb::Comp2 part[2];  // even and odd pairs of each word, merged in a fixed order below
+        // A thread adds its (at most 7) words plainly into eight partial sums, one per
+        // column of the word: each takes a handful of values in (0, 1], so its rounding
+        // error is a few units of 2^-24 of itself. Everything after that (the eight
+        // partials, the lanes, the warps) is merged with compensated adds.
+        fb::F2 part[4] = {0, 0, 0, 0};
         for (int i = threadIdx.x; i < full_chunks; i += kCeThreads) {
             fb::F2 x[4];
             gaps8(x, in[i], floor2, mx2);
@@ -529,21 +533,16 @@ __global__ void __launch_bounds__(kCeThreads, 1)
             for (int c = 0; c < 4; ++c) {
                 float e0, e1;
                 exp_pair(x[c], e0, e1);
-                fb::comp_add2(part[c & 1], fb::f2_pack(e0, e1));
+                part[c] = fb::f2_add(part[c], fb::f2_pack(e0, e1));
             }
         }
         Comp mine;
-        {
-            float s0, s1, e0, e1;
-            fb::f2_unpack(part[0].s, s0, s1);
-            fb::f2_unpack(part[0].e, e0, e1);
-            mine.s = s0;
-            mine.e = e0;
-            fb::comp_merge(mine, s1, e1);
-            fb::f2_unpack(part[1].s, s0, s1);
-            fb::f2_unpack(part[1].e, e0, e1);
-            fb::comp_merge(mine, s0, e0);
-            fb::comp_merge(mine, s1, e1);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            float s0, s1;
+            fb::f2_unpack(part[c], s0, s1);
+            fb::comp_add(mine, s0);
+            fb::comp_add(mine, s1);
         }
         if (full_chunks < vocab_chunks && threadIdx.x == (full_chunks % kCeThreads)) {
             // The last, partly filled word: its counted values one by one.
