@@ -91,9 +91,10 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
-// Named barrier among the compute warps only (barrier 0 is __syncthreads).
-__device__ __forceinline__ void compute_sync(int threads) {
-    asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
+// Named barrier between the two warps that share a TMEM lane quadrant (the two
+// halves of the same 32 rows); barrier 0 is __syncthreads, 1..4 are the quadrants'.
+__device__ __forceinline__ void quadrant_sync(int quadrant) {
+    asm volatile("bar.sync %0, 64;" ::"r"(quadrant + 1) : "memory");
 }
 
 // Writes 32 FP16 values (columns [col, col+32) of row `row`) of a 128 x 128
@@ -319,7 +320,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2)
                 }
             }
             pair_max[j & 1][half][row] = local;
-            compute_sync(256);
+            quadrant_sync(quadrant);
             const float mx = fmaxf(m, fmaxf(local, pair_max[j & 1][half ^ 1][row]));
             const float alpha = fast_exp2(m - mx);
             l *= alpha;
@@ -367,7 +368,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2)
         }
         // The row sum is the two threads' shares added together.
         pair_max[0][half][row] = l;
-        compute_sync(256);
+        quadrant_sync(quadrant);
         const float total = l + pair_max[0][half ^ 1][row];
         if (ok && q_index < p.length) {
             const float inv = 1.0f / total;
