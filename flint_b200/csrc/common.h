@@ -99,7 +99,16 @@ cudaError_t launch_layernorm_backward(void* dx, void* dgamma, void* dbeta, const
                                       const void* x, const void* mean, const void* rstd,
                                       const void* gamma, size_t rows, size_t cols,
                                       bool accumulate_dx, bool accumulate_params, void* workspace,
-                                      cudaStream_t stream, void* dx_half);
+                                      cudaStream_t stream, void* dx_half, bool plain);
+
+// flint_bias_gradient's kernels without the argument checks. `plain` (here and above)
+// selects column sums whose row streams use ordinary FP32 adds, merged by compensated
+// adds in the same fixed order: deterministic, within a few 2^-24 of the pinned
+// arithmetic's result, about seven times less FP32 work. The public entry points pass
+// false; the model built on the fused attention kernels passes true.
+cudaError_t launch_bias_gradient(void* dbias, const void* dy, size_t rows, size_t cols,
+                                 bool accumulate, void* workspace, cudaStream_t stream,
+                                 bool plain);
 
 // Device error word of the column-sum kernels: set when a bounded wait for a
 // staged row gave up (read, and cleared if asked, by flint_b200_kernel_fault).

@@ -390,6 +390,12 @@ flint_status weight_gradient(const flint_gpt2& m, const Tensor* weight, const vo
 
 flint_status bias_gradient(const flint_gpt2& m, const Tensor* bias, const void* dy, int accumulate,
                            flint_stream s) {
+    if (m.flash) {
+        // The extension model: bandwidth-bound column sums (see fb::launch_bias_gradient).
+        FB_CUDA(fb::launch_bias_gradient(bias->gradient, dy, m.rows, bias->cols, accumulate != 0,
+                                         m.workspace, s, true));
+        return FLINT_OK;
+    }
     return flint_bias_gradient(bias->gradient, dy, m.rows, bias->cols, accumulate, m.workspace,
                                m.workspace_bytes, s);
 }
@@ -403,7 +409,7 @@ flint_status layernorm_backward(const flint_gpt2& m, const Tensor* gain, const T
     FB_CUDA(fb::launch_layernorm_backward(m.dres, gain->gradient, bias->gradient, m.dh, x, mean,
                                           rstd, gain->data, m.rows, m.config.width,
                                           accumulate_dx != 0, accumulate != 0, m.workspace, s,
-                                          half_copy ? m.dres_half : nullptr));
+                                          half_copy ? m.dres_half : nullptr, m.flash));
     return FLINT_OK;
 }
 

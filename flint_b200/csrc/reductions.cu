@@ -105,7 +105,12 @@ struct ColumnMaps {
     int use;
 };
 
-template <Source kSource>
+// kPlain: a stream adds its rows with ordinary FP32 adds (one instruction per pair
+// instead of seven); the eight streams, the chunks and the lanes are still merged with
+// compensated adds in the same fixed order. This is not the reference's pinned
+// arithmetic (the public entry points never use it); the model built on the fused
+// attention kernels does, where it makes these kernels bandwidth-bound.
+template <Source kSource, bool kPlain>
 __global__ void __launch_bounds__(kTilePieces * (kLaneRows + 1))
     fb_column_partials(const __grid_constant__ ColumnMaps maps, float4* __restrict__ partial,
                        const void* __restrict__ src, const float4* __restrict__ x,
@@ -287,12 +292,20 @@ __global__ void __launch_bounds__(kTilePieces * (kLaneRows + 1))
 #pragma unroll
                         for (int c = 0; c < 4; ++c) {
                             const fb::F2 xhat = fb::f2_mul(fb::f2_sub(xs[c], m2), rs2);
-                            fb::comp_add_product2(acc[c], v[c], xhat);
+                            if constexpr (kPlain) {
+                                acc[c].s = fb::f2_fma(v[c], xhat, acc[c].s);
+                            } else {
+                                fb::comp_add_product2(acc[c], v[c], xhat);
+                            }
                         }
                     } else {
 #pragma unroll
                         for (int c = 0; c < 4; ++c) {
-                            fb::comp_add2(acc[c], v[c]);
+                            if constexpr (kPlain) {
+                                acc[c].s = fb::f2_add(acc[c].s, v[c]);
+                            } else {
+                                fb::comp_add2(acc[c], v[c]);
+                            }
                         }
                     }
                 }
@@ -402,7 +415,7 @@ __global__ void __launch_bounds__(32 * kFinishWarps)
     out[quad] = result;
 }
 
-template <Source kSource>
+template <Source kSource, bool kPlain = false>
 cudaError_t launch_partials(void* workspace, const void* src, const void* x, const void* mean,
                             const void* rstd, size_t rows, size_t cols, cudaStream_t stream) {
     const unsigned chunks = static_cast<unsigned>((rows + kChunkRows - 1) / kChunkRows);
@@ -416,7 +429,7 @@ cudaError_t launch_partials(void* workspace, const void* src, const void* x, con
         return e;
     }
     if (device >= 64 || !configured[device]) {
-        e = cudaFuncSetAttribute(fb_column_partials<kSource>,
+        e = cudaFuncSetAttribute(fb_column_partials<kSource, kPlain>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, kDynamic);
         if (e != cudaSuccess) {
             return e;
@@ -438,7 +451,7 @@ cudaError_t launch_partials(void* workspace, const void* src, const void* x, con
             return e;
         }
     }
-    return fb::launch_dependent(fb_column_partials<kSource>, dim3(chunks, tiles),
+    return fb::launch_dependent(fb_column_partials<kSource, kPlain>, dim3(chunks, tiles),
                                 dim3(kTilePieces, kLaneRows + 1), kDynamic, stream, maps,
                                 static_cast<float4*>(workspace), src, static_cast<const float4*>(x),
                                 static_cast<const float*>(mean), static_cast<const float*>(rstd),
@@ -874,9 +887,13 @@ cudaError_t reductions_error_flag(int* value, bool reset) {
 
 // Internal launchers, also used by the model assembly.
 cudaError_t launch_bias_gradient(void* dbias, const void* dy, size_t rows, size_t cols,
-                                 bool accumulate, void* workspace, cudaStream_t stream) {
-    cudaError_t e = launch_partials<Source::kHalf>(workspace, dy, nullptr, nullptr, nullptr, rows,
-                                                   cols, stream);
+                                 bool accumulate, void* workspace, cudaStream_t stream,
+                                 bool plain) {
+    cudaError_t e =
+        plain ? launch_partials<Source::kHalf, true>(workspace, dy, nullptr, nullptr, nullptr, rows,
+                                                     cols, stream)
+              : launch_partials<Source::kHalf>(workspace, dy, nullptr, nullptr, nullptr, rows, cols,
+                                               stream);
     if (e != cudaSuccess) {
         return e;
     }
@@ -887,15 +904,18 @@ cudaError_t launch_layernorm_backward(void* dx, void* dgamma, void* dbeta, const
                                       const void* x, const void* mean, const void* rstd,
                                       const void* gamma, size_t rows, size_t cols,
                                       bool accumulate_dx, bool accumulate_params, void* workspace,
-                                      cudaStream_t stream, void* dx_half) {
+                                      cudaStream_t stream, void* dx_half, bool plain) {
     // dbeta first; its second pass is done with the workspace before dgamma's
     // partial sums reuse it (stream order).
     cudaError_t e = launch_bias_gradient(dbeta, dy, rows, cols, accumulate_params, workspace,
-                                         stream);
+                                         stream, plain);
     if (e != cudaSuccess) {
         return e;
     }
-    e = launch_partials<Source::kHalfTimesXhat>(workspace, dy, x, mean, rstd, rows, cols, stream);
+    e = plain ? launch_partials<Source::kHalfTimesXhat, true>(workspace, dy, x, mean, rstd, rows,
+                                                              cols, stream)
+              : launch_partials<Source::kHalfTimesXhat>(workspace, dy, x, mean, rstd, rows, cols,
+                                                        stream);
     if (e != cudaSuccess) {
         return e;
     }
@@ -1069,7 +1089,8 @@ flint_status flint_bias_gradient(void* dbias, const void* dy, size_t rows, size_
         {"dy", dy, rows * cols * 2},
     };
     FB_TRY(fb::check_spans(name, spans, 2));
-    FB_CUDA(fb::launch_bias_gradient(dbias, dy, rows, cols, accumulate != 0, workspace, stream));
+    FB_CUDA(fb::launch_bias_gradient(dbias, dy, rows, cols, accumulate != 0, workspace, stream,
+                                     false));
     return FLINT_OK;
 }
 
@@ -1096,7 +1117,8 @@ flint_status flint_b200_bias_gradient_static(void* dbias, const void* dy, size_t
     FB_TRY(fb::check_spans(name, spans, 1));
     // The first pass overwrites every partial sum the second pass reads, so what an
     // earlier call left in the array never matters and nothing needs clearing.
-    FB_CUDA(fb::launch_bias_gradient(dbias, dy, rows, cols, accumulate != 0, scratch, stream));
+    FB_CUDA(fb::launch_bias_gradient(dbias, dy, rows, cols, accumulate != 0, scratch, stream,
+                                     false));
     return FLINT_OK;
 }
 
@@ -1133,7 +1155,7 @@ flint_status flint_layernorm_backward(void* dx, void* dgamma, void* dbeta, const
     FB_TRY(fb::check_spans(name, spans, 4));
     FB_CUDA(fb::launch_layernorm_backward(dx, dgamma, dbeta, dy, x, mean, rstd, gamma, rows, cols,
                                           accumulate_dx != 0, accumulate_params != 0, workspace,
-                                          stream, nullptr));
+                                          stream, nullptr, false));
     return FLINT_OK;
 }
 
