@@ -1161,19 +1161,6 @@ cudaError_t make_map(CUtensorMap* map, const AttentionView& v, const AttentionSh
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-template <typename Kernel>
-cudaError_t configure(Kernel kernel, int smem, bool* done) {
-    if (*done) {
-        return cudaSuccess;
-    }
-    const cudaError_t e =
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e == cudaSuccess) {
-        *done = true;
-    }
-    return e;
-}
-
 AttnParams base_params(const AttentionShape& s, float scale) {
     AttnParams p;
     std::memset(&p, 0, sizeof p);
@@ -1202,8 +1189,8 @@ cudaError_t attention_forward(const AttentionView& o, float* lse, const Attentio
     p.out_head = o.head_stride;
     p.out_seq = o.sequence_stride;
     p.lse = lse;
-    static bool configured = false;
-    e = configure(fb_attention_forward, kFwdSmem, &configured);
+    static bool configured[64] = {};
+    e = fb::allow_shared_memory(fb_attention_forward, kFwdSmem, configured);
     if (e != cudaSuccess) {
         return e;
     }
@@ -1250,8 +1237,8 @@ cudaError_t attention_backward(const AttentionView& dq, const AttentionView& dk,
     const unsigned items = static_cast<unsigned>(shape.sequences * shape.heads * p.blocks);
     const unsigned bwd_grid = std::min(items, static_cast<unsigned>(sms));
 
-    static bool dkv_configured = false;
-    e = configure(fb_attention_dkv, kBwdSmem, &dkv_configured);
+    static bool dkv_configured[64] = {};
+    e = fb::allow_shared_memory(fb_attention_dkv, kBwdSmem, dkv_configured);
     if (e != cudaSuccess) {
         return e;
     }
@@ -1266,8 +1253,8 @@ cudaError_t attention_backward(const AttentionView& dq, const AttentionView& dk,
     if (e != cudaSuccess) {
         return e;
     }
-    static bool dq_configured = false;
-    e = configure(fb_attention_dq, kBwdSmem, &dq_configured);
+    static bool dq_configured[64] = {};
+    e = fb::allow_shared_memory(fb_attention_dq, kBwdSmem, dq_configured);
     if (e != cudaSuccess) {
         return e;
     }

@@ -82,6 +82,25 @@ cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, s
     return e != cudaSuccess ? e : last;
 }
 
+// Raises a kernel's dynamic shared-memory limit once per device (the attribute belongs
+// to the device's copy of the function); `done` is the caller's static per-kernel table.
+template <typename Kernel>
+cudaError_t allow_shared_memory(Kernel kernel, int bytes, bool (&done)[64]) {
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) {
+        return e;
+    }
+    if (device >= 0 && device < 64 && done[device]) {
+        return cudaSuccess;
+    }
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess && device >= 0 && device < 64) {
+        done[device] = true;
+    }
+    return e;
+}
+
 // Number of SMs of the current device (cached per device index).
 cudaError_t sm_count(int* sms);
 

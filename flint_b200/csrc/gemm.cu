@@ -1446,15 +1446,11 @@ cudaError_t launch_tc(GemmParams& p, const void* x, const void* w, int sms, cuda
     const long long z = L == Layout::kTN && !batched ? p.splits : p.batches;
     p.tiles_total = static_cast<long long>(p.tiles_m) * p.tiles_n * z;
 
-    static bool configured = false;
+    static bool configured[64] = {};
     auto kernel = fb_gemm_tc<L, E, BN>;
-    if (!configured) {
-        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 R::kSmemBytes);
-        if (e != cudaSuccess) {
-            return e;
-        }
-        configured = true;
+    e = fb::allow_shared_memory(kernel, R::kSmemBytes, configured);
+    if (e != cudaSuccess) {
+        return e;
     }
     const unsigned grid = static_cast<unsigned>(std::min<long long>(p.tiles_total, sms));
     return fb::launch_dependent(kernel, dim3(grid), dim3(kThreads), R::kSmemBytes, stream, p);
@@ -1518,15 +1514,11 @@ cudaError_t launch_pair(GemmParams& p, const void* x, const void* w, int sms, cu
     const long long z = L == Layout::kTN && !batched ? p.splits : p.batches;
     p.tiles_total = static_cast<long long>(p.tiles_m) * p.tiles_n * z;
 
-    static bool configured = false;
+    static bool configured[64] = {};
     auto kernel = fb_gemm_pair<L, E>;
-    if (!configured) {
-        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 kPairSmemBytes);
-        if (e != cudaSuccess) {
-            return e;
-        }
-        configured = true;
+    e = fb::allow_shared_memory(kernel, kPairSmemBytes, configured);
+    if (e != cudaSuccess) {
+        return e;
     }
     const long long pairs = std::min<long long>(p.tiles_total, sms / 2);
     return fb::launch_dependent(kernel, dim3(static_cast<unsigned>(2 * pairs)),
