@@ -611,6 +611,183 @@ __global__ void __launch_bounds__(kCeThreads, 1)
     }
 }
 
+// The same arithmetic with each exponential evaluated once. A thread keeps its
+// (at most kHeld) 16-byte words of the row in registers from the load to the sum
+// pass; the sum pass leaves every e^(x - max) in shared memory as FP32 (two planes
+// of four values per word, so that a warp's accesses are contiguous), and the
+// gradient pass only scales, rounds and stores them. The next row's words are
+// requested before the gradient pass, so they arrive while it runs.
+template <int kHeld>
+__global__ void __launch_bounds__(kCeThreads, 1)
+    fb_softmax_cross_entropy_once(uint4* __restrict__ dlogits, float* __restrict__ row_loss,
+                                  const uint4* __restrict__ logits,
+                                  const uint16_t* __restrict__ targets, float scale, size_t rows,
+                                  int vocab, int cols) {
+    extern __shared__ uint4 staged[];
+    __shared__ float scratch[2 * kCeWarps];
+    const int chunks = cols / 8;
+    const int vocab_chunks = (vocab + 7) / 8;
+    const int full_chunks = vocab / 8;  // chunks whose 8 values all count
+    const int last_count = vocab - (vocab_chunks - 1) * 8;  // values in the last chunk
+    float4* plane0 = reinterpret_cast<float4*>(staged);
+    float4* plane1 = plane0 + vocab_chunks;
+    const int tid = static_cast<int>(threadIdx.x);
+
+    uint4 held[kHeld];
+    auto fetch = [&](size_t row) {
+        const uint4* in = logits + row * chunks;
+#pragma unroll
+        for (int j = 0; j < kHeld; ++j) {
+            const int i = tid + j * kCeThreads;
+            held[j] = i < vocab_chunks ? __ldg(in + i) : make_uint4(0u, 0u, 0u, 0u);
+        }
+    };
+
+    fb::dependency_wait();
+    if (threadIdx.x == 0) {
+        fb::dependency_release();
+    }
+    if (blockIdx.x < rows) {
+        fetch(blockIdx.x);
+    }
+    for (size_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        uint4* out = dlogits + row * chunks;
+        if (threadIdx.x == 0 && row + gridDim.x < rows) {
+            // The next row starts towards the L2 now, a whole row ahead of its loads.
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(
+                             logits + (row + gridDim.x) * chunks),
+                         "r"(static_cast<uint32_t>(vocab_chunks) * 16u)
+                         : "memory");
+        }
+        const int target = targets[row];
+        const int target_chunk = target / 8;
+        const int target_slot = target % 8;
+
+        float mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < kHeld; ++j) {
+            const int i = tid + j * kCeThreads;
+            if (i < full_chunks) {
+                mx = fmaxf(mx, half_max8(held[j]));
+            } else if (i < vocab_chunks) {
+                float v[8];
+                fb::unpack8(v, held[j]);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    mx = c < last_count ? fmaxf(mx, v[c]) : mx;
+                }
+            }
+        }
+        mx = ce_block_max(mx, scratch);  // also: the pass before is done with the planes
+
+        const __half2 floor2 = __float2half2_rn(fmaxf(__fsub_rn(mx, 64.0f), -65504.0f));
+        const fb::F2 mx2 = fb::f2_pack(mx, mx);
+
+        // Plain per-column partial sums of a thread's words, everything after that merged
+        // with compensated adds (as in the kernel above).
+        fb::F2 part[4] = {0, 0, 0, 0};
+        Comp mine;
+        float target_logit = 0.0f;
+#pragma unroll
+        for (int j = 0; j < kHeld; ++j) {
+            const int i = tid + j * kCeThreads;
+            if (i >= vocab_chunks) {
+                continue;
+            }
+            fb::F2 x[4];
+            gaps8(x, held[j], floor2, mx2);
+            float e[8];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                exp_pair(x[c], e[2 * c], e[2 * c + 1]);
+            }
+            plane0[i] = make_float4(e[0], e[1], e[2], e[3]);
+            plane1[i] = make_float4(e[4], e[5], e[6], e[7]);
+            if (i < full_chunks) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    part[c] = fb::f2_add(part[c], fb::f2_pack(e[2 * c], e[2 * c + 1]));
+                }
+            } else {
+                // The last, partly filled word: its counted values one by one, after the
+                // thread's full words.
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    float s0, s1;
+                    fb::f2_unpack(part[c], s0, s1);
+                    fb::comp_add(mine, s0);
+                    fb::comp_add(mine, s1);
+                    part[c] = 0;
+                }
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    if (c < last_count) {
+                        fb::comp_add(mine, e[c]);
+                    }
+                }
+            }
+            if (i == target_chunk) {
+                float v[8];
+                fb::unpack8(v, held[j]);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    target_logit = c == target_slot ? v[c] : target_logit;
+                }
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            float s0, s1;
+            fb::f2_unpack(part[c], s0, s1);
+            fb::comp_add(mine, s0);
+            fb::comp_add(mine, s1);
+        }
+        const float sum = ce_block_total(mine, scratch);
+        const float inv = __fdiv_rn(1.0f, sum);
+        const fb::F2 inv2 = fb::f2_pack(inv, inv);
+        const fb::F2 scale2 = fb::f2_pack(scale, scale);
+
+        if (row + gridDim.x < rows) {
+            fetch(row + gridDim.x);
+        }
+        for (int i = tid; i < chunks; i += kCeThreads) {
+            if (i >= vocab_chunks) {
+                out[i] = make_uint4(0u, 0u, 0u, 0u);
+                continue;
+            }
+            const float4 a = plane0[i];
+            const float4 b = plane1[i];
+            const float e[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+            float o[8];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                fb::f2_unpack(
+                    fb::f2_mul(fb::f2_mul(fb::f2_pack(e[2 * c], e[2 * c + 1]), inv2), scale2),
+                    o[2 * c], o[2 * c + 1]);
+            }
+            if (i >= full_chunks) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    o[c] = c < last_count ? o[c] : 0.0f;
+                }
+            }
+            if (i == target_chunk) {
+                // The target column: p - 1, and the row's loss, from the unclamped logit.
+                const float gap = __fsub_rn(target_logit, mx);
+                float e0, e1;
+                exp_pair(fb::f2_pack(fmaxf(gap, -64.0f), 0.0f), e0, e1);
+                row_loss[row] = __fsub_rn(logf(sum), gap);
+                const float mine_out = __fmul_rn(__fsub_rn(__fmul_rn(e0, inv), 1.0f), scale);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    o[c] = c == target_slot ? mine_out : o[c];
+                }
+            }
+            out[i] = fb::pack8(o);
+        }
+    }
+}
+
 }  // namespace
 
 extern "C" {
@@ -766,24 +943,31 @@ flint_status flint_softmax_cross_entropy(void* dlogits, void* row_loss, const vo
     };
     FB_TRY(fb::check_spans(name, spans, 2));
 
-    // Only the vocab columns are staged; two row buffers when they fit.
-    const size_t row_bytes = (vocab + 7) / 8 * 16;
-    constexpr size_t kMaxSmem = 220 * 1024;
-    const int buffers = 2 * row_bytes <= kMaxSmem ? 2 : 1;
-    static bool configured[64] = {};
-    int device = 0;
-    FB_CUDA(cudaGetDevice(&device));
-    if (device < 0 || device >= 64 || !configured[device]) {
-        FB_CUDA(cudaFuncSetAttribute(fb_softmax_cross_entropy,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     static_cast<int>(kMaxSmem)));
-        if (device >= 0 && device < 64) {
-            configured[device] = true;
-        }
-    }
     int sms = 148;
     FB_CUDA(fb::sm_count(&sms));
     const unsigned blocks = static_cast<unsigned>(std::min<size_t>(rows, static_cast<size_t>(sms)));
+    constexpr size_t kMaxSmem = 220 * 1024;
+    constexpr int kHeld = 7;
+    const size_t vocab_chunks = (vocab + 7) / 8;
+    if (vocab_chunks <= static_cast<size_t>(kHeld) * kCeThreads && vocab_chunks * 32 <= kMaxSmem) {
+        // The row's exponentials fit in shared memory as FP32: each is evaluated once.
+        static bool once_configured[64] = {};
+        FB_CUDA(fb::allow_shared_memory(fb_softmax_cross_entropy_once<kHeld>,
+                                        static_cast<int>(kMaxSmem), once_configured));
+        FB_CUDA(fb::launch_dependent(fb_softmax_cross_entropy_once<kHeld>, dim3(blocks),
+                                     dim3(kCeThreads), vocab_chunks * 32, stream,
+                                     static_cast<uint4*>(dlogits), static_cast<float*>(row_loss),
+                                     static_cast<const uint4*>(logits),
+                                     static_cast<const uint16_t*>(targets), scale, rows,
+                                     static_cast<int>(vocab), static_cast<int>(cols)));
+        return FLINT_OK;
+    }
+    // Longer rows: only the vocab columns are staged as FP16; two row buffers when they fit.
+    const size_t row_bytes = vocab_chunks * 16;
+    const int buffers = 2 * row_bytes <= kMaxSmem ? 2 : 1;
+    static bool configured[64] = {};
+    FB_CUDA(fb::allow_shared_memory(fb_softmax_cross_entropy, static_cast<int>(kMaxSmem),
+                                    configured));
     FB_CUDA(fb::launch_dependent(fb_softmax_cross_entropy, dim3(blocks), dim3(kCeThreads),
                                  buffers * row_bytes, stream, static_cast<uint4*>(dlogits),
                                  static_cast<float*>(row_loss), static_cast<const uint4*>(logits),
