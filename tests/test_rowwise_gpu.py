@@ -291,8 +291,11 @@ def test_causal_softmax_backward_matches_the_oracle_at_full_size(flint):
 # ---- softmax + cross-entropy ----------------------------------------------------------------------
 
 
+# The last two shapes give every persistent CTA several rows (unevenly), the first of them at
+# GPT-2's width.
 @pytest.mark.parametrize("shape", [(64, 50257, 50304), (5, 8, 8), (9, 1000, 1024),
-                                   (3, 65536, 65536), (4, 3, 16)])
+                                   (3, 65536, 65536), (4, 3, 16), (700, 50257, 50304),
+                                   (1500, 1003, 1008)])
 def test_cross_entropy_loss_and_gradient(flint, shape):
     rows, vocab, cols = shape
     g = torch.Generator().manual_seed(rows)
