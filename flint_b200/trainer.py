@@ -20,11 +20,13 @@ the global mean loss and every rank takes the same skip decision.
 """
 
 import math
-from dataclasses import dataclass
+from dataclasses import asdict, dataclass
 
+import numpy as np
 import torch
 
 from .binding import Flint, Gpt2, Gpt2Config
+from .checkpoint import CheckpointError, read_checkpoint, write_checkpoint
 
 
 @dataclass
@@ -164,6 +166,9 @@ class Trainer:
         self.v = torch.zeros(self.gradient_count, device="cuda")
         half = self._half_copies()
         tensors = []
+        # (name, master address, rows, cols, first float in the gradient/moment arenas)
+        self.layout = [(name, address, rows, cols, (grad - arena) // 4)
+                       for (name, address, rows, cols), (_, grad, _, _) in zip(self.parameters, gradients)]
         for (name, address, rows, cols), (_, grad, _, _) in zip(self.parameters, gradients):
             offset = grad - arena
             decay = config.weight_decay if rows > 1 else 0.0
@@ -294,3 +299,62 @@ class Trainer:
             self.skipped += 1
         self.scaler.update(found)
         return loss
+
+    # -- checkpoints ----------------------------------------------------------------------
+
+    MODEL_KEYS = ("layers", "heads", "width", "block_size", "vocab", "padded_vocab")
+
+    def save(self, path, data_state: dict = None) -> str:
+        """Writes the FP32 master weights (under PyTorch's parameter names), both AdamW
+        moments, the loss scaler and the step counters to path, with data_state (for
+        instance TokenBatches.state()) alongside. Every rank holds the same state, so one
+        rank writing is enough. Returns the file's sha256."""
+        torch.cuda.synchronize()
+        arrays = {}
+        for name, address, rows, cols, first in self.layout:
+            count = rows * cols
+            shape = (cols,) if rows == 1 else (rows, cols)
+            arrays["param/" + name] = device_tensor(address, count).cpu().numpy().reshape(shape)
+            arrays["m/" + name] = self.m[first:first + count].cpu().numpy().reshape(shape)
+            arrays["v/" + name] = self.v[first:first + count].cpu().numpy().reshape(shape)
+        meta = {
+            "kind": "flint-b200 trainer",
+            "config": asdict(self.config),
+            "step_count": self.step_count,
+            "skipped": self.skipped,
+            "loss_scale": self.scaler.scale,
+            "good_steps": self.scaler.good_steps,
+            "data": data_state,
+        }
+        return write_checkpoint(path, meta, arrays)
+
+    def restore(self, path, verify: bool = True):
+        """Loads a checkpoint written by save() into this trainer (same model shape) and
+        returns the data_state stored with it. The FP16 compute copies are refreshed from
+        the restored masters."""
+        meta, arrays = read_checkpoint(path, verify=verify)
+        if meta.get("kind") != "flint-b200 trainer":
+            raise CheckpointError("not a trainer checkpoint")
+        mine = asdict(self.config)
+        for key in self.MODEL_KEYS:
+            if meta["config"].get(key) != mine[key]:
+                raise CheckpointError(
+                    f"checkpoint's {key} is {meta['config'].get(key)}, this trainer's {mine[key]}")
+        state = {}
+        for name, _, rows, cols, first in self.layout:
+            count = rows * cols
+            for prefix in ("param/", "m/", "v/"):
+                if prefix + name not in arrays or arrays[prefix + name].size != count:
+                    raise CheckpointError(f"checkpoint lacks {prefix}{name} with {count} values")
+            state[name] = torch.from_numpy(np.array(arrays["param/" + name], dtype=np.float32)).cuda()
+            self.m[first:first + count].copy_(
+                torch.from_numpy(np.array(arrays["m/" + name], dtype=np.float32).reshape(-1)))
+            self.v[first:first + count].copy_(
+                torch.from_numpy(np.array(arrays["v/" + name], dtype=np.float32).reshape(-1)))
+        self.model.load(state)
+        self.step_count = int(meta["step_count"])
+        self.skipped = int(meta["skipped"])
+        self.scaler.scale = float(meta["loss_scale"])
+        self.scaler.good_steps = int(meta["good_steps"])
+        torch.cuda.synchronize()
+        return meta.get("data")

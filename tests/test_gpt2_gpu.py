@@ -155,3 +155,79 @@ def test_trainer_skips_a_step_with_nonfinite_gradients(flint, case):
             assert torch.equal(trainer.model.read(a, (r, c), torch.float32), before[n]), n
     finally:
         trainer.close()
+
+
+def test_a_resumed_run_repeats_the_uninterrupted_one_bit_for_bit(flint, case, tmp_path):
+    """Token files feed the trainer; a checkpoint taken after two steps (weights, moments,
+    loss scale, counters, the stream's position) restored into a fresh trainer gives the
+    same losses and the same final weights as the run that never stopped."""
+    from flint_b200.tokens import TokenBatches, write_token_file
+
+    params = case[0]
+    rng = np.random.default_rng(11)
+    paths = []
+    for i, size in enumerate((SEQUENCES * LENGTH * 3 + 1, SEQUENCES * LENGTH * 2 + 40)):
+        paths.append(tmp_path / f"shard_{i:03d}.bin")
+        write_token_file(paths[-1], rng.integers(0, SMALL["vocab_size"], size=size, dtype=np.uint16))
+    config = TrainerConfig(layers=2, heads=2, width=128, block_size=64, vocab=200, padded_vocab=208,
+                           sequences=SEQUENCES, length=LENGTH, loss_scale=1024.0, growth_interval=3)
+
+    def run(trainer, batches, steps):
+        losses = []
+        for _ in range(steps):
+            tokens, targets = batches.next_batch()
+            trainer.step(torch.from_numpy(tokens.view(np.int16)).to(DEV).flatten(),
+                         torch.from_numpy(targets.view(np.int16)).to(DEV).flatten())
+            losses.append(trainer.finish_step())
+        return losses
+
+    def weights(trainer):
+        return {n: trainer.model.read(a, (r, c), torch.float32).cpu()
+                for n, a, r, c in trainer.model.parameters()}
+
+    first = Trainer(flint, config, state=params)
+    try:
+        batches = TokenBatches(paths, SEQUENCES, LENGTH, vocab=SMALL["vocab_size"])
+        run(first, batches, 2)
+        first.save(tmp_path / "step2.ckpt", data_state=batches.state())
+        want_losses = run(first, batches, 4)  # crosses into the second shard and a scale growth
+        want = weights(first)
+        want_scale, want_steps = first.scaler.scale, first.step_count
+    finally:
+        first.close()
+
+    second = Trainer(flint, config, state={k: torch.zeros_like(v) for k, v in params.items()})
+    try:
+        batches = TokenBatches(paths, SEQUENCES, LENGTH, vocab=SMALL["vocab_size"])
+        batches.restore(second.restore(tmp_path / "step2.ckpt"))
+        assert second.step_count == 2
+        assert run(second, batches, 4) == want_losses
+        assert second.scaler.scale == want_scale and second.step_count == want_steps
+        got = weights(second)
+        for name in want:
+            assert torch.equal(got[name], want[name]), name
+    finally:
+        second.close()
+    assert not flint.kernel_fault()
+
+
+def test_the_training_driver_resumes_from_its_checkpoint(tmp_path, capsys):
+    """`python -m flint_b200.train` in process: four steps in one go, and two + two through
+    a checkpoint file, log the same losses."""
+    from flint_b200 import train
+    from flint_b200.tokens import write_token_file
+
+    rng = np.random.default_rng(3)
+    shard = tmp_path / "shard_001.bin"
+    write_token_file(shard, rng.integers(0, 200, size=2 * 64 * 5 + 1, dtype=np.uint16))
+    common = ["--tokens", str(shard), "--sequences", "2", "--length", "64", "--layers", "2",
+              "--heads", "2", "--width", "128", "--block-size", "64", "--vocab", "200",
+              "--padded-vocab", "208", "--loss-scale", "1024"]
+    whole = train.main(common + ["--steps", "4"])
+    ckpt = str(tmp_path / "run.ckpt")
+    head = train.main(common + ["--steps", "2", "--checkpoint", ckpt])
+    tail = train.main(common + ["--steps", "2", "--resume", ckpt])
+    assert len(whole) == 4 and head + tail == whole
+    assert all(np.isfinite(whole))
+    lines = [line for line in capsys.readouterr().out.splitlines() if line.startswith("{")]
+    assert len(lines) == 8 and '"step": 4' in lines[3] and '"step": 4' in lines[7]
