@@ -32,6 +32,8 @@ def parse(argv=None):
     p.add_argument("--steps", type=int, default=10)
     p.add_argument("--sequences", type=int, default=16, help="sequences per GPU per step")
     p.add_argument("--length", type=int, default=1024)
+    p.add_argument("--accumulate", type=int, default=1,
+                   help="micro-batches per optimizer step (gradient accumulation)")
     p.add_argument("--layers", type=int, default=12)
     p.add_argument("--heads", type=int, default=12)
     p.add_argument("--width", type=int, default=768)
@@ -73,12 +75,15 @@ def main(argv=None) -> list:
         if saved is not None:
             batches.restore(saved)
 
+    # One pinned host pair and one device pair per micro-batch of a step.
     shape = (args.sequences, args.length)
-    host = [torch.empty(shape, dtype=torch.int16).pin_memory() for _ in range(2)]
-    views = [h.numpy().view(np.uint16) for h in host]
-    device = [torch.empty(shape, dtype=torch.int16, device="cuda") for _ in range(2)]
+    micro = max(1, args.accumulate)
+    host = [[torch.empty(shape, dtype=torch.int16).pin_memory() for _ in range(2)] for _ in range(micro)]
+    views = [[h.numpy().view(np.uint16) for h in pair] for pair in host]
+    device = [[torch.empty(shape, dtype=torch.int16, device="cuda") for _ in range(2)]
+              for _ in range(micro)]
     losses = []
-    tokens_per_step = args.sequences * args.length * world
+    tokens_per_step = args.sequences * args.length * world * micro
 
     def checkpoint():
         if args.checkpoint and rank == 0:
@@ -87,10 +92,11 @@ def main(argv=None) -> list:
     try:
         for index in range(args.steps):
             begin = time.perf_counter()
-            batches.next_batch(views[0], views[1])
-            device[0].copy_(host[0], non_blocking=True)
-            device[1].copy_(host[1], non_blocking=True)
-            trainer.step(device[0].flatten(), device[1].flatten())
+            for m in range(micro):
+                batches.next_batch(views[m][0], views[m][1])
+                device[m][0].copy_(host[m][0], non_blocking=True)
+                device[m][1].copy_(host[m][1], non_blocking=True)
+            trainer.step_batches([(pair[0].flatten(), pair[1].flatten()) for pair in device])
             loss = trainer.finish_step()  # waits for the step: the pinned buffers are free again
             seconds = time.perf_counter() - begin
             if rank == 0 and (index + 1) % max(1, args.log_every) == 0:

@@ -184,6 +184,9 @@ class Trainer:
             self.split_plans = (flint.adamw_plan(tensors[:2]), flint.adamw_plan(tensors[2:]))
         self.found = torch.zeros(1, dtype=torch.int32, device="cuda")
         self.norm_squared = torch.zeros(1, dtype=torch.float64, device="cuda")
+        self._row_loss = device_tensor(self.model.outputs()[2], self.rows)
+        self._loss_sum = torch.zeros((), dtype=torch.float64, device="cuda")
+        self._micro_batches = 1
         self.scaler = LossScaler(config.loss_scale, config.growth_interval)
         self.step_count = 0
         self.skipped = 0
@@ -242,17 +245,39 @@ class Trainer:
     def step(self, tokens: torch.Tensor, targets: torch.Tensor) -> None:
         """Enqueues forward, backward (with overlapped all-reduce), the gradient check and
         the AdamW update for one micro-batch of uint16 tokens/targets on this rank."""
+        self.step_batches([(tokens, targets)])
+
+    def step_batches(self, batches) -> None:
+        """One optimizer step over several micro-batches, a list of (tokens, targets), as the
+        reference's ``train_step`` takes them (``scripts/gpt2_torch.py:178-192``): each
+        micro-batch's loss is divided by their number and the gradients accumulate in place
+        (``flint_gpt2_backward`` with accumulate set from the second one on). With more
+        than one rank only the last micro-batch's backward starts the all-reduces, on the
+        accumulated gradients."""
         c = self.config
-        scale = cross_entropy_scale(self.scaler.scale, self.rows, self.world)
-        self.model.forward(tokens, targets, scale)
+        count = len(batches)
+        if count == 0:
+            raise ValueError("a step needs at least one micro-batch")
+        scale = cross_entropy_scale(self.scaler.scale, self.rows, self.world) / count
         inverse = 1.0 / self.scaler.scale
-        if self._pipelined():
+        pipelined = self._pipelined()
+        self._micro_batches = count
+        if count > 1:
+            self._loss_sum.zero_()
+        if pipelined:
+            self.found.zero_()
+        for index, (tokens, targets) in enumerate(batches):
+            self.model.forward(tokens, targets, scale)
+            if count > 1:
+                self._loss_sum += self._row_loss.sum(dtype=torch.float64)
+            reduce_now = self.world > 1 and index + 1 == count
+            self.model.backward(tokens, index > 0,
+                                callback=self._on_bucket if reduce_now else None)
+        if pipelined:
             # Every bucket but the last is summed while backward runs; the last one (the
             # embeddings, a third of the bytes) would otherwise be waited for with nothing
             # to do. Its non-finite flag is settled early (see _on_bucket), so the rest of
             # the model is checked and updated while that all-reduce is in flight.
-            self.found.zero_()
-            self.model.backward(tokens, False, callback=self._on_bucket)
             done = torch.cuda.Event()
             done.record(self.comm_stream)
             self.stream.wait_event(self._flag_ready)
@@ -268,12 +293,9 @@ class Trainer:
                                  step, self.found)
             return
         if self.world > 1:
-            self.model.backward(tokens, False, callback=self._on_bucket)
             done = torch.cuda.Event()
             done.record(self.comm_stream)
             self.stream.wait_event(done)
-        else:
-            self.model.backward(tokens, False)
         self.found.zero_()
         clip = c.max_grad_norm > 0
         if clip:
@@ -292,8 +314,11 @@ class Trainer:
 
     def finish_step(self) -> float:
         """Waits for the step, updates the loss scale from the non-finite flag and returns
-        this rank's mean loss (a device-to-host read)."""
-        loss = self.model.mean_loss()
+        this rank's mean loss over the step's micro-batches (a device-to-host read)."""
+        if self._micro_batches > 1:
+            loss = self._loss_sum.item() / (self.rows * self._micro_batches)
+        else:
+            loss = self.model.mean_loss()
         found = bool(self.found.item())
         if found:
             self.skipped += 1

@@ -231,3 +231,38 @@ def test_the_training_driver_resumes_from_its_checkpoint(tmp_path, capsys):
     assert all(np.isfinite(whole))
     lines = [line for line in capsys.readouterr().out.splitlines() if line.startswith("{")]
     assert len(lines) == 8 and '"step": 4' in lines[3] and '"step": 4' in lines[7]
+
+
+def test_accumulated_micro_batches_equal_one_large_batch(flint, case):
+    """Two micro-batches accumulated into one optimizer step (the reference's train_step over
+    a list of batches, scripts/gpt2_torch.py:178-192) against the same six sequences as one
+    batch: the same mean loss, and weight updates that agree to rounding."""
+    params = case[0]
+    idx, targets = oracle.synthetic_tokens(2 * SEQUENCES, LENGTH, SMALL["vocab_size"], seed=21)
+    shape = dict(layers=2, heads=2, width=128, block_size=64, vocab=200, padded_vocab=208,
+                 length=LENGTH, loss_scale=1024.0)
+
+    def updated(trainer):
+        return torch.cat([trainer.model.read(a, (r, c), torch.float32).cpu().flatten()
+                          for _, a, r, c in trainer.model.parameters()])
+
+    whole = Trainer(flint, TrainerConfig(sequences=2 * SEQUENCES, **shape), state=params)
+    try:
+        start = torch.cat([params[name].flatten() for name, *_ in whole.model.parameters()])
+        whole.step(u16(idx.flatten()), u16(targets.flatten()))
+        want_loss = whole.finish_step()
+        want = updated(whole)
+    finally:
+        whole.close()
+    parts = Trainer(flint, TrainerConfig(sequences=SEQUENCES, **shape), state=params)
+    try:
+        parts.step_batches([(u16(idx[:SEQUENCES].flatten()), u16(targets[:SEQUENCES].flatten())),
+                            (u16(idx[SEQUENCES:].flatten()), u16(targets[SEQUENCES:].flatten()))])
+        loss = parts.finish_step()
+        got = updated(parts)
+        assert parts.step_count == 1 and parts.skipped == 0
+    finally:
+        parts.close()
+    assert abs(loss - want_loss) <= 1e-5
+    assert cosine(got - start, want - start) >= 0.999
+    assert not flint.kernel_fault()
