@@ -232,9 +232,13 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank) {
     return remote;
 }
 
+// An arrive on a barrier of another CTA of the cluster. CTA-scope release (the
+// instruction's default): what the barrier hands over here is tensor memory, which the
+// tcgen05 fences on either side order; a cluster-scope release would also wait for
+// every earlier global and shared-memory write of the thread to become visible to the
+// other SM (measured at about 2,400 clocks per arrive behind an epilogue's stores).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
-                 : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
 
 // TMA loads whose completion bytes may be counted on the pair leader's mbarrier.
