@@ -1152,6 +1152,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + 32 * pair_epilo
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
+        // A chunk's second operands (residual, pre-activations) are requested while the
+        // chunk before it is processed. For the dGELU epilogue the first chunk of a tile
+        // counts as following the last chunk of the tile before, so only this CTA's very
+        // first chunk waits for its operands with nothing else to do; the others request
+        // a tile's first operands before they wait for its accumulator.
+        Aux<E> aux;
+        bool aux_requested = false;
         for (long long id = pair; ok && id < p.tiles_total; id += pairs) {
             const TileCoord t = decode_pair_tile(p, id);
             const size_t row = static_cast<size_t>(t.tm) * 256 + rank * 128 + quadrant * 32 + lane;
@@ -1159,13 +1166,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + 32 * pair_epilo
             const int col0 = t.tn * kPairBN;
             const size_t batch_offset =
                 p.batched ? static_cast<size_t>(t.z) * p.m * static_cast<size_t>(p.n) : 0;
-            // The first chunk's second operands are requested before the accumulator is
-            // awaited, each later chunk's while the one before it is processed.
-            Aux<E> aux;
-            if (prefetch && p.n - (col0 + column_part * 32) > 0) {
+            if (prefetch && !aux_requested && p.n - (col0 + column_part * 32) > 0) {
                 load_aux<E>(aux, p, batch_offset, row - lane, col0 + column_part * 32,
                             min(32, p.n - (col0 + column_part * 32)), lane);
             }
+            aux_requested = false;
             float bias_next = load_bias_lane<E>(p, col0 + column_part * 32, lane);
             if (!sm100::mbar_wait(acc_full_bar(acc), acc_phase, abort)) {
                 ok = false;
@@ -1204,6 +1209,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + 32 * pair_epilo
                 if (kAhead && prefetch && !last && chunk_valid(i + 1) > 0) {
                     load_aux<E>(next, p, batch_offset, row - lane, col + kColumnStep,
                                 chunk_valid(i + 1), lane);
+                }
+                // (Only where the operands are few registers: with the FP32 residual's 32
+                // registers held through the last chunk as well, the kernel was slower.)
+                if (E == Epilogue::kDGelu && kAhead && prefetch && last &&
+                    id + pairs < p.tiles_total) {
+                    // The next tile's first chunk.
+                    const TileCoord t2 = decode_pair_tile(p, id + pairs);
+                    const size_t row2 =
+                        static_cast<size_t>(t2.tm) * 256 + rank * 128 + quadrant * 32;
+                    const int col2 = t2.tn * kPairBN + column_part * 32;
+                    const size_t offset2 =
+                        p.batched ? static_cast<size_t>(t2.z) * p.m * static_cast<size_t>(p.n) : 0;
+                    if (p.n - col2 > 0) {
+                        load_aux<E>(next, p, offset2, row2, col2, min(32, p.n - col2), lane);
+                        aux_requested = true;
+                    }
                 }
                 const int kSet = kPipelined ? (i & 1) : 0;  // static once unrolled
                 if (!kPipelined && valid > 0) {
