@@ -109,7 +109,10 @@ struct ColumnMaps {
 // instead of seven); the eight streams, the chunks and the lanes are still merged with
 // compensated adds in the same fixed order. This is not the reference's pinned
 // arithmetic (the public entry points never use it); the model built on the fused
-// attention kernels does, where it makes these kernels bandwidth-bound.
+// attention kernels does, where it makes these kernels bandwidth-bound. In that variant
+// the FP16-times-xhat kernel (LayerNorm's dgamma) also sums the FP16 values themselves
+// (dbeta) from the same staged rows, with the operations the plain FP16 kernel would
+// use, and writes those partial sums as a second block right behind the first one.
 template <Source kSource, bool kPlain>
 __global__ void __launch_bounds__(kTilePieces * (kLaneRows + 1))
     fb_column_partials(const __grid_constant__ ColumnMaps maps, float4* __restrict__ partial,
@@ -161,6 +164,8 @@ __global__ void __launch_bounds__(kTilePieces * (kLaneRows + 1))
     volatile int* abort = &abort_flag;
     bool ok = true;
     fb::Comp2 acc[4];
+    constexpr bool kAlsoPlainSums = kPlain && kSource == Source::kHalfTimesXhat;
+    fb::F2 also[4] = {0, 0, 0, 0};
 
     if (ly == kLaneRows) {
         // ---- fetching warp: lane l copies row l of each stage (and its x segment) ----
@@ -294,6 +299,7 @@ __global__ void __launch_bounds__(kTilePieces * (kLaneRows + 1))
                             const fb::F2 xhat = fb::f2_mul(fb::f2_sub(xs[c], m2), rs2);
                             if constexpr (kPlain) {
                                 acc[c].s = fb::f2_fma(v[c], xhat, acc[c].s);
+                                also[c] = fb::f2_add(also[c], v[c]);
                             } else {
                                 fb::comp_add_product2(acc[c], v[c], xhat);
                             }
@@ -327,42 +333,49 @@ __global__ void __launch_bounds__(kTilePieces * (kLaneRows + 1))
     __syncthreads();
     float* sh_s = reinterpret_cast<float*>(staging_raw + (staging - shared_address(staging_raw)));
     float* sh_e = sh_s + kLaneRows * kTilePieces * 8;
-    if (ly < kLaneRows) {
+    const size_t block_quads = size_t{gridDim.x} * pieces * 4;  // float4s in one block of partials
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            float lo, hi;
-            fb::f2_unpack(acc[c].s, lo, hi);
-            sh_s[(ly * kTilePieces + px) * 8 + 2 * c] = lo;
-            sh_s[(ly * kTilePieces + px) * 8 + 2 * c + 1] = hi;
-            fb::f2_unpack(acc[c].e, lo, hi);
-            sh_e[(ly * kTilePieces + px) * 8 + 2 * c] = lo;
-            sh_e[(ly * kTilePieces + px) * 8 + 2 * c + 1] = hi;
+    for (int set = 0; set < (kAlsoPlainSums ? 2 : 1); ++set) {
+        if (set == 1) {
+            __syncthreads();  // stream 0 has read the first set
         }
-    }
-    __syncthreads();
-    if (ly != 0 || piece >= pieces) {
-        return;
-    }
-    Comp total[8];
+        if (ly < kLaneRows) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        total[j].s = sh_s[px * 8 + j];
-        total[j].e = sh_e[px * 8 + j];
-    }
-    for (int other = 1; other < kLaneRows; ++other) {
+            for (int c = 0; c < 4; ++c) {
+                float lo, hi;
+                fb::f2_unpack(set == 0 ? acc[c].s : also[c], lo, hi);
+                sh_s[(ly * kTilePieces + px) * 8 + 2 * c] = lo;
+                sh_s[(ly * kTilePieces + px) * 8 + 2 * c + 1] = hi;
+                fb::f2_unpack(set == 0 ? acc[c].e : fb::F2{0}, lo, hi);
+                sh_e[(ly * kTilePieces + px) * 8 + 2 * c] = lo;
+                sh_e[(ly * kTilePieces + px) * 8 + 2 * c + 1] = hi;
+            }
+        }
+        __syncthreads();
+        if (ly != 0 || piece >= pieces) {
+            continue;
+        }
+        Comp total[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            fb::comp_merge(total[j], sh_s[(other * kTilePieces + px) * 8 + j],
-                           sh_e[(other * kTilePieces + px) * 8 + j]);
+            total[j].s = sh_s[px * 8 + j];
+            total[j].e = sh_e[px * 8 + j];
         }
+        for (int other = 1; other < kLaneRows; ++other) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                fb::comp_merge(total[j], sh_s[(other * kTilePieces + px) * 8 + j],
+                               sh_e[(other * kTilePieces + px) * 8 + j]);
+            }
+        }
+        // Chunk c occupies rows 2c (sums) and 2c+1 (errors) of a [2*chunks, cols] FP32 matrix.
+        float4* out = partial + set * block_quads + size_t{blockIdx.x} * pieces * 4 + size_t(piece) * 2;
+        out[0] = make_float4(total[0].s, total[1].s, total[2].s, total[3].s);
+        out[1] = make_float4(total[4].s, total[5].s, total[6].s, total[7].s);
+        out += size_t(pieces) * 2;
+        out[0] = make_float4(total[0].e, total[1].e, total[2].e, total[3].e);
+        out[1] = make_float4(total[4].e, total[5].e, total[6].e, total[7].e);
     }
-    // Chunk c occupies rows 2c (sums) and 2c+1 (errors) of a [2*chunks, cols] FP32 matrix.
-    float4* out = partial + size_t{blockIdx.x} * pieces * 4 + size_t(piece) * 2;
-    out[0] = make_float4(total[0].s, total[1].s, total[2].s, total[3].s);
-    out[1] = make_float4(total[4].s, total[5].s, total[6].s, total[7].s);
-    out += size_t(pieces) * 2;
-    out[0] = make_float4(total[0].e, total[1].e, total[2].e, total[3].e);
-    out[1] = make_float4(total[4].e, total[5].e, total[6].e, total[7].e);
 }
 
 // Second pass: a warp per 4 columns.
@@ -905,23 +918,42 @@ cudaError_t launch_layernorm_backward(void* dx, void* dgamma, void* dbeta, const
                                       const void* gamma, size_t rows, size_t cols,
                                       bool accumulate_dx, bool accumulate_params, void* workspace,
                                       cudaStream_t stream, void* dx_half, bool plain) {
-    // dbeta first; its second pass is done with the workspace before dgamma's
-    // partial sums reuse it (stream order).
-    cudaError_t e = launch_bias_gradient(dbeta, dy, rows, cols, accumulate_params, workspace,
-                                         stream, plain);
-    if (e != cudaSuccess) {
-        return e;
-    }
-    e = plain ? launch_partials<Source::kHalfTimesXhat, true>(workspace, dy, x, mean, rstd, rows,
-                                                              cols, stream)
-              : launch_partials<Source::kHalfTimesXhat>(workspace, dy, x, mean, rstd, rows, cols,
-                                                        stream);
-    if (e != cudaSuccess) {
-        return e;
-    }
-    e = launch_finish(dgamma, workspace, rows, cols, accumulate_params, stream);
-    if (e != cudaSuccess) {
-        return e;
+    cudaError_t e = cudaSuccess;
+    if (plain) {
+        // One pass over dy serves both parameter gradients: dgamma's partial sums fill the
+        // first block of the workspace, dbeta's the second (the caller provides twice the
+        // public workspace size for this variant).
+        e = launch_partials<Source::kHalfTimesXhat, true>(workspace, dy, x, mean, rstd, rows, cols,
+                                                          stream);
+        if (e != cudaSuccess) {
+            return e;
+        }
+        e = launch_finish(dgamma, workspace, rows, cols, accumulate_params, stream);
+        if (e != cudaSuccess) {
+            return e;
+        }
+        e = launch_finish(dbeta, static_cast<unsigned char*>(workspace) + column_sum_workspace(rows, cols),
+                          rows, cols, accumulate_params, stream);
+        if (e != cudaSuccess) {
+            return e;
+        }
+    } else {
+        // dbeta first; its second pass is done with the workspace before dgamma's
+        // partial sums reuse it (stream order).
+        e = launch_bias_gradient(dbeta, dy, rows, cols, accumulate_params, workspace, stream,
+                                 false);
+        if (e != cudaSuccess) {
+            return e;
+        }
+        e = launch_partials<Source::kHalfTimesXhat>(workspace, dy, x, mean, rstd, rows, cols,
+                                                    stream);
+        if (e != cudaSuccess) {
+            return e;
+        }
+        e = launch_finish(dgamma, workspace, rows, cols, accumulate_params, stream);
+        if (e != cudaSuccess) {
+            return e;
+        }
     }
     const int pieces = static_cast<int>(cols / 8);
     const unsigned blocks = static_cast<unsigned>((rows + kWarpsPerBlock - 1) / kWarpsPerBlock);
