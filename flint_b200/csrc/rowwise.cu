@@ -419,7 +419,8 @@ __device__ __forceinline__ float half_max8(const uint4& q) {
 // shared memory with one bulk asynchronous copy (two row buffers when they fit,
 // so the next row loads while this one is processed); the three passes (max on
 // the raw FP16 values, compensated sum of exp, gradient) then run out of shared
-// memory, and the row leaves as coalesced 16-byte stores.
+// memory, and the row leaves as coalesced 16-byte stores. This kernel serves rows of
+// more than 53,248 columns; shorter rows take the rolling kernel further down.
 __global__ void __launch_bounds__(kCeThreads, 1)
     fb_softmax_cross_entropy(uint4* __restrict__ dlogits, float* __restrict__ row_loss,
                              const uint4* __restrict__ logits,
