@@ -8,7 +8,7 @@ It imports the reference's own test helpers (the bit-exact numpy emulations
 of its kernels and its float references) and its PyTorch GPT-2 model, runs
 them on seeded inputs, and stores inputs and outputs as small fixtures. The
 fixtures pin oracle/flint_oracle.py (tests/test_oracle_golden.py) and serve
-as known-answer vectors for the CUDA kernels (tests/test_parity_golden.py).
+as known-answer vectors for the CUDA kernels (the `golden` cases of tests/test_*_gpu.py).
 Nothing else reads the reference, and no test needs it at run time.
 """
 
@@ -165,4 +165,6 @@ def main(reference_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py /path/to/reference")
+    main(sys.argv[1])
