@@ -11,7 +11,11 @@ against tests/golden/*.npz, which tests/golden/make_golden.py generated in a
 container that had the reference checked out, by calling the reference's own
 bit-exact emulations (tests/test_bias_gradient.py, test_layernorm_backward.py,
 test_softmax_backward.py, test_embedding_backward.py), its float references
-(tests/gate.py) and its PyTorch model (scripts/gpt2_torch.py).
+(tests/gate.py and the float64 references inside test_layernorm.py,
+test_softmax.py, test_cross_entropy.py, test_embedding.py,
+test_gemm_bias_gelu.py, test_gemm_dgelu.py and the attention chain of
+test_softmax_backward.py) and its PyTorch model and optimizer
+(scripts/gpt2_torch.py).
 
 Each function cites the reference file:line whose arithmetic it follows.
 """
@@ -339,6 +343,54 @@ def gelu_tanh_grad(pre):
     return pre.grad
 
 
+def gelu_exponent(s):
+    """a in gelu(s) = s / (1 + exp(a)): -2 sqrt(2/pi) (s + 0.044715 s^3), float64
+    (tests/test_gemm_bias_gelu.py:199-203)."""
+    s = _t64(s)
+    return -2.0 * math.sqrt(2.0 / math.pi) * s * (1.0 + 0.044715 * s * s)
+
+
+def gelu_tanh_derivative(s):
+    """(g, a): the derivative of the tanh GELU in closed form, float64, and its exponent a.
+    With sigma = 1 / (1 + exp(a)): g = sigma + s sigma (1 - sigma) (-da/ds)
+    (tests/test_gemm_dgelu.py:262-280). Limits 0 and 1 at -inf and +inf."""
+    s = _t64(s)
+    a = gelu_exponent(s)
+    sigma = torch.sigmoid(-a)
+    slope = 2.0 * math.sqrt(2.0 / math.pi) * (1.0 + 3 * 0.044715 * s * s)
+    second = s * sigma * (1.0 - sigma) * slope
+    second = torch.where(torch.isfinite(second), second, torch.zeros_like(second))
+    return sigma + second, a
+
+
+def half_ordered(h):
+    """FP16 values as integers that rise with the value (both zeros are 0), so that
+    neighbouring values differ by 1 (tests/test_gemm_bias_gelu.py:206-210)."""
+    b = torch.as_tensor(np.asarray(h)).view(torch.int16).to(torch.int32)
+    return torch.where(b < 0, -(b & 0x7FFF), b)
+
+
+def half_rounding_margin(v):
+    """How far each float64 value is from the nearest boundary between two FP16 roundings,
+    as a fraction of the value; infinite for 0 and for values that overflow whatever their
+    error (tests/test_gemm_bias_gelu.py:213-227)."""
+    v = _t64(v)
+    a = v.abs()
+    exponent = torch.frexp(a)[1].double()
+    ulp = torch.where(a < 2.0 ** -14, torch.full_like(a, 2.0 ** -24), torch.exp2(exponent - 11))
+    fraction = (a / ulp) % 1.0
+    margin = (fraction - 0.5).abs() * ulp / a
+    margin = torch.where(a == 0, torch.full_like(a, math.inf), margin)
+    return torch.where(a >= 65536, torch.full_like(a, math.inf), margin)
+
+
+def round_to_half(v):
+    """float64 -> FP16 with one rounding to nearest even. numpy converts directly; torch's
+    double -> half goes through float and rounds twice (tests/test_gemm_dgelu.py:283-288)."""
+    with np.errstate(over="ignore"):
+        return torch.from_numpy(_t64(v).numpy().astype(np.float16))
+
+
 def gemm_nt(x, w, bias=None):
     y = _t64(x) @ _t64(w).transpose(-1, -2)
     return y if bias is None else y + _t64(bias)
@@ -443,9 +495,10 @@ def gpt2_round_to_half(params):
     return {k: v.half().float() for k, v in params.items()}
 
 
-def gpt2_loss(cfg, params, idx, targets, dtype=torch.float32):
-    """Mean cross-entropy of the model on idx/targets [batch, length] (int64), with
-    explicit causal-softmax attention; differentiable in params."""
+def gpt2_logits(cfg, params, idx, dtype=torch.float32):
+    """Logits [batch * length, vocab_size] (padded columns dropped) of the model on idx
+    [batch, length] (int64), with explicit causal-softmax attention; differentiable in
+    params."""
     p = {k: v.to(dtype) for k, v in params.items()} if dtype != torch.float32 else params
     batch, length = idx.shape
     w, h = cfg["n_embd"], cfg["n_head"]
@@ -465,16 +518,54 @@ def gpt2_loss(cfg, params, idx, targets, dtype=torch.float32):
         y = gelu_tanh(torch.nn.functional.linear(y, p[b + "mlp.c_fc.weight"], p[b + "mlp.c_fc.bias"]))
         x = x + torch.nn.functional.linear(y, p[b + "mlp.c_proj.weight"], p[b + "mlp.c_proj.bias"])
     x = torch.nn.functional.layer_norm(x, (w,), p["ln_f.weight"], p["ln_f.bias"], 1e-5)
-    logits = torch.nn.functional.linear(x.reshape(-1, w), p["wte.weight"])[:, :cfg["vocab_size"]]
+    return torch.nn.functional.linear(x.reshape(-1, w), p["wte.weight"])[:, :cfg["vocab_size"]]
+
+
+def gpt2_loss(cfg, params, idx, targets, dtype=torch.float32):
+    """Mean cross-entropy of the model on idx/targets [batch, length] (int64)."""
+    logits = gpt2_logits(cfg, params, idx, dtype)
     return torch.nn.functional.cross_entropy(logits, targets.reshape(-1))
 
 
-def gpt2_loss_and_gradients(cfg, params, idx, targets, dtype=torch.float32):
-    """(loss, {name: gradient}) by autograd on the CPU."""
+def gpt2_loss_and_gradients(cfg, params, idx, targets, dtype=torch.float32, with_logits=False):
+    """(loss, {name: gradient}) by autograd on the CPU; with_logits adds the detached
+    logits [rows, vocab_size] as a third value."""
     leaves = {k: v.detach().clone().to(dtype).requires_grad_(True) for k, v in params.items()}
-    loss = gpt2_loss(cfg, leaves, idx, targets)
+    logits = gpt2_logits(cfg, leaves, idx)
+    loss = torch.nn.functional.cross_entropy(logits, targets.reshape(-1))
     loss.backward()
-    return loss.item(), {k: v.grad for k, v in leaves.items()}
+    grads = {k: v.grad for k, v in leaves.items()}
+    if with_logits:
+        return loss.item(), grads, logits.detach()
+    return loss.item(), grads
+
+
+def clip_coefficient(grads, max_norm=MAX_GRAD_NORM):
+    """(coefficient, total norm) of torch.nn.utils.clip_grad_norm_ over an iterable of
+    gradients: min(1, max_norm / (norm + 1e-6)) (scripts/gpt2_torch.py:187-188)."""
+    total = math.sqrt(sum(float(g.double().pow(2).sum()) for g in grads))
+    return min(1.0, max_norm / (total + 1e-6)), total
+
+
+def train_step(cfg, params, moments, batches, step, loss_scale=1.0, max_grad_norm=MAX_GRAD_NORM):
+    """One optimizer step of scripts/gpt2_torch.py:178-192 on the CPU, in place: the
+    micro-batches' gradients of loss / len(batches) accumulated, unscaled, clipped to
+    max_grad_norm (0 or None: no clipping), then AdamW with the reference's two parameter
+    groups. A non-finite gradient skips the update. Returns (mean loss, skipped, norm)."""
+    total, loss_sum = None, 0.0
+    for idx, targets in batches:
+        loss, grads = gpt2_loss_and_gradients(cfg, params, idx, targets)
+        loss_sum += loss
+        scaled = {k: g * (loss_scale / len(batches)) for k, g in grads.items()}
+        total = scaled if total is None else {k: total[k] + scaled[k] for k in total}
+    grads = {k: g / loss_scale for k, g in total.items()}
+    if not all(bool(torch.isfinite(g).all()) for g in grads.values()):
+        return loss_sum / len(batches), True, math.inf
+    coefficient, norm = clip_coefficient(grads.values(), max_grad_norm) if max_grad_norm else (1.0, 0.0)
+    for name, p in params.items():
+        wd = WEIGHT_DECAY if decayed(name, p.shape) else 0.0
+        adamw_step(p, *moments[name], grads[name] * coefficient, step, weight_decay=wd)
+    return loss_sum / len(batches), False, norm
 
 
 def adamw_step(param, m, v, grad, step, lr=LEARNING_RATE, betas=BETAS, eps=EPSILON,

@@ -115,3 +115,94 @@ def test_gpt2_loss_gradients_and_adamw_match_the_reference_model(golden):
         wd = oracle.WEIGHT_DECAY if oracle.decayed(name, p.shape) else 0.0
         oracle.adamw_step(p, m, v, grad, 1, weight_decay=wd)
         assert torch.allclose(p, torch.from_numpy(g["stepped/" + name]), rtol=1e-5, atol=1e-7), name
+
+
+# ---- float64 references and the optimizer (float_references.npz, optimizer.npz) --------------
+
+def close64(a, b, tol=1e-12):
+    return np.allclose(np.asarray(a, dtype=np.float64), np.asarray(b, dtype=np.float64), rtol=tol,
+                       atol=tol)
+
+
+@pytest.mark.parametrize("case", ["ln_a", "ln_b", "ln_c"])
+def test_layernorm_forward_matches_the_reference_float64(golden, case):
+    g = golden("float_references")
+    y, mean, rstd = oracle.layernorm_forward(g[case + "_x"], g[case + "_gamma"], g[case + "_beta"],
+                                             float(np.float32(1e-5)))
+    assert close64(mean, g[case + "_mean"]) and close64(rstd, g[case + "_rstd"], 1e-11)
+    assert close64(y, g[case + "_y"], 1e-10)
+
+
+@pytest.mark.parametrize("case", ["sm_a", "sm_b", "sm_c"])
+def test_causal_softmax_forward_matches_the_reference_float64(golden, case):
+    g = golden("float_references")
+    assert close64(oracle.causal_softmax_forward(g[case + "_s"]), g[case + "_p"])
+
+
+@pytest.mark.parametrize("case", ["ce_a", "ce_b", "ce_c"])
+def test_cross_entropy_matches_the_reference_float64(golden, case):
+    g = golden("float_references")
+    vocab = int(g[case + "_vocab"])
+    loss, grad = oracle.softmax_cross_entropy(g[case + "_logits"], g[case + "_targets"], 0.75, vocab)
+    assert close64(loss, g[case + "_loss"])
+    assert close64(grad[:, :vocab], g[case + "_grad"]) and not grad[:, vocab:].any()
+    rows = np.arange(len(loss))
+    assert close64(np.exp(-loss), g[case + "_p_target"])
+    assert (grad[rows, g[case + "_targets"]] < 0).all()
+
+
+def test_embedding_forward_matches_the_reference(golden):
+    g = golden("float_references")
+    _, length, _, _ = (int(v) for v in g["emb_shape"])
+    got = oracle.embedding_forward(g["emb_ids"], g["emb_wte"], g["emb_wpe"], length)
+    assert same_bits(got, g["emb_x"])
+
+
+@pytest.mark.parametrize("case", ["at_a", "at_b", "at_c"])
+def test_attention_matches_the_reference_float64(golden, case):
+    g = golden("float_references")
+    o, lse, dq, dk, dv = oracle.attention(g[case + "_q"], g[case + "_k"], g[case + "_v"], 0.125,
+                                          g[case + "_do"])
+    assert close64(o, g[case + "_o"], 1e-10)
+    assert close64(dq, g[case + "_dq"], 1e-10) and close64(dk, g[case + "_dk"], 1e-10)
+    assert close64(dv, g[case + "_dv"], 1e-10)
+    # The log-sum-exp against the scores' own definition.
+    s = np.einsum("bqd,bkd->bqk", g[case + "_q"].astype(np.float64),
+                  g[case + "_k"].astype(np.float64)) * 0.125
+    t = s.shape[1]
+    s = np.where(np.tril(np.ones((t, t), dtype=bool)), s, -np.inf)
+    assert close64(lse, np.log(np.exp(s - s.max(-1, keepdims=True)).sum(-1)) + s.max(-1), 1e-10)
+
+
+def test_gelu_helpers_match_the_reference_closed_forms(golden):
+    g = golden("float_references")
+    s = torch.from_numpy(g["gelu_s"])
+    assert close64(oracle.gelu_tanh(s), g["gelu_y"], 1e-14)
+    assert close64(oracle.gelu_exponent(s), g["gelu_exponent"], 1e-14)
+    margin = oracle.half_rounding_margin(oracle.gelu_tanh(s)).numpy()
+    finite = np.isfinite(g["gelu_margin"])
+    assert np.array_equal(finite, np.isfinite(margin))
+    assert close64(margin[finite], g["gelu_margin"][finite], 1e-9)
+    assert np.array_equal(oracle.half_ordered(s.half().numpy()).numpy(), g["gelu_ordered"])
+    derivative, exponent = oracle.gelu_tanh_derivative(s)
+    assert close64(derivative, g["dgelu_g"], 1e-13)
+    assert close64(-exponent, g["dgelu_a"], 1e-14)     # the reference names -a
+    assert same_bits(oracle.round_to_half(derivative * 3.0).numpy(), g["dgelu_rounded"])
+
+
+def test_three_clipped_adamw_steps_match_the_reference_optimizer(golden):
+    """oracle.clip_coefficient + oracle.adamw_step against torch.optim.AdamW and
+    clip_grad_norm_ as the reference configures them, on the reference's own gradients."""
+    g = golden("optimizer")
+    names = [str(n) for n in g["names"]]
+    params = {n: torch.from_numpy(g["start/" + n].copy()) for n in names}
+    moments = {n: (torch.zeros_like(p), torch.zeros_like(p)) for n, p in params.items()}
+    for step in (1, 2, 3):
+        grads = {n: torch.from_numpy(g[f"grad/{step}/" + n]) for n in names}
+        coefficient, norm = oracle.clip_coefficient(grads.values())
+        assert norm == pytest.approx(float(g[f"norm/{step}"]), rel=1e-5) and coefficient < 0.02
+        for n, p in params.items():
+            wd = oracle.WEIGHT_DECAY if oracle.decayed(n, p.shape) else 0.0
+            oracle.adamw_step(p, *moments[n], grads[n] * coefficient, step, weight_decay=wd)
+            want = torch.from_numpy(g[f"param/{step}/" + n])
+            assert torch.allclose(p, want, rtol=2e-6, atol=1e-8), (step, n)
