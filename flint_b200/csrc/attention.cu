@@ -23,6 +23,7 @@
 // [B, H, T, 64] or GPT-2's packed qkv rows [B*T, 3*H*64] without a split/merge
 // pass. Softmax runs in base 2: t = s * scale * log2(e), p = 2^(t - max).
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstdint>
 #include <cstring>
@@ -1189,7 +1190,7 @@ cudaError_t attention_forward(const AttentionView& o, float* lse, const Attentio
     p.out_head = o.head_stride;
     p.out_seq = o.sequence_stride;
     p.lse = lse;
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64] = {};
     e = fb::allow_shared_memory(fb_attention_forward, kFwdSmem, configured);
     if (e != cudaSuccess) {
         return e;
@@ -1237,7 +1238,7 @@ cudaError_t attention_backward(const AttentionView& dq, const AttentionView& dk,
     const unsigned items = static_cast<unsigned>(shape.sequences * shape.heads * p.blocks);
     const unsigned bwd_grid = std::min(items, static_cast<unsigned>(sms));
 
-    static bool dkv_configured[64] = {};
+    static std::atomic<bool> dkv_configured[64] = {};
     e = fb::allow_shared_memory(fb_attention_dkv, kBwdSmem, dkv_configured);
     if (e != cudaSuccess) {
         return e;
@@ -1253,7 +1254,7 @@ cudaError_t attention_backward(const AttentionView& dq, const AttentionView& dk,
     if (e != cudaSuccess) {
         return e;
     }
-    static bool dq_configured[64] = {};
+    static std::atomic<bool> dq_configured[64] = {};
     e = fb::allow_shared_memory(fb_attention_dq, kBwdSmem, dq_configured);
     if (e != cudaSuccess) {
         return e;

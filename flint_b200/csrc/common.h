@@ -6,6 +6,7 @@
 // match on them.
 #pragma once
 
+#include <atomic>
 #include <cstddef>
 #include <cstdint>
 
@@ -84,19 +85,21 @@ cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, s
 
 // Raises a kernel's dynamic shared-memory limit once per device (the attribute belongs
 // to the device's copy of the function); `done` is the caller's static per-kernel table.
+// Host threads may race on a first call: the slots are atomics and the attribute call is
+// idempotent, so two threads that both miss simply set it twice.
 template <typename Kernel>
-cudaError_t allow_shared_memory(Kernel kernel, int bytes, bool (&done)[64]) {
+cudaError_t allow_shared_memory(Kernel kernel, int bytes, std::atomic<bool> (&done)[64]) {
     int device = 0;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) {
         return e;
     }
-    if (device >= 0 && device < 64 && done[device]) {
+    if (device >= 0 && device < 64 && done[device].load(std::memory_order_relaxed)) {
         return cudaSuccess;
     }
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (e == cudaSuccess && device >= 0 && device < 64) {
-        done[device] = true;
+        done[device].store(true, std::memory_order_relaxed);
     }
     return e;
 }
@@ -132,6 +135,8 @@ cudaError_t launch_bias_gradient(void* dbias, const void* dy, size_t rows, size_
 // Device error word of the column-sum kernels: set when a bounded wait for a
 // staged row gave up (read, and cleared if asked, by flint_b200_kernel_fault).
 cudaError_t reductions_error_flag(int* value, bool reset);
+// The same for the cross-entropy kernel that stages whole rows by bulk copy.
+cudaError_t rowwise_error_flag(int* value, bool reset);
 
 }  // namespace fb
 

@@ -23,6 +23,7 @@
 // Reference behaviour: src/kernels/gemm.cu:419-587 (main loop and epilogues),
 // :733-784 (split rule) and src/api/gemm.cpp:27-454 (checks and messages).
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstdint>
 #include <cstdlib>
@@ -1467,7 +1468,7 @@ cudaError_t launch_tc(GemmParams& p, const void* x, const void* w, int sms, cuda
     const long long z = L == Layout::kTN && !batched ? p.splits : p.batches;
     p.tiles_total = static_cast<long long>(p.tiles_m) * p.tiles_n * z;
 
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64] = {};
     auto kernel = fb_gemm_tc<L, E, BN>;
     e = fb::allow_shared_memory(kernel, R::kSmemBytes, configured);
     if (e != cudaSuccess) {
@@ -1535,7 +1536,7 @@ cudaError_t launch_pair(GemmParams& p, const void* x, const void* w, int sms, cu
     const long long z = L == Layout::kTN && !batched ? p.splits : p.batches;
     p.tiles_total = static_cast<long long>(p.tiles_m) * p.tiles_n * z;
 
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64] = {};
     auto kernel = fb_gemm_pair<L, E>;
     e = fb::allow_shared_memory(kernel, kPairSmemBytes, configured);
     if (e != cudaSuccess) {

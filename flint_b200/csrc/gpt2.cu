@@ -119,7 +119,9 @@ flint_status size_workspaces(flint_gpt2& m) {
         most = std::max(most, bytes);
     }
     FB_TRY(flint_layernorm_backward_workspace(m.rows, w, &bytes));
-    most = std::max(most, bytes);
+    // The fused-attention model's LayerNorm backward writes dgamma's and dbeta's partial
+    // sums as two blocks of the public size, one behind the other.
+    most = std::max(most, m.flash ? 2 * bytes : bytes);
     FB_TRY(flint_embedding_backward_workspace(c.sequences, c.length, c.padded_vocab, w, &bytes));
     m.workspace_bytes = std::max(most, bytes);
 
@@ -301,6 +303,10 @@ flint_status allocate(flint_gpt2& m) {
         m.gradient_bytes = static_cast<size_t>(static_cast<char*>(last.gradient) -
                                                static_cast<char*>(m.gradient_base)) +
                            round_up(last.count() * 4);
+        // A trainer treats the arena as one FP32 array (non-finite check, all-reduce). The
+        // 256-byte rounding gaps between tensors are never written by backward, so they
+        // start as zeros rather than as whatever the allocation held.
+        FB_CUDA(cudaMemset(m.gradient_base, 0, m.gradient_bytes));
     }
     return FLINT_OK;
 }

@@ -438,7 +438,9 @@ flint_status flint_b200_kernel_fault(int* raised) {
     FB_CUDA(fb::attention_error_flag(&attention, true));
     int reductions = 0;
     FB_CUDA(fb::reductions_error_flag(&reductions, true));
-    *raised = (gemm != 0 || attention != 0 || reductions != 0) ? 1 : 0;
+    int rowwise = 0;
+    FB_CUDA(fb::rowwise_error_flag(&rowwise, true));
+    *raised = (gemm != 0 || attention != 0 || reductions != 0 || rowwise != 0) ? 1 : 0;
     return FLINT_OK;
 }
 

@@ -16,6 +16,7 @@
 // Argument checks follow src/api/bias_gradient.cpp:11-67,
 // src/api/layernorm.cpp:55-119 and src/api/embedding.cpp:55-134.
 #include <algorithm>
+#include <atomic>
 #include <cstdint>
 
 #include <cuda.h>
@@ -163,6 +164,7 @@ __global__ void __launch_bounds__(kTilePieces * (kLaneRows + 1))
     __syncthreads();
     volatile int* abort = &abort_flag;
     bool ok = true;
+    int issued = 0;  // fetching warp: stages whose copies have been started
     fb::Comp2 acc[4];
     constexpr bool kAlsoPlainSums = kPlain && kSource == Source::kHalfTimesXhat;
     fb::F2 also[4] = {0, 0, 0, 0};
@@ -179,6 +181,7 @@ __global__ void __launch_bounds__(kTilePieces * (kLaneRows + 1))
                 ok = false;
                 break;
             }
+            issued = k + 1;
             const int here = min(S::kRows, chunk_rows - k * S::kRows);
             if (maps.use != 0) {
                 // One tensor load per operand: the box is always delivered whole (zeros
@@ -327,10 +330,24 @@ __global__ void __launch_bounds__(kTilePieces * (kLaneRows + 1))
     if (!ok && px == 0) {
         atomicExch(&g_reduction_error, 1);
     }
-    // Every stage has been consumed (or the wait gave up): the ring's memory now
-    // carries the eight streams' (sum, error) pairs to stream 0, which merges them
-    // in stream order.
     __syncthreads();
+    if (abort_flag != 0) {
+        // A wait gave up (the flag was written before the barrier above, so every thread
+        // sees the same value). The error word is set; this CTA writes no sums. Before it
+        // leaves, the fetching warp waits, again with a limit, for the copies it started
+        // into the ring: shared memory must not be handed to another CTA with a copy
+        // still on its way.
+        if (ly == kLaneRows && px == 0) {
+            for (int k = max(0, issued - S::kStages); k < issued; ++k) {
+                int unused = 0;
+                staged_wait(full_bar(k % S::kStages), static_cast<uint32_t>(k / S::kStages) & 1u,
+                            &unused);
+            }
+        }
+        return;
+    }
+    // Every stage has been consumed: the ring's memory now carries the eight streams'
+    // (sum, error) pairs to stream 0, which merges them in stream order.
     float* sh_s = reinterpret_cast<float*>(staging_raw + (staging - shared_address(staging_raw)));
     float* sh_e = sh_s + kLaneRows * kTilePieces * 8;
     const size_t block_quads = size_t{gridDim.x} * pieces * 4;  // float4s in one block of partials
@@ -435,20 +452,20 @@ cudaError_t launch_partials(void* workspace, const void* src, const void* x, con
     const int pieces = static_cast<int>(cols / 8);
     const unsigned tiles = static_cast<unsigned>((pieces + kTilePieces - 1) / kTilePieces);
     constexpr int kDynamic = Staging<kSource>::kBytes;
-    static bool configured[64] = {};  // per instantiation and device
+    static std::atomic<bool> configured[64] = {};  // per instantiation and device
     int device = 0;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) {
         return e;
     }
-    if (device >= 64 || !configured[device]) {
+    if (device >= 64 || !configured[device].load(std::memory_order_relaxed)) {
         e = cudaFuncSetAttribute(fb_column_partials<kSource, kPlain>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, kDynamic);
         if (e != cudaSuccess) {
             return e;
         }
         if (device < 64) {
-            configured[device] = true;
+            configured[device].store(true, std::memory_order_relaxed);
         }
     }
     ColumnMaps maps;
@@ -1063,25 +1080,31 @@ static __device__ __align__(256) unsigned char g_bias_gradient_scratch[kStaticSc
 // In host code the array's name is only a handle for the runtime, not an address
 // a kernel can use; the device address comes from cudaGetSymbolAddress, asked
 // once per device while that device is current.
+// Host threads may make their first calls at the same time: the cache slots are
+// atomics, and two threads that both miss simply store the same address.
 cudaError_t static_scratch(void** pointer) {
     constexpr int kMaxDevices = 64;
-    static void* cached[kMaxDevices] = {};
+    static std::atomic<void*> cached[kMaxDevices] = {};
     int device = 0;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) {
         return e;
     }
-    if (device >= 0 && device < kMaxDevices && cached[device] != nullptr) {
-        *pointer = cached[device];
-        return cudaSuccess;
+    const bool slot = device >= 0 && device < kMaxDevices;
+    if (slot) {
+        void* known = cached[device].load(std::memory_order_relaxed);
+        if (known != nullptr) {
+            *pointer = known;
+            return cudaSuccess;
+        }
     }
     void* address = nullptr;
     e = cudaGetSymbolAddress(&address, g_bias_gradient_scratch);
     if (e != cudaSuccess) {
         return e;
     }
-    if (device >= 0 && device < kMaxDevices) {
-        cached[device] = address;
+    if (slot) {
+        cached[device].store(address, std::memory_order_relaxed);
     }
     *pointer = address;
     return cudaSuccess;
@@ -1140,13 +1163,14 @@ flint_status flint_b200_bias_gradient_static(void* dbias, const void* dy, size_t
                         "scratch holds %zu; use flint_bias_gradient with a workspace",
                         name, rows, cols, needed, kStaticScratchBytes);
     }
-    void* scratch = nullptr;
-    FB_CUDA(static_scratch(&scratch));
+    // Arguments are judged before any CUDA call, like everywhere else in the library.
     const fb::Span spans[] = {
         {"dbias", dbias, cols * 4},
         {"dy", dy, rows * cols * 2},
     };
     FB_TRY(fb::check_spans(name, spans, 1));
+    void* scratch = nullptr;
+    FB_CUDA(static_scratch(&scratch));
     // The first pass overwrites every partial sum the second pass reads, so what an
     // earlier call left in the array never matters and nothing needs clearing.
     FB_CUDA(fb::launch_bias_gradient(dbias, dy, rows, cols, accumulate != 0, scratch, stream,

@@ -13,6 +13,7 @@
 // Argument checks follow src/api/layernorm.cpp:11-51, src/api/softmax.cpp:11-76
 // and src/api/cross_entropy.cpp:9-49.
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstdint>
 
@@ -415,6 +416,10 @@ __device__ __forceinline__ float half_max8(const uint4& q) {
     return fmaxf(__low2float(m), __high2float(m));
 }
 
+// Set when a bounded wait in this file gave up; read and cleared by
+// flint_b200_kernel_fault through rowwise_error_flag.
+__device__ int g_rowwise_error = 0;
+
 // Persistent CTAs, one row at a time. Thread 0 streams each row's logits into
 // shared memory with one bulk asynchronous copy (two row buffers when they fit,
 // so the next row loads while this one is processed); the three passes (max on
@@ -466,10 +471,13 @@ __global__ void __launch_bounds__(kCeThreads, 1)
 
     int buffer = 0;
     uint32_t phase[2] = {0u, 0u};
+    bool aborted = false;
+    bool pending[2] = {blockIdx.x < rows, false};  // thread 0: copies started and not yet seen
     for (size_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const size_t next = row + gridDim.x;
         if (buffers == 2 && threadIdx.x == 0 && next < rows) {
             issue(next, buffer ^ 1);  // that buffer's readers finished at the last __syncthreads
+            pending[buffer ^ 1] = true;
         }
         // Wait for this row's bytes (bounded; on a timeout the row is skipped).
         {
@@ -493,9 +501,13 @@ __global__ void __launch_bounds__(kCeThreads, 1)
                 }
             }
             phase[buffer] ^= 1u;
-            if (!landed) {
+            // One decision for the whole block: a thread whose wait succeeded must not go
+            // on to the block-wide reductions below while others have given up.
+            if (__syncthreads_or(landed ? 0 : 1) != 0) {
+                aborted = true;
                 break;
             }
+            pending[buffer] = false;
         }
         const uint4* in = staged + static_cast<size_t>(buffer) * vocab_chunks;
         uint4* out = dlogits + row * chunks;
@@ -605,9 +617,33 @@ __global__ void __launch_bounds__(kCeThreads, 1)
         __syncthreads();  // everyone is done with this buffer before it is refilled
         if (buffers == 1 && threadIdx.x == 0 && next < rows) {
             issue(next, 0);
+            pending[0] = true;
         }
         if (buffers == 2) {
             buffer ^= 1;
+        }
+    }
+    if (aborted && threadIdx.x == 0) {
+        // The rows from here on were not computed: report it, and give the copies that were
+        // started a second, equally bounded chance to land before the CTA's shared memory
+        // is released. (The failed buffer's phase bit was already flipped above.)
+        atomicExch(&g_rowwise_error, 1);
+        for (int b = 0; b < 2; ++b) {
+            if (!pending[b]) {
+                continue;
+            }
+            const uint32_t parity = b == buffer ? phase[b] ^ 1u : phase[b];
+            const long long start = clock64();
+            uint32_t done = 0;
+            while (done == 0 && clock64() - start < 2000000000LL) {
+                asm volatile(
+                    "{\n.reg .pred p;\n"
+                    "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+                    "selp.u32 %0, 1, 0, p;\n}\n"
+                    : "=r"(done)
+                    : "r"(bar0 + 8u * b), "r"(parity)
+                    : "memory");
+            }
         }
     }
 }
@@ -850,6 +886,19 @@ __global__ void __launch_bounds__(kThreadsT, 1)
 
 }  // namespace
 
+namespace fb {
+
+cudaError_t rowwise_error_flag(int* value, bool reset) {
+    cudaError_t e = cudaMemcpyFromSymbol(value, g_rowwise_error, sizeof(int));
+    if (e == cudaSuccess && reset && *value != 0) {
+        const int zero = 0;
+        e = cudaMemcpyToSymbol(g_rowwise_error, &zero, sizeof(int));
+    }
+    return e;
+}
+
+}  // namespace fb
+
 extern "C" {
 
 flint_status flint_layernorm_forward(void* y, void* mean, void* rstd, const void* x,
@@ -1013,7 +1062,7 @@ flint_status flint_softmax_cross_entropy(void* dlogits, void* row_loss, const vo
     constexpr int kRollThreads = 512, kRollHeld = 13;
     static_assert(size_t{kRollThreads} * kRollHeld * 32 <= kMaxSmem, "the exponentials' planes");
     if (vocab_chunks <= static_cast<size_t>(kRollHeld) * kRollThreads) {
-        static bool roll_configured[64] = {};
+        static std::atomic<bool> roll_configured[64] = {};
         FB_CUDA(fb::allow_shared_memory(fb_softmax_cross_entropy_rolling<kRollThreads, kRollHeld>,
                                         static_cast<int>(kMaxSmem), roll_configured));
         FB_CUDA(fb::launch_dependent(fb_softmax_cross_entropy_rolling<kRollThreads, kRollHeld>,
@@ -1028,7 +1077,7 @@ flint_status flint_softmax_cross_entropy(void* dlogits, void* row_loss, const vo
     // Longer rows: only the vocab columns are staged as FP16; two row buffers when they fit.
     const size_t row_bytes = vocab_chunks * 16;
     const int buffers = 2 * row_bytes <= kMaxSmem ? 2 : 1;
-    static bool configured[64] = {};
+    static std::atomic<bool> configured[64] = {};
     FB_CUDA(fb::allow_shared_memory(fb_softmax_cross_entropy, static_cast<int>(kMaxSmem),
                                     configured));
     FB_CUDA(fb::launch_dependent(fb_softmax_cross_entropy, dim3(blocks), dim3(kCeThreads),

@@ -296,6 +296,17 @@ class Trainer:
             done = torch.cuda.Event()
             done.record(self.comm_stream)
             self.stream.wait_event(done)
+        self.apply_update()
+
+    def apply_update(self) -> None:
+        """The optimizer's half of a step on whatever the gradient arena holds (gradients
+        times the loss scale, already summed over the ranks): the non-finite check, the
+        optional clip of the unscaled gradients' global norm
+        (``scripts/gpt2_torch.py:186-188``: ``unscale_`` then ``clip_grad_norm_``) and one
+        AdamW launch that also writes the FP16 compute copies. A non-finite gradient leaves
+        weights and moments untouched (the kernels read the flag on the device)."""
+        c = self.config
+        inverse = 1.0 / self.scaler.scale
         self.found.zero_()
         clip = c.max_grad_norm > 0
         if clip:

@@ -15,9 +15,9 @@
 extern "C" {
 #endif
 
-/* 1 if a GEMM or attention kernel gave up on a barrier wait since the last
- * call (the flag is cleared), 0 otherwise. Synchronises the device; meant for
- * tests. */
+/* 1 if a kernel (GEMM, attention, column sums, cross-entropy) gave up on a
+ * bounded barrier wait since the last call (the flag is cleared), 0 otherwise.
+ * Synchronises the device; meant for tests. */
 FLINT_API flint_status flint_b200_kernel_fault(int* raised);
 
 /* Kernels this library has launched in this process so far (host counter). */

@@ -14,6 +14,8 @@ GOLDEN = ROOT / "tests" / "golden"
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (sm_100a)")
+    config.addinivalue_line("markers", "full_size: a GPU test at a benchmark configuration's whole "
+                                       "size (tens of seconds of CPU oracle time)")
 
 
 @pytest.fixture(scope="session")

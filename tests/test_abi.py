@@ -103,6 +103,10 @@ def test_validation_runs_before_any_cuda_call(flint):
     raises(flint, "heads of 64 columns from column 8 run past row_width (128)",
            lambda: flint.heads_split(16, 32, 1, 8, 2, 64, 128, 8, stream=s))
     raises(flint, "count", lambda: flint.fp32_to_fp16(16, 32, 2**63, stream=s))
+    raises(flint, "flint_b200_bias_gradient_static: dbias is null",
+           lambda: flint.bias_gradient_static(None, 32, 8, 8, False, stream=s))
+    raises(flint, "built-in scratch holds 4194304",
+           lambda: flint.bias_gradient_static(16, 32, 65536, 4096, False, stream=s))
     raises(flint, "needs 64 bytes of workspace, given 0",
            lambda: flint.bias_gradient(1 << 20, 2 << 20, 8, 8, False, None, 0, stream=s))
     # Zero-sized calls succeed with null pointers.

@@ -84,3 +84,24 @@ def test_attention_backward_is_deterministic_over_many_items(flint):
     assert not flint.kernel_fault()
     for a, b in zip(*runs):
         assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+
+
+@pytest.mark.parametrize("case", ["at_a", "at_b", "at_c"])
+def test_attention_matches_the_golden_vectors(flint, golden, case):
+    """Known answers made by the reference's float64 attention chain
+    (tests/golden/make_golden.py: float_references)."""
+    g = golden("float_references")
+    q, k, v, d_o = (torch.from_numpy(g[case + n]).to(DEV) for n in ("_q", "_k", "_v", "_do"))
+    batches, length, _ = q.shape
+    o = torch.zeros_like(q)
+    lse = torch.zeros(batches, length, device=DEV)
+    flint.attention_forward(o, lse, q, k, v, batches, length, 64, 0.125)
+    dq, dk, dv = (torch.zeros_like(q) for _ in range(3))
+    delta = torch.zeros(batches, length, device=DEV)
+    flint.attention_backward(dq, dk, dv, d_o, o, lse, delta, q, k, v, batches, length, 64, 0.125)
+    torch.cuda.synchronize()
+    assert not flint.kernel_fault()
+    assert rel_error(o, g[case + "_o"]) <= 2e-3
+    assert rel_error(dq, g[case + "_dq"]) <= 5e-3
+    assert rel_error(dk, g[case + "_dk"]) <= 5e-3
+    assert rel_error(dv, g[case + "_dv"]) <= 5e-3

@@ -256,3 +256,152 @@ def test_argument_errors_name_the_problem(flint):
     flint.gemm_nt(None, None, None, 0, 8, 8)
     flint.gemm_tn(None, None, None, 8, 0, 8)
     flint.gemm_nn_batched(None, None, None, 0, 8, 8, 8)
+
+
+# ---- the logits shapes of the GPT-2 sweep at full size ----------------------------------------
+# 8192 x 50304 x 768 and its two gradients. The float64 product of the whole matrix would take
+# minutes on the host, so sampled rows / columns are compared (every tile column of the output
+# is crossed by a sampled row and every tile row by a sampled column) and the rest is covered by
+# a checksum identity: the sum over an output row equals x_row . (sum of w's rows).
+
+VOCAB_COLUMNS = 50304
+
+
+def sample(count, size, seed):
+    g = torch.Generator().manual_seed(seed)
+    picked = torch.randperm(size, generator=g)[:count]
+    edge = torch.tensor([0, size - 1, size // 2])
+    return torch.unique(torch.cat([picked, edge]))
+
+
+def test_gemm_nt_at_the_full_logits_shape(flint):
+    m, n, k = GPT2_ROWS, VOCAB_COLUMNS, 768
+    x, w = inputs((m, k), (n, k), 50)
+    y = torch.zeros(m, n, dtype=torch.half, device=DEV)
+    flint.gemm_nt(y, x.to(DEV), w.to(DEV), m, n, k)
+    no_fault(flint)
+    rows = sample(48, m, 1)
+    assert rel_error(y[rows.to(DEV)], oracle.gemm_nt(x[rows], w)) <= 2e-3
+    cols = sample(48, n, 2)
+    assert rel_error(y[:, cols.to(DEV)], oracle.gemm_nt(x, w[cols])) <= 2e-3
+    # Every element takes part: row sums against x . sum(w) in float64.
+    want = x.double() @ w.double().sum(0)
+    got = y.double().sum(1).cpu()
+    scale = (x.double().abs() @ w.double().abs().sum(0))
+    assert ((got - want).abs() <= 2e-3 * scale).all()
+
+
+def test_gemm_nn_at_the_full_logits_gradient_shape(flint):
+    m, n, k = GPT2_ROWS, 768, VOCAB_COLUMNS
+    g = torch.Generator().manual_seed(51)
+    x = (torch.randn(m, k, generator=g) * 0.05).half()
+    w = (torch.randn(k, n, generator=g) * 0.02).half()
+    y = torch.zeros(m, n, dtype=torch.half, device=DEV)
+    flint.gemm_nn(y, x.to(DEV), w.to(DEV), m, n, k)
+    no_fault(flint)
+    rows = sample(48, m, 3)
+    assert rel_error(y[rows.to(DEV)], oracle.gemm_nn(x[rows], w)) <= 2e-3
+    cols = sample(24, n, 4)
+    assert rel_error(y[:, cols.to(DEV)], oracle.gemm_nn(x, w[:, cols])) <= 2e-3
+
+
+def test_gemm_tn_at_the_full_tied_weight_gradient_shape(flint):
+    m, n, k = VOCAB_COLUMNS, 768, GPT2_ROWS
+    g = torch.Generator().manual_seed(52)
+    x = (torch.randn(k, m, generator=g) * 0.05).half()
+    w = torch.randn(k, n, generator=g).half()
+    ws = torch.empty(max(flint.gemm_tn_workspace(m, n, k), 16), dtype=torch.uint8, device=DEV)
+    xd, wd = x.to(DEV), w.to(DEV)
+    y = torch.full((m, n), 3.0, device=DEV)
+    flint.gemm_tn(y, xd, wd, m, n, k, False, ws)
+    old = torch.randn(m, n, generator=g).to(DEV)
+    acc = old.clone()
+    flint.gemm_tn(acc, xd, wd, m, n, k, True, ws)
+    no_fault(flint)
+    rows = sample(48, m, 5)
+    assert rel_error(y[rows.to(DEV)], oracle.gemm_tn(x[:, rows], w)) <= 1e-4
+    cols = sample(16, n, 6)
+    assert rel_error(y[:, cols.to(DEV)], oracle.gemm_tn(x, w[:, cols])) <= 1e-4
+    assert torch.equal(acc, old + y)
+
+
+# ---- the GELU and its derivative, point by point -------------------------------------------------
+# With x = 0 every sum is exactly the bias, so y must be GELU(bias) rounded once to FP16; with
+# a one-hot x and w every sum is exactly dh, so y must be dh * GELU'(pre) rounded once. The
+# bounds are the reference's (tests/test_gemm_bias_gelu.py:255-306, tests/test_gemm_dgelu.py:377-406):
+# within one FP16 ulp everywhere, and the correctly rounded value wherever the exact result is
+# farther from a rounding boundary than the FP32 evaluation's error model.
+
+
+def gelu_sweep():
+    g = torch.Generator().manual_seed(7)
+    grid = torch.linspace(-12.0, 12.0, 32768, dtype=torch.float64)
+    random = torch.rand(16384, generator=g, dtype=torch.float64) * 24 - 12
+    extremes = []
+    for magnitude in (1e-40, 1e-30, 2.0 ** -25, 6e-8, 1e-5, 65504.0, 65519.0, 65520.0, 65536.0, 1e5,
+                      1e6, 1e30, 3.4028234e38, 20.0, 30.0, 100.0, 1000.0, 1e4, 65000.0):
+        extremes += [magnitude, -magnitude]
+    extremes.append(0.0)
+    return torch.cat([grid, random, torch.tensor(extremes, dtype=torch.float64)]).float()
+
+
+def test_gelu_is_the_correctly_rounded_function_of_the_unrounded_sum(flint):
+    bias = gelu_sweep()
+    n = bias.numel()
+    m, k = 2, 8
+    x = torch.zeros(m, k, dtype=torch.half, device=DEV)
+    w = torch.ones(n, k, dtype=torch.half, device=DEV)
+    y = torch.zeros(m, n, dtype=torch.half, device=DEV)
+    pre = torch.zeros_like(y)
+    flint.gemm_nt_bias_gelu(y, pre, x, w, bias.to(DEV), m, n, k)
+    no_fault(flint)
+    y, pre = y.cpu(), pre.cpu()
+    assert torch.equal(pre.view(torch.int16), bias.half().expand(m, n).contiguous().view(torch.int16))
+    assert torch.equal(y[0].view(torch.int16), y[1].view(torch.int16))
+    exact64 = oracle.gelu_tanh(bias.double())
+    exact = oracle.round_to_half(exact64)
+    distance = (oracle.half_ordered(y[0]) - oracle.half_ordered(exact)).abs()
+    assert distance.max().item() <= 1, bias[distance.argmax()].item()
+    safe = oracle.half_rounding_margin(exact64) > 2.0 ** -21 * (2 + oracle.gelu_exponent(bias).abs())
+    assert safe.sum() > 0.95 * n
+    wrong = safe & (oracle.half_ordered(y[0]) != oracle.half_ordered(exact))
+    assert not wrong.any(), (int(wrong.sum()), bias[wrong][0].item())
+    # GELU of the FP32 sum, not of the sum rounded to FP16 first.
+    from_pre = oracle.round_to_half(oracle.gelu_tanh(bias.half().double()))
+    differs = safe & (oracle.half_ordered(from_pre) != oracle.half_ordered(exact))
+    assert differs.sum() > 1000
+    assert (oracle.half_ordered(y[0])[differs] != oracle.half_ordered(from_pre)[differs]).all()
+
+
+def test_gelu_derivative_is_within_one_ulp_and_correctly_rounded_where_that_is_defined(flint):
+    all_bits = torch.arange(-32768, 32768, dtype=torch.int32).to(torch.int16)
+    values = all_bits.view(torch.float16)
+    s = values[torch.isfinite(values)]
+    n = s.numel()
+    assert n == 63488
+    sweep_dh = [1.0, 1000.0, 2.0 ** -10, -1.0, -3.0, float(np.float16(0.1))]
+    m, k = len(sweep_dh), 8
+    x = torch.zeros(m, k, dtype=torch.half)
+    x[:, 0] = torch.tensor(sweep_dh).half()
+    w = torch.zeros(k, n, dtype=torch.half)
+    w[0] = 1
+    y = torch.zeros(m, n, dtype=torch.half, device=DEV)
+    flint.gemm_nn_dgelu(y, x.to(DEV), w.to(DEV), s[None, :].expand(m, n).contiguous().to(DEV), m, n, k)
+    no_fault(flint)
+    y = y.cpu()
+    g, a = oracle.gelu_tanh_derivative(s)           # a is the forward form's exponent (-2c(...))
+    dh = x[:, 0].double()[:, None]
+    v = dh * g[None, :]
+    exact = oracle.round_to_half(v)
+    root, window, root_e = -0.7525, 0.25, 1e-7       # the derivative's zero: absolute bound there
+    near_root = ((s.double() - root).abs() < window)[None, :].expand(m, n)
+    distance = (oracle.half_ordered(y) - oracle.half_ordered(exact)).abs()
+    close = (y.double() - v).abs() <= dh.abs() * root_e
+    wrong = (distance > 1) & ~(near_root & close)
+    assert not wrong.any(), int(wrong.sum())
+    relative = 2.0 ** -21 * (2 + a.clamp(min=0))
+    absolute = torch.where(near_root[0], root_e / g.abs(), torch.zeros_like(g))
+    safe = oracle.half_rounding_margin(v) > (relative + absolute)[None, :]
+    assert safe.sum() > 0.95 * safe.numel()
+    wrong = safe & (oracle.half_ordered(y) != oracle.half_ordered(exact))
+    assert not wrong.any(), int(wrong.sum())

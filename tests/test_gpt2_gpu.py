@@ -266,3 +266,31 @@ def test_accumulated_micro_batches_equal_one_large_batch(flint, case):
     assert abs(loss - want_loss) <= 1e-5
     assert cosine(got - start, want - start) >= 0.999
     assert not flint.kernel_fault()
+
+
+def test_trainer_on_the_reference_layout_with_a_width_that_leaves_gaps_in_the_arena(flint):
+    """Width 72: 72 * 4 bytes is not a multiple of the arena's 256-byte rounding, so there
+    are gaps between the gradient tensors that backward never writes. The trainer checks and
+    reduces the arena as one array; the gaps start as zeros, so no step is skipped."""
+    cfg = dict(n_layer=2, n_head=3, n_embd=72, block_size=64, vocab_size=200, padded_vocab_size=208)
+    params = oracle.gpt2_round_to_half(oracle.gpt2_init(cfg, seed=1234))
+    idx, targets = oracle.synthetic_tokens(2, 64, 200, seed=8)
+    want_loss, _ = oracle.gpt2_loss_and_gradients(cfg, params, idx, targets)
+    config = TrainerConfig(layers=2, heads=3, width=72, block_size=64, vocab=200, padded_vocab=208,
+                           sequences=2, length=64, loss_scale=1024.0, flash_attention=False)
+    trainer = Trainer(flint, config, state=params)
+    try:
+        for _ in range(2):
+            trainer.step(u16(idx.flatten()), u16(targets.flatten()))
+            loss = trainer.finish_step()
+        assert trainer.skipped == 0 and trainer.scaler.scale == 1024.0
+        assert np.isfinite(loss)
+    finally:
+        trainer.close()
+    trainer = Trainer(flint, config, state=params)
+    try:
+        trainer.step(u16(idx.flatten()), u16(targets.flatten()))
+        assert abs(trainer.finish_step() - want_loss) <= 1e-2
+        assert trainer.skipped == 0
+    finally:
+        trainer.close()

@@ -417,3 +417,133 @@ def test_cross_entropy_with_extreme_and_non_finite_logits(flint):
     for r in (3, 4):
         assert np.isnan(got[r, :vocab]).all(), r
         assert np.isnan(got_loss[r]), r
+
+
+# ---- known answers from the reference's float64 references (tests/golden/float_references.npz) ----
+
+
+def ulp16_of(want):
+    return np.spacing(np.abs(np.asarray(want)).astype(np.float16)).astype(np.float64)
+
+
+@pytest.mark.parametrize("case", ["ln_a", "ln_b", "ln_c"])
+def test_layernorm_forward_matches_the_golden_vectors(flint, golden, case):
+    g = golden("float_references")
+    x, gamma, beta = (torch.from_numpy(g[case + k]).to(DEV) for k in ("_x", "_gamma", "_beta"))
+    rows, cols = x.shape
+    y = torch.zeros(rows, cols, dtype=torch.half, device=DEV)
+    mean, rstd = torch.zeros(rows, device=DEV), torch.zeros(rows, device=DEV)
+    flint.layernorm_forward(y, mean, rstd, x, gamma, beta, rows, cols, 1e-5)
+    torch.cuda.synchronize()
+    assert ulps32(mean.cpu().numpy(), g[case + "_mean"]).max() <= 1.5
+    assert ulps32(rstd.cpu().numpy(), g[case + "_rstd"]).max() <= 3.0
+    want = g[case + "_y"]
+    assert (np.abs(y.cpu().numpy().astype(np.float64) - want) <= ulp16_of(want) + 1e-7).all()
+    if case == "ln_a":  # the constant row: mean exact, y exactly beta rounded
+        assert mean[2].item() == 4.25
+        assert same_bits(y[2], beta.half())
+
+
+@pytest.mark.parametrize("case", ["sm_a", "sm_b", "sm_c"])
+def test_causal_softmax_forward_matches_the_golden_vectors(flint, golden, case):
+    g = golden("float_references")
+    s = torch.from_numpy(g[case + "_s"]).to(DEV)
+    batches, length, _ = s.shape
+    p = torch.full_like(s, 7.0)
+    flint.causal_softmax_forward(p, s, batches, length)
+    torch.cuda.synchronize()
+    want = g[case + "_p"]
+    assert (np.abs(p.cpu().numpy().astype(np.float64) - want) <= ulp16_of(want)).all()
+
+
+@pytest.mark.parametrize("case", ["ce_a", "ce_b", "ce_c"])
+def test_cross_entropy_matches_the_golden_vectors(flint, golden, case):
+    g = golden("float_references")
+    logits = torch.from_numpy(g[case + "_logits"]).to(DEV)
+    targets = g[case + "_targets"]
+    vocab = int(g[case + "_vocab"])
+    rows, cols = logits.shape
+    dl = torch.full((rows, cols), 9.0, dtype=torch.half, device=DEV)
+    loss = torch.zeros(rows, device=DEV)
+    flint.softmax_cross_entropy(dl, loss, logits, tokens16(targets), 0.75, rows, vocab, cols)
+    torch.cuda.synchronize()
+    assert np.allclose(loss.cpu().numpy(), g[case + "_loss"], rtol=2e-6, atol=2e-6)
+    got = dl.cpu().numpy().astype(np.float64)
+    want = g[case + "_grad"]
+    assert (np.abs(got[:, :vocab] - want) <= ulp16_of(want)).all()
+    assert (got[:, vocab:] == 0).all()
+    assert (got[np.arange(rows), targets] < 0).all() and ((got < 0).sum(1) == 1).all()
+
+
+def test_embedding_forward_matches_the_golden_vectors(flint, golden):
+    g = golden("float_references")
+    seqs, length, vocab, width = (int(v) for v in g["emb_shape"])
+    x = torch.zeros(seqs * length, width, device=DEV)
+    flint.embedding_forward(x, tokens16(g["emb_ids"]), torch.from_numpy(g["emb_wte"]).to(DEV),
+                            torch.from_numpy(g["emb_wpe"]).to(DEV), seqs, length, vocab, width)
+    torch.cuda.synchronize()
+    assert same_bits(x, g["emb_x"])
+
+
+# ---- what embedding backward leaves in its workspace ------------------------------------------
+
+
+def embedding_workspace_parts(ws, sequences, length, vocab, width):
+    """(sorted tokens, sorted rows, offsets, position partial sums, position partial errors)
+    read from the workspace. Its layout is part of the interface: the position-table partial
+    sums first (the bias gradient's workspace for dx viewed as sequences x (length * width)),
+    then, each 16-byte aligned, the sorted tokens (uint16), their rows (uint32) and
+    offsets[vocab + 1] (uint32) (src/kernels/embedding_backward.cuh:31-79 in the reference)."""
+    up = lambda b: -(-b // 16) * 16
+    rows = sequences * length
+    chunks = -(-sequences // 256)
+    cols = length * width
+    raw = ws.cpu().numpy()
+    partials = raw[: chunks * cols * 8].view(np.float32).reshape(chunks, 2, cols)
+    at = up(chunks * cols * 8)
+    tokens = raw[at:at + rows * 2].view(np.uint16)
+    at += up(rows * 2)
+    sorted_rows = raw[at:at + rows * 4].view(np.uint32)
+    at += up(rows * 4)
+    offsets = raw[at:at + (vocab + 1) * 4].view(np.uint32)
+    return tokens, sorted_rows, offsets, partials[:, 0], partials[:, 1]
+
+
+@pytest.mark.parametrize("case", ["eb_a", "eb_b", "eb_c"])
+def test_embedding_backward_workspace_holds_the_sorted_tokens_rows_and_offsets(flint, golden, case):
+    g = golden("embedding_backward")
+    seqs, length, vocab, width = (int(v) for v in g[case + "_shape"])
+    ws = workspace(flint.embedding_backward_workspace(seqs, length, vocab, width))
+    ws.fill_(0xA5)
+    dwte = torch.zeros(vocab, width, device=DEV)
+    dwpe = torch.zeros(length, width, device=DEV)
+    flint.embedding_backward(dwte, dwpe, torch.from_numpy(g[case + "_dx"]).to(DEV),
+                             tokens16(g[case + "_tokens"]), seqs, length, vocab, width, False, False, ws)
+    torch.cuda.synchronize()
+    tokens, rows, offsets, _, _ = embedding_workspace_parts(ws, seqs, length, vocab, width)
+    assert np.array_equal(tokens, g[case + "_sorted_tokens"].astype(np.uint16))
+    assert np.array_equal(rows, g[case + "_sorted_rows"].astype(np.uint32))
+    assert np.array_equal(offsets, g[case + "_offsets"].astype(np.uint32))
+
+
+def test_embedding_backward_workspace_at_gpt2_size_matches_the_oracle(flint):
+    seqs, length, vocab, width = 8, 1024, 50304, 768
+    rng = np.random.default_rng(12)
+    tokens = rng.integers(0, 50257, seqs * length).astype(np.uint16)
+    tokens[::5] = 50256  # a token above 2^15 repeated many times
+    dx = crafted(rng, (seqs * length, width), 3).astype(np.float32)
+    ws = workspace(flint.embedding_backward_workspace(seqs, length, vocab, width))
+    dwte = torch.zeros(vocab, width, device=DEV)
+    dwpe = torch.zeros(length, width, device=DEV)
+    flint.embedding_backward(dwte, dwpe, torch.from_numpy(dx).to(DEV), tokens16(tokens), seqs,
+                             length, vocab, width, False, False, ws)
+    torch.cuda.synchronize()
+    _, _, want_tokens, want_rows, want_offsets = oracle.embedding_backward(dx, tokens, seqs, length, vocab)
+    got_tokens, got_rows, got_offsets, sums, errors = embedding_workspace_parts(ws, seqs, length, vocab, width)
+    assert np.array_equal(got_tokens, want_tokens.astype(np.uint16))
+    assert np.array_equal(got_rows, want_rows.astype(np.uint32))
+    assert np.array_equal(got_offsets, want_offsets.astype(np.uint32))
+    # The position table's partial sums are the column-sum scheme's over [sequences, length * width].
+    want_s, want_e, _ = oracle._column_sums(dx.reshape(seqs, length * width))
+    assert same_bits(torch.from_numpy(sums.copy()), want_s)
+    assert same_bits(torch.from_numpy(errors.copy()), want_e)

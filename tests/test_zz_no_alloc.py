@@ -6,7 +6,7 @@ budget, or a loop that cannot take cudaMalloc's device-wide synchronisation). Th
 entry point keeps its partial sums in an array built into the library. The test calls
 it through the C ABI twice in a row, with different shapes so the second call finds the
 first one's leftovers in the shared array, and requires the same bits as
-flint_bias_gradient each time. The file sorts last so a run that stops at the first
+flint_bias_gradient, and as the CPU oracle's emulation of the pinned order, each time. The file sorts last so a run that stops at the first
 failure has already exercised every other test.
 """
 
@@ -15,6 +15,7 @@ import pytest
 import torch
 
 import flint_b200
+import flint_oracle as oracle
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -37,6 +38,8 @@ def test_static_scratch_matches_the_workspace_version_on_consecutive_calls(flint
         flint.bias_gradient_static(got, dy, rows, cols, False)
         torch.cuda.synchronize()
         assert torch.equal(got.view(torch.int32), want.view(torch.int32))
+        from_oracle = torch.from_numpy(oracle.bias_gradient(dy.cpu().numpy()))
+        assert torch.equal(got.cpu().view(torch.int32), from_oracle.view(torch.int32))
         # Accumulating adds the same sums to what is there, with one FP32 add each.
         old = torch.arange(cols, dtype=torch.float32, device=DEV)
         acc_want = old.clone()
@@ -55,3 +58,13 @@ def test_static_scratch_rejects_shapes_beyond_its_size(flint):
         flint.bias_gradient_static(out, dy, rows, cols, False)
     assert error.value.status == flint_b200.ERROR_INVALID_ARGUMENT
     flint.bias_gradient_static(None, None, 1, 0, False)  # zero columns: nothing to do
+
+
+def test_static_scratch_names_a_bad_pointer_like_every_other_entry_point(flint):
+    dy = torch.zeros(64, 8, dtype=torch.half, device=DEV)
+    out = torch.zeros(8, device=DEV)
+    with pytest.raises(flint_b200.FlintError, match="dbias is null") as error:
+        flint.bias_gradient_static(None, dy, 64, 8, False)
+    assert error.value.status == flint_b200.ERROR_INVALID_ARGUMENT
+    with pytest.raises(flint_b200.FlintError, match="dy is not 16-byte aligned"):
+        flint.bias_gradient_static(out, dy.data_ptr() + 2, 32, 8, False)
