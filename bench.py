@@ -4,7 +4,7 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
     python bench.py --impl reference ...                      (the CPU arm)
 
-Workload: BASELINE's data-parallel training configuration: GPT-2 124M (12 layers, width 768,
+Workload: the data-parallel training configuration: GPT-2 124M (12 layers, width 768,
 12 heads, vocabulary 50257 padded to 50304, context 1024), a micro-batch of 16 x 1024 tokens
 per GPU of seeded uniform token ids, forward + backward with fused attention, FP32 gradient
 all-reduce over NCCL overlapped with backward, AdamW and dynamic loss scaling; FP16 operands
@@ -14,13 +14,18 @@ The JSON line's `value` is timed with the batches already in HBM; `e2e` is the s
 through Trainer.step()/finish_step() with the tokens copied from pinned host memory and the
 loss read back every step. `roofline` describes the dominant kernel, the tensor-core GEMM:
 all of one step's GEMM launches are replayed on the launch stream between CUDA events and
-their algorithmic FLOPs (2 m n k each) divided by the measured time. `cpu_baseline` times
-the CPU oracle (a port of the reference's PyTorch FP32 model) on the host cores.
+their algorithmic FLOPs (2 m n k each) divided by the measured time; `roofline.per_kernel`
+(one GPU only) is the per-kernel sweep of flint_b200.kernel_bench in its short form: every
+GEMM shape, fused epilogue, attention and row-wise kernel beside its cuBLAS / cuBLASLt / ATen
+counterpart, with fractions of the nominal and measured peaks. `cpu_baseline` and
+`--impl reference` time the CPU oracle (a port of the reference's PyTorch FP32 model) on all
+the host cores, each step a bounded sample of 1 x 1024 tokens of the same workload.
 """
 
 import argparse
 import json
 import os
+import re
 import statistics
 import subprocess
 import sys
@@ -105,15 +110,24 @@ def step_gemms(rows: int):
                                             ("nn", rows, w, v)]
 
 
-# DRAM bytes (read + write) per GEMM call, averaged over the 147 calls of one step's replay
-# below: `dram__bytes_read.sum + dram__bytes_write.sum` summed over the replay's kernels in the
-# ncu capture summarised in profiles/gemm_step_replay_gpt2_124m.md.
-GEMM_TRAFFIC_BYTES_PER_LAUNCH = 167.1e6
+def gemm_traffic():
+    """(DRAM bytes read + written per GEMM call, commit it was captured on) from the committed
+    ncu summary of the replay below, or (None, None). The summary carries one line of the form
+    `roofline.traffic: <bytes> bytes per GEMM call, captured on commit <sha>`."""
+    path = ROOT / "profiles" / "gemm_step_replay_gpt2_124m.md"
+    if path.is_file():
+        found = re.search(r"roofline\.traffic:\s*([0-9.eE+]+) bytes per GEMM call, captured on commit (\w+)",
+                          path.read_text())
+        if found:
+            return float(found.group(1)), found.group(2)
+    return None, None
 
 
 def gemm_roofline(flint, torch, rows: int, reps: int = 3):
     """Replays one step's GEMM launches, with the epilogues the model uses, between CUDA
-    events on the launch stream."""
+    events on the launch stream. The buffers are fixed, so consecutive calls find the 25 MB
+    activations and the weights of the call before in the 126 MB L2, as they do inside the
+    real step: the per-shape numbers with operands rotated past the L2 are in `per_kernel`."""
     dev = "cuda"
     shapes = step_gemms(rows)
     a = torch.randn(rows * 50304, device=dev).half()      # big enough for every operand
@@ -160,63 +174,108 @@ def gemm_roofline(flint, torch, rows: int, reps: int = 3):
             "achieved": round(achieved, 1), "peak": peak, "unit": "TFLOP/s",
             "frac": round(achieved / peak, 4), "peak_source": source + " (sustained bf16 GEMM)",
             "launches_per_step": len(shapes), "avg_launch_us": round(seconds / len(shapes) * 1e6, 2),
-            "traffic": GEMM_TRAFFIC_BYTES_PER_LAUNCH}
+            "operands": "fixed buffers (L2-warm between consecutive calls, as in the step)",
+            "traffic": gemm_traffic()[0], "traffic_captured_on": gemm_traffic()[1]}
 
 
-def cpu_step_tokens_per_second(budget_seconds: float, threads=None):
-    """The CPU oracle's training step (FP32 forward, backward and AdamW of GPT-2 124M) on
-    1 x 1024 tokens per step, repeated while the budget lasts. Returns (tokens/s, cores, sample)."""
-    import torch
+def host_cores() -> int:
+    """Cores this process may run on (the launcher's OMP_NUM_THREADS=1 does not count)."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
 
-    sys.path.insert(0, str(ROOT / "oracle"))
-    import flint_oracle as oracle
 
-    if threads:
-        torch.set_num_threads(threads)
-    cores = torch.get_num_threads()
-    cfg = oracle.GPT2
-    params = oracle.gpt2_init(cfg, seed=1234)
-    moments = {k: (torch.zeros_like(v), torch.zeros_like(v)) for k, v in params.items()}
-    sequences, length = 1, 1024
-    idx, targets = oracle.synthetic_tokens(sequences, length, cfg["vocab_size"], seed=1)
+class CpuStep:
+    """The CPU oracle's training step (FP32 forward, backward and AdamW of GPT-2 124M) on a
+    bounded sample of the workload: 1 x 1024 tokens per step, on every host core."""
 
-    def one(step):
-        _, grads = oracle.gpt2_loss_and_gradients(cfg, params, idx, targets)
-        for name, p in params.items():
-            wd = oracle.WEIGHT_DECAY if oracle.decayed(name, p.shape) else 0.0
-            oracle.adamw_step(p, *moments[name], grads[name], step, weight_decay=wd)
+    SEQUENCES, LENGTH = 1, 1024
 
-    one(1)  # warm-up
-    done, begin = 0, time.perf_counter()
-    while done < 8 and (done == 0 or time.perf_counter() - begin < budget_seconds):
-        one(done + 2)
-        done += 1
-    seconds = time.perf_counter() - begin
-    sample = (f"{done} steps of {sequences}x{length} tokens (GPT-2 124M FP32 forward+backward+AdamW, "
-              f"torch CPU, {cores} threads) after 1 warm-up")
-    return sequences * length * done / seconds, cores, sample, seconds / done
+    def __init__(self):
+        import torch
+
+        sys.path.insert(0, str(ROOT / "oracle"))
+        import flint_oracle as oracle
+
+        # torch.distributed.run exports OMP_NUM_THREADS=1 to its workers; the baseline is
+        # the reference's PyTorch path on all the cores the process may use.
+        self.cores = host_cores()
+        torch.set_num_threads(self.cores)
+        self.oracle = oracle
+        self.params = oracle.gpt2_init(oracle.GPT2, seed=1234)
+        self.moments = {k: (torch.zeros_like(v), torch.zeros_like(v)) for k, v in self.params.items()}
+        self.batch = oracle.synthetic_tokens(self.SEQUENCES, self.LENGTH, oracle.GPT2["vocab_size"], seed=1)
+        self.step = 0
+
+    def run(self, steps: int) -> float:
+        """Runs `steps` optimizer steps; returns the seconds they took."""
+        begin = time.perf_counter()
+        for _ in range(steps):
+            self.step += 1
+            self.oracle.train_step(self.oracle.GPT2, self.params, self.moments, [self.batch], self.step,
+                                   max_grad_norm=0.0)
+        return time.perf_counter() - begin
+
+    def sample(self, warmup: int, steps: int) -> str:
+        return (f"{steps} steps of {self.SEQUENCES}x{self.LENGTH} tokens each (GPT-2 124M FP32 forward + "
+                f"backward + AdamW, torch CPU, {self.cores} threads) after {warmup} warm-up steps; the "
+                f"GPU arm's step is 16x1024 tokens per GPU")
+
+
+def static_config(world: int) -> dict:
+    """What both arms measure; identical in the two JSON lines."""
+    return {"workload": WORKLOAD, "tokens_per_gpu_per_step": SEQUENCES * LENGTH,
+            "parallelism": f"dp{world}",
+            "l2": "each step streams several GB of activations and weights, far more than the "
+                  "126 MB L2, so no flush is needed between steps"}
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    value, cores, sample, step_seconds = cpu_step_tokens_per_second(
-        budget_seconds=max(10.0, 4.0 * args.steps))
+    cpu = CpuStep()
+    cpu.run(args.warmup)
+    seconds = cpu.run(args.steps)
+    tokens = CpuStep.SEQUENCES * CpuStep.LENGTH * args.steps
+    value = tokens / seconds
     line = {
         "impl": "reference", "metric": METRIC, "value": round(value, 2), "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(step_seconds * 1e3, 2), "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": round(seconds / args.steps * 1e3, 2), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "note": "CPU oracle port of the reference's PyTorch "
-                   "model; each step is a bounded sample of 1x1024 tokens"},
-        "cpu_baseline": {"value": round(value, 2), "unit": "tokens/s", "cores": cores,
-                         "kind": "port", "sample": sample},
+        "config": static_config(args.gpus),
+        "cpu_baseline": {"value": round(value, 2), "unit": "tokens/s", "cores": cpu.cores,
+                         "kind": "port", "sample": cpu.sample(args.warmup, args.steps)},
         "e2e": {"value": round(value, 2), "unit": "tokens/s", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def per_kernel_summary(flint):
+    """The per-kernel sweep in its short form (3 rounds of 25 ms samples per arm), condensed
+    to one small object per case."""
+    from flint_b200 import kernel_bench
+
+    results = kernel_bench.run(flint, list(kernel_bench.GROUPS), 8192, quick=True)
+    out = []
+    for r in results:
+        base, ratio = r["baseline"], r["flint_over_baseline"]
+        out.append({"case": r["case"], "us": r["flint"]["us"], "rate": r["flint"]["rate"],
+                    "unit": r["unit"], "frac_nominal": r["flint"]["frac_nominal"],
+                    "frac_measured": r["flint"]["frac_measured"],
+                    "baseline_us": base["us"] if base else None,
+                    "flint_over_baseline": ratio["median"] if ratio else None,
+                    "sm_mhz": r["sm_mhz_median"]})
+    return {"protocol": "operands rotated past 4x L2, 3 interleaved rounds of 25 ms samples per arm "
+                        "(python -m flint_b200.kernel_bench runs 10 rounds of 100 ms); baseline = "
+                        "cuBLAS / cuBLASLt / ATen through torch",
+            "nominal_peaks": {"TFLOP/s": kernel_bench.NOMINAL_TFLOPS, "GB/s": kernel_bench.NOMINAL_GBS},
+            "measured_peaks": dict(zip(("TFLOP/s", "GB/s"), kernel_bench.measured_peaks()[:2])),
+            "cases": out}
 
 
 def run_flint(args):
@@ -305,28 +364,35 @@ def run_flint(args):
         raise RuntimeError("a tensor-core kernel gave up on a barrier wait during the bench")
 
     roofline = gemm_roofline(flint, torch, rows) if rank == 0 else None
+    run_facts = {"loss_scale": trainer.scaler.scale, "skipped_steps": trainer.skipped,
+                 "last_loss": round(last_loss, 4)}
+    trainer.close()
+    trainer = None
+    torch.cuda.empty_cache()
+    if rank == 0 and world == 1 and not args.no_per_kernel:
+        roofline["per_kernel"] = per_kernel_summary(flint)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        value, cores, sample, _ = cpu_step_tokens_per_second(budget_seconds=15.0)
-        cpu = {"value": round(value, 2), "unit": "tokens/s", "cores": cores, "kind": "port",
-               "sample": sample}
+        step = CpuStep()
+        step.run(2)
+        steps = 12
+        seconds = step.run(steps)
+        value = CpuStep.SEQUENCES * CpuStep.LENGTH * steps / seconds
+        cpu = {"value": round(value, 2), "unit": "tokens/s", "cores": step.cores, "kind": "port",
+               "sample": step.sample(2, steps)}
     if rank == 0:
         peak, _, _ = peaks()
+        run_facts["model_tflops"] = round(tokens_per_second * FLOPS_PER_TOKEN / 1e12, 1)
+        run_facts["mfu_of_sustained_peak"] = round(
+            tokens_per_second * FLOPS_PER_TOKEN / 1e12 / (peak * world), 4)
         line = {
             "metric": METRIC, "value": round(tokens_per_second, 1), "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms / args.steps, 3), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "fp16 (fp32 accumulate)",
             "data": "synthetic",
-            "config": {"workload": WORKLOAD, "tokens_per_gpu_per_step": rows,
-                       "parallelism": f"dp{world}",
-                       "l2": "each step streams several GB of activations and weights, far "
-                             "more than the 126 MB L2, so no flush is needed between steps",
-                       "loss_scale": trainer.scaler.scale, "skipped_steps": trainer.skipped,
-                       "last_loss": round(last_loss, 4),
-                       "model_tflops": round(tokens_per_second * FLOPS_PER_TOKEN / 1e12, 1),
-                       "mfu_of_sustained_peak": round(
-                           tokens_per_second * FLOPS_PER_TOKEN / 1e12 / (peak * world), 4)},
+            "config": static_config(world),
+            "run": run_facts,
             "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": 4 * rows,
                     "d2h_bytes_per_step": 4 * rows + 4},
             "gpu_launches": launches,
@@ -335,7 +401,8 @@ def run_flint(args):
             "cpu_baseline": cpu,
         }
         print(json.dumps(line), flush=True)
-    trainer.close()
+    if trainer is not None:
+        trainer.close()
     if world > 1:
         dist.destroy_process_group()
 
@@ -347,6 +414,8 @@ def main():
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="flint", choices=["flint", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-per-kernel", action="store_true",
+                        help="skip the per-kernel sweep beside cuBLAS (roofline.per_kernel)")
     parser.add_argument("--gemm-replay", action="store_true",
                         help="only replay one step's GEMM calls once after a warm-up replay and "
                              "print the roofline object (the command profiled for its DRAM traffic)")

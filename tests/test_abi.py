@@ -153,4 +153,5 @@ def test_the_kernel_bench_module_lists_its_groups():
     bench harness; importing it needs no GPU."""
     from flint_b200 import kernel_bench
 
-    assert set(kernel_bench.GROUPS) == {"gemm", "attention", "rowwise", "reductions"}
+    assert set(kernel_bench.GROUPS) == {"gemm", "epilogue", "batched", "attention", "rowwise"}
+    assert kernel_bench.measured_peaks()[0] > 1000 and kernel_bench.NOMINAL_TFLOPS == 2250.0

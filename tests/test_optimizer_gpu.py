@@ -37,10 +37,13 @@ def oracle_steps(p, grads, weight_decay, grad_scale=1.0, first_step=1):
     return out
 
 
-def assert_close(got, want, rtol, what):
+def assert_close(got, want, rtol, what, operands=None):
+    """|got - want| <= rtol * max(|want|, |operands|): where a result is the small difference
+    of larger operands (a weight crossing zero, a moment changing sign) FP32's error is
+    relative to those operands, not to the result."""
     got, want = got.double().cpu(), want.double()
-    bound = rtol * want.abs() + 1e-30
-    worst = ((got - want).abs() - bound).max().item()
+    size = want.abs() if operands is None else torch.maximum(want.abs(), operands.double().abs())
+    worst = ((got - want).abs() - rtol * size - 1e-30).max().item()
     assert worst <= 0, (what, worst)
 
 
@@ -64,8 +67,10 @@ def test_adamw_follows_the_oracle_element_by_element(flint, count, weight_decay)
                     HYPER["eps"], weight_decay, grad_scale, step)
         torch.cuda.synchronize()
         wp, wm, wv = want[step - 1]
-        assert_close(p, wp, 1e-6, f"p at step {step}")
-        assert_close(m, wm, 1e-6, f"m at step {step}")
+        scaled = grad.double() * grad_scale
+        assert_close(p, wp, 1e-6, f"p at step {step}", torch.full_like(wp, HYPER["lr"]).maximum(previous.abs()))
+        earlier = want[step - 2][1].abs() if step > 1 else torch.zeros_like(wm)
+        assert_close(m, wm, 1e-6, f"m at step {step}", torch.maximum(scaled.abs(), earlier))
         assert_close(v, wv, 1e-6, f"v at step {step}")
         moved, expected = p.double().cpu() - previous, wp - previous
         assert ((moved - expected).abs() <= 1e-4 * expected.abs() + 1e-8).all(), step
@@ -119,8 +124,8 @@ def test_adamw_run_updates_every_tensor_of_a_plan_with_its_own_decay(flint):
     torch.cuda.synchronize()
     for i, (n, wd, has_half) in enumerate(sizes):
         wp, wm, wv = oracle_steps(starts[i], [grads[s][i] for s in range(3)], wd, 0.5)[-1]
-        assert_close(ps[i], wp, 1e-6, f"tensor {i} p")
-        assert_close(ms[i], wm, 1e-6, f"tensor {i} m")
+        assert_close(ps[i], wp, 1e-6, f"tensor {i} p", starts[i].abs().clamp_min(3 * HYPER["lr"]))
+        assert_close(ms[i], wm, 1e-6, f"tensor {i} m", torch.stack([grads[s][i] for s in range(3)]).abs().amax(0))
         assert_close(vs[i], wv, 1e-6, f"tensor {i} v")
         if has_half:
             assert torch.equal(hs[i].view(torch.int16), ps[i].half().view(torch.int16))
@@ -266,6 +271,8 @@ def test_trainer_clip_coefficient_uses_the_norm_of_the_unscaled_gradients(flint)
                                   weight_decay=wd)
                 got = trainer.model.read(address, (rows * cols,), torch.float32).cpu().double()
                 moved, expected = got - previous[name], want[name] - before
-                assert ((moved - expected).abs() <= 2e-4 * expected.abs() + 1e-8).all(), (step, name)
+                # FP32 rounds the new weight to 2^-24 of itself (LayerNorm gains are near 1).
+                rounding = 2.0 ** -23 * previous[name].abs().clamp_min(0.05)
+                assert ((moved - expected).abs() <= 2e-4 * expected.abs() + rounding).all(), (step, name)
     finally:
         trainer.close()
