@@ -302,6 +302,49 @@ def gemm_cases(f: Flint, rows: int, once: bool, sigma_x: float):
     return cases
 
 
+def gelu_case(f: Flint, rows: int, once: bool, gen):
+    """MLP up + bias + tanh-GELU (flint also writes the pre-activation)."""
+    m, n, k = rows, 4 * WIDTH, WIDTH
+    sets = rotation_sets((m * k + n * k + 2 * m * n) * 2, once)
+    x = [half(m, k, gen=gen) for _ in range(sets)]
+    wt = [half(n, k, scale=0.02, gen=gen) for _ in range(sets)]
+    y = [torch.empty(m, n, dtype=torch.half, device=DEV) for _ in range(sets)]
+    pre = [torch.empty(m, n, dtype=torch.half, device=DEV) for _ in range(sets)]
+    bias = torch.randn(n, device=DEV, generator=gen) * 0.02
+    bias16 = bias.half()
+    return Case(
+        "epilogue", f"nt+bias+gelu {m}x{n}x{k}", "TFLOP/s", flop(m, n, k), sets,
+        lambda i: f.gemm_nt_bias_gelu(y[i], pre[i], x[i], wt[i], bias, m, n, k),
+        lambda i: torch._addmm_activation(bias16, x[i], wt[i].t(), use_gelu=True),
+        "cuBLASLt GELU_BIAS epilogue (torch._addmm_activation; no pre-activation output)",
+        lambda: (f.gemm_nt_bias_gelu(y[0], pre[0], x[0], wt[0], bias, m, n, k),
+                 rel_l2(y[0], torch._addmm_activation(bias16, x[0], wt[0].t(), use_gelu=True)))[1],
+        note="flint writes two outputs (GELU and the saved pre-activation), the baseline one",
+        layout="NT", epilogue="bias+gelu", m=m, n=n, k=k)
+
+
+def dgelu_case(f: Flint, rows: int, once: bool, gen):
+    """MLP-down input gradient + GELU backward from the saved pre-activation."""
+    m, n, k = rows, 4 * WIDTH, WIDTH
+    sets = rotation_sets((m * k + n * k + 2 * m * n) * 2, once)
+    dy = [half(m, k, gen=gen) for _ in range(sets)]
+    wn = [half(k, n, scale=0.02, gen=gen) for _ in range(sets)]
+    saved = [half(m, n, scale=2.0, gen=gen) for _ in range(sets)]
+    dh = [torch.empty(m, n, dtype=torch.half, device=DEV) for _ in range(sets)]
+    tmp = torch.empty(m, n, dtype=torch.half, device=DEV)
+
+    def baseline(i):
+        torch.mm(dy[i], wn[i], out=tmp)
+        return torch.ops.aten.gelu_backward(tmp, saved[i], approximate="tanh")
+
+    return Case(
+        "epilogue", f"nn+dgelu {m}x{n}x{k}", "TFLOP/s", flop(m, n, k), sets,
+        lambda i: f.gemm_nn_dgelu(dh[i], dy[i], wn[i], saved[i], m, n, k), baseline,
+        "cuBLAS GEMM + ATen gelu_backward (torch exposes no DGELU epilogue): two kernels",
+        lambda: (f.gemm_nn_dgelu(dh[0], dy[0], wn[0], saved[0], m, n, k), rel_l2(dh[0], baseline(0)))[1],
+        layout="NN", epilogue="dgelu", m=m, n=n, k=k)
+
+
 def epilogue_cases(f: Flint, rows: int, once: bool):
     w, w4 = WIDTH, 4 * WIDTH
     gen = torch.Generator(device=DEV).manual_seed(0x5EED0002)
@@ -327,44 +370,8 @@ def epilogue_cases(f: Flint, rows: int, once: bool):
                 torch.addmm(bias16, x[0], wt[0].t(), out=yb), rel_l2(y[0], yb))[2],
             layout="NT", epilogue="bias", m=m, n=n, k=k))
 
-    # MLP up + bias + tanh-GELU (flint also writes the pre-activation)
-    m, n, k = rows, w4, w
-    sets = rotation_sets((m * k + n * k + 2 * m * n) * 2, once)
-    x = [half(m, k, gen=gen) for _ in range(sets)]
-    wt = [half(n, k, scale=0.02, gen=gen) for _ in range(sets)]
-    y = [torch.empty(m, n, dtype=torch.half, device=DEV) for _ in range(sets)]
-    pre = [torch.empty(m, n, dtype=torch.half, device=DEV) for _ in range(sets)]
-    bias = torch.randn(n, device=DEV, generator=gen) * 0.02
-    bias16 = bias.half()
-    cases.append(Case(
-        "epilogue", f"nt+bias+gelu {m}x{n}x{k}", "TFLOP/s", flop(m, n, k), sets,
-        lambda i: f.gemm_nt_bias_gelu(y[i], pre[i], x[i], wt[i], bias, m, n, k),
-        lambda i: torch._addmm_activation(bias16, x[i], wt[i].t(), use_gelu=True),
-        "cuBLASLt GELU_BIAS epilogue (torch._addmm_activation; no pre-activation output)",
-        lambda: (f.gemm_nt_bias_gelu(y[0], pre[0], x[0], wt[0], bias, m, n, k),
-                 rel_l2(y[0], torch._addmm_activation(bias16, x[0], wt[0].t(), use_gelu=True)))[1],
-        note="flint writes two outputs (GELU and the saved pre-activation), the baseline one",
-        layout="NT", epilogue="bias+gelu", m=m, n=n, k=k))
-
-    # MLP-down input gradient + GELU backward from the saved pre-activation
-    m, n, k = rows, w4, w
-    dy = [half(m, k, gen=gen) for _ in range(sets)]
-    wn = [half(k, n, scale=0.02, gen=gen) for _ in range(sets)]
-    saved = [half(m, n, scale=2.0, gen=gen) for _ in range(sets)]
-    dh = [torch.empty(m, n, dtype=torch.half, device=DEV) for _ in range(sets)]
-    tmp = torch.empty(m, n, dtype=torch.half, device=DEV)
-
-    def dgelu_baseline(i):
-        torch.mm(dy[i], wn[i], out=tmp)
-        return torch.ops.aten.gelu_backward(tmp, saved[i], approximate="tanh")
-
-    cases.append(Case(
-        "epilogue", f"nn+dgelu {m}x{n}x{k}", "TFLOP/s", flop(m, n, k), sets,
-        lambda i: f.gemm_nn_dgelu(dh[i], dy[i], wn[i], saved[i], m, n, k), dgelu_baseline,
-        "cuBLAS GEMM + ATen gelu_backward (torch exposes no DGELU epilogue): two kernels",
-        lambda: (f.gemm_nn_dgelu(dh[0], dy[0], wn[0], saved[0], m, n, k),
-                 rel_l2(dh[0], dgelu_baseline(0)))[1],
-        layout="NN", epilogue="dgelu", m=m, n=n, k=k))
+    cases.append(gelu_case(f, rows, once, gen))
+    cases.append(dgelu_case(f, rows, once, gen))
 
     # bias + FP32 residual, FP32 out: attention projection and MLP down
     for label, (m, n, k) in {"projection": (rows, w, w), "mlp down": (rows, w, w4)}.items():
@@ -529,7 +536,6 @@ def rowwise_cases(f: Flint, rows: int, once: bool):
                       lambda i: f.causal_softmax_backward(ds[i], p[0], dp[i], batches, t, 0.125),
                       lambda i: torch.ops.aten._softmax_backward_data(dp[i], p[0], -1, torch.half),
                       "ATen _softmax_backward_data over full rows", batches=batches, length=t))
-    del s, dp
 
     # Fused softmax + cross-entropy.
     sets = rotation_sets(rows * PADDED_VOCAB * 4.0, once)
