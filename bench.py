@@ -293,11 +293,16 @@ def run_flint(args):
     group = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # The process group only carries rank 0's NCCL id, barriers and the max over ranks
+        # (host-side, gloo); the gradient collectives are the training library's own NCCL calls.
+        dist.init_process_group("gloo")
         group = dist.group.WORLD
 
     flint = flint_b200.Flint()
+    # More than one rank: the optimizer state is sharded (reduce-scatter, AdamW on 1/world,
+    # all-gather under the next forward pass) unless FLINT_B200_SHARD=0 asks for replicas.
     config = TrainerConfig(sequences=SEQUENCES, length=LENGTH,
+                           shard_optimizer=os.environ.get("FLINT_B200_SHARD", "1") != "0",
                            overlap_update=os.environ.get("FLINT_B200_OVERLAP_UPDATE", "1") != "0")
     trainer = Trainer(flint, config, group=group, seed=1234)
     rows = SEQUENCES * LENGTH
@@ -323,7 +328,7 @@ def run_flint(args):
     def max_over_ranks(ms: float) -> float:
         if world == 1:
             return ms
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        t = torch.tensor([ms], dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return t.item()
 

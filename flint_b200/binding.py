@@ -20,7 +20,9 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent.parent
 HEADER = ROOT / "include" / "flint" / "flint.h"
 EXTENSION_HEADER = ROOT / "include" / "flint" / "flint_b200.h"
+TRAIN_HEADER = ROOT / "include" / "flint" / "flint_train.h"
 LIBRARY_NAME = "libflint.so"
+TRAIN_LIBRARY_NAME = "libflint_train.so"
 
 OK = 0
 ERROR_INVALID_ARGUMENT = 1
@@ -69,8 +71,51 @@ class AdamwTensor(ctypes.Structure):
     ]
 
 
+class TrainerConfigC(ctypes.Structure):
+    """flint_trainer_config."""
+
+    _fields_ = [
+        ("model", Gpt2Config),
+        ("flash_attention", ctypes.c_int),
+        ("lr", ctypes.c_float),
+        ("beta1", ctypes.c_float),
+        ("beta2", ctypes.c_float),
+        ("eps", ctypes.c_float),
+        ("weight_decay", ctypes.c_float),
+        ("loss_scale", ctypes.c_float),
+        ("growth_interval", ctypes.c_int),
+        ("max_grad_norm", ctypes.c_float),
+        ("world", ctypes.c_int),
+        ("rank", ctypes.c_int),
+        ("shard_optimizer", ctypes.c_int),
+        ("overlap_update", ctypes.c_int),
+    ]
+
+
+class TrainerStatus(ctypes.Structure):
+    """flint_trainer_status."""
+
+    _fields_ = [
+        ("loss_scale", ctypes.c_float),
+        ("good_steps", ctypes.c_int),
+        ("step_count", ctypes.c_longlong),
+        ("skipped", ctypes.c_longlong),
+        ("grad_norm", ctypes.c_double),
+    ]
+
+
+class TrainerRange(ctypes.Structure):
+    """flint_trainer_range."""
+
+    _fields_ = [("first", ctypes.c_size_t), ("count", ctypes.c_size_t), ("storage", ctypes.c_size_t),
+                ("shared", ctypes.c_int)]
+
+
+BUCKET_HOOK = ctypes.CFUNCTYPE(None, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t,
+                               ctypes.c_void_p)
 BUCKET_CALLBACK = ctypes.CFUNCTYPE(None, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p,
                                    ctypes.c_size_t)
+STAGE_CALLBACK = ctypes.CFUNCTYPE(None, ctypes.c_void_p, ctypes.c_int)
 
 _C_TYPES = {
     "void": None,
@@ -95,7 +140,20 @@ _C_TYPES = {
     "const flint_gpt2_config*": ctypes.POINTER(Gpt2Config),
     "flint_gpt2_parameter_info*": ctypes.POINTER(Gpt2ParameterInfo),
     "flint_b200_bucket_callback": BUCKET_CALLBACK,
+    "flint_b200_stage_callback": STAGE_CALLBACK,
     "const flint_b200_adamw_tensor*": ctypes.POINTER(AdamwTensor),
+    "float*": ctypes.POINTER(ctypes.c_float),
+    "int**": ctypes.POINTER(ctypes.c_void_p),
+    "double**": ctypes.POINTER(ctypes.c_void_p),
+    "const void* const*": ctypes.POINTER(ctypes.c_void_p),
+    "flint_trainer*": ctypes.c_void_p,
+    "const flint_trainer*": ctypes.c_void_p,
+    "flint_trainer**": ctypes.POINTER(ctypes.c_void_p),
+    "const flint_trainer_config*": ctypes.POINTER(TrainerConfigC),
+    "flint_trainer_status*": ctypes.POINTER(TrainerStatus),
+    "const flint_trainer_status*": ctypes.POINTER(TrainerStatus),
+    "flint_trainer_range*": ctypes.POINTER(TrainerRange),
+    "flint_trainer_bucket_hook": BUCKET_HOOK,
 }
 
 _DECLARATION = re.compile(r"FLINT_API\s+([^;(]*?)\b(flint_\w+)\s*\(([^;]*?)\)\s*;", re.S)
@@ -130,6 +188,7 @@ def declared_functions() -> dict:
 
 SIGNATURES = parse_header(HEADER)
 EXTENSION_SIGNATURES = parse_header(EXTENSION_HEADER)
+TRAIN_SIGNATURES = parse_header(TRAIN_HEADER)
 
 
 class FlintError(RuntimeError):
@@ -171,6 +230,13 @@ def _nbytes(tensor) -> int:
     return tensor.numel() * tensor.element_size()
 
 
+def _bind(lib, functions: dict) -> None:
+    for name, (ret, params) in functions.items():
+        function = getattr(lib, name)  # AttributeError if a declared symbol is missing
+        function.restype = _C_TYPES[ret]
+        function.argtypes = [_C_TYPES[c_type] for c_type, _ in params]
+
+
 class Flint:
     """The loaded library. Methods mirror the C functions without the flint_ prefix."""
 
@@ -181,12 +247,29 @@ class Flint:
                 f"{self.path} not found: build it with `python -c 'import __graft_entry__ as g; "
                 "g.build()'` (or `make -C flint_b200/csrc`); there is no fallback implementation"
             )
-        self.lib = ctypes.CDLL(str(self.path))
+        self.lib = ctypes.CDLL(str(self.path), mode=ctypes.RTLD_GLOBAL)
         self.functions = declared_functions()
-        for name, (ret, params) in self.functions.items():
-            function = getattr(self.lib, name)  # AttributeError if a declared symbol is missing
-            function.restype = _C_TYPES[ret]
-            function.argtypes = [_C_TYPES[c_type] for c_type, _ in params]
+        _bind(self.lib, self.functions)
+        self._train = None
+
+    @property
+    def train(self):
+        """libflint_train.so (the training step behind a C ABI), loaded on first use from
+        beside libflint.so. It is a client of libflint.so and opens NCCL itself at run time."""
+        if self._train is None:
+            path = self.path.with_name(TRAIN_LIBRARY_NAME)
+            if not path.is_file():
+                raise FileNotFoundError(f"{path} not found: build it with `make -C flint_b200/csrc`")
+            lib = ctypes.CDLL(str(path))
+            _bind(lib, TRAIN_SIGNATURES)
+            self._train = lib
+        return self._train
+
+    def check_train(self, status: int) -> None:
+        if status != OK:
+            detail = self.train.flint_train_last_error().decode()
+            message = f"{self.status_string(status)} (status {status})"
+            raise FlintError(status, f"{message}: {detail}" if detail else message)
 
     # -- plumbing ---------------------------------------------------------------------
 
@@ -410,9 +493,13 @@ class Gpt2:
     """A flint_gpt2 model; freed by close() or on leaving a with block. Addresses of its
     weights, gradients and outputs are device addresses as ints."""
 
-    def __init__(self, flint: Flint, config: Gpt2Config, flash_attention=None):
+    def __init__(self, flint: Flint, config: Gpt2Config, flash_attention=None, borrowed=None):
         self.flint = flint
         self.config = config
+        self.owned = borrowed is None
+        if borrowed is not None:  # a model that something else (a trainer) owns and frees
+            self.handle = borrowed
+            return
         handle = ctypes.c_void_p()
         if flash_attention is None:
             status = flint.lib.flint_gpt2_create(ctypes.byref(config), ctypes.byref(handle))
@@ -424,9 +511,9 @@ class Gpt2:
         self.handle = handle.value
 
     def close(self) -> None:
-        if self.handle is not None:
+        if self.handle is not None and self.owned:
             self.flint.lib.flint_gpt2_destroy(self.handle)
-            self.handle = None
+        self.handle = None
 
     def __enter__(self):
         return self

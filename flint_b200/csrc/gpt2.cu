@@ -584,6 +584,49 @@ flint_status backward_impl(const char* name, flint_gpt2* model, const void* toke
     return FLINT_OK;
 }
 
+using StageCallback = void (*)(void* user, int stage);
+
+flint_status forward_impl(const char* name, flint_gpt2* model, const void* tokens,
+                          const void* targets, float scale, flint_stream stream,
+                          StageCallback callback, void* user) {
+    if (model == nullptr) {
+        return fb::fail(kInvalid, "%s: model is null", name);
+    }
+    if (!std::isfinite(scale)) {
+        return fb::fail(kInvalid, "%s: scale (%g) must be finite", name,
+                        static_cast<double>(scale));
+    }
+    const flint_gpt2& m = *model;
+    const flint_gpt2_config& c = m.config;
+    const size_t rows = m.rows;
+    const fb::Span spans[] = {
+        {"logits", m.logits, rows * c.padded_vocab * 2},
+        {"dlogits", m.dlogits, rows * c.padded_vocab * 2},
+        {"row_loss", m.row_loss, rows * 4},
+        {"tokens", tokens, rows * 2},
+        {"targets", targets, rows * 2},
+    };
+    FB_TRY(fb::check_spans(name, spans, 3));
+    auto enter = [&](int stage) {
+        if (callback != nullptr) {
+            callback(user, stage);
+        }
+    };
+
+    enter(0);
+    FB_TRY(flint_embedding_forward(m.blocks[0].x_in, tokens, m.wte->data, m.wpe->data, c.sequences,
+                                   c.length, c.padded_vocab, c.width, stream));
+    for (size_t i = 0; i < m.blocks.size(); ++i) {
+        enter(static_cast<int>(i) + 1);
+        FB_TRY(forward_block(m, i, stream));
+    }
+    enter(static_cast<int>(m.blocks.size()) + 1);
+    FB_TRY(layernorm(m, m.lnf_w, m.lnf_b, m.x_final, m.h_f, m.mean_f, m.rstd_f, stream));
+    FB_TRY(flint_gemm_nt(m.logits, m.h_f, m.wte->half, rows, c.padded_vocab, c.width, stream));
+    return flint_softmax_cross_entropy(m.dlogits, m.row_loss, m.logits, targets, scale, rows,
+                                       c.vocab, c.padded_vocab, stream);
+}
+
 }  // namespace
 
 flint_gpt2::~flint_gpt2() {
@@ -651,35 +694,15 @@ flint_status flint_gpt2_sync_weights(flint_gpt2* model, flint_stream stream) {
 
 flint_status flint_gpt2_forward(flint_gpt2* model, const void* tokens, const void* targets,
                                 float scale, flint_stream stream) {
-    constexpr const char* name = "flint_gpt2_forward";
-    if (model == nullptr) {
-        return fb::fail(kInvalid, "%s: model is null", name);
-    }
-    if (!std::isfinite(scale)) {
-        return fb::fail(kInvalid, "%s: scale (%g) must be finite", name,
-                        static_cast<double>(scale));
-    }
-    const flint_gpt2& m = *model;
-    const flint_gpt2_config& c = m.config;
-    const size_t rows = m.rows;
-    const fb::Span spans[] = {
-        {"logits", m.logits, rows * c.padded_vocab * 2},
-        {"dlogits", m.dlogits, rows * c.padded_vocab * 2},
-        {"row_loss", m.row_loss, rows * 4},
-        {"tokens", tokens, rows * 2},
-        {"targets", targets, rows * 2},
-    };
-    FB_TRY(fb::check_spans(name, spans, 3));
+    return forward_impl("flint_gpt2_forward", model, tokens, targets, scale, stream, nullptr,
+                        nullptr);
+}
 
-    FB_TRY(flint_embedding_forward(m.blocks[0].x_in, tokens, m.wte->data, m.wpe->data, c.sequences,
-                                   c.length, c.padded_vocab, c.width, stream));
-    for (size_t i = 0; i < m.blocks.size(); ++i) {
-        FB_TRY(forward_block(m, i, stream));
-    }
-    FB_TRY(layernorm(m, m.lnf_w, m.lnf_b, m.x_final, m.h_f, m.mean_f, m.rstd_f, stream));
-    FB_TRY(flint_gemm_nt(m.logits, m.h_f, m.wte->half, rows, c.padded_vocab, c.width, stream));
-    return flint_softmax_cross_entropy(m.dlogits, m.row_loss, m.logits, targets, scale, rows,
-                                       c.vocab, c.padded_vocab, stream);
+flint_status flint_b200_gpt2_forward_stages(flint_gpt2* model, const void* tokens,
+                                            const void* targets, float scale, flint_stream stream,
+                                            flint_b200_stage_callback callback, void* user) {
+    return forward_impl("flint_b200_gpt2_forward_stages", model, tokens, targets, scale, stream,
+                        callback, user);
 }
 
 flint_status flint_gpt2_backward(flint_gpt2* model, const void* tokens, int accumulate,

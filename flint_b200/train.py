@@ -61,7 +61,7 @@ def main(argv=None) -> list:
         import torch.distributed as dist
 
         if not dist.is_initialized():
-            dist.init_process_group("nccl")
+            dist.init_process_group("gloo")  # carries the NCCL id only; see flint_train.h
         group = dist.group.WORLD
 
     config = TrainerConfig(layers=args.layers, heads=args.heads, width=args.width,

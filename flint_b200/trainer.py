@@ -1,4 +1,4 @@
-"""Data-parallel GPT-2 training step over the C ABI (one process per GPU).
+"""Data-parallel GPT-2 training from Python: a thin caller of libflint_train.so.
 
 The reference has no trainer in C++ (its README lists the optimizer, loss
 scaling and multi-GPU as planned); what a step must do is fixed by its PyTorch
@@ -7,16 +7,14 @@ FP32 accumulation and a dynamic loss scale, AdamW (lr 6e-4, betas 0.9/0.95,
 eps 1e-8, weight decay 0.1 on parameters with two or more dimensions), and a
 step that is skipped, with the scale halved, when a gradient is not finite.
 
-Here every kernel is the library's: ``flint_gpt2_forward`` /
-``flint_b200_gpt2_backward_buckets`` on a model built on the fused attention
-kernels, ``flint_b200_check_gradients`` and one multi-tensor
-``flint_b200_adamw_run`` that also refreshes the FP16 weight copies. With more
-than one rank the FP32 gradients are summed by NCCL all-reduce over
-NVLink/NVSwitch, one contiguous bucket per transformer block, started from the
-backward pass's bucket callback on a second stream so the transfers overlap the
-remaining backward kernels. Each rank scales its loss by
-``loss_scale / (rows_per_rank * world)``, so the plain sum is the gradient of
-the global mean loss and every rank takes the same skip decision.
+The step itself lives in C++ behind ``include/flint/flint_train.h``
+(``flint_b200/csrc/train.cpp``): streams, events, the per-bucket NCCL collectives
+(all-reduce, or reduce-scatter + all-gather around a sharded AdamW), the loss-scale
+policy and the optimizer launches. This module holds what is left for the host
+language: the configuration, the initial weights, checkpoints, and zero-copy torch
+views of the trainer's device arrays for tests and tools. torch supplies device
+buffers, the current stream and (with any backend) the process group that carries
+rank 0's NCCL id to the other ranks; it runs no kernel of the step.
 """
 
 import math
@@ -48,7 +46,8 @@ class TrainerConfig:
     growth_interval: int = 2000
     max_grad_norm: float = 0.0   # 0 disables clipping
     flash_attention: bool = True
-    overlap_update: bool = True  # ranks > 1: update most of the model under the last all-reduce
+    overlap_update: bool = True  # replicated ranks > 1: update most of the model under the last all-reduce
+    shard_optimizer: bool = False  # ranks > 1: reduce-scatter, per-rank AdamW on 1/world, all-gather
 
 
 class _DeviceView:
@@ -130,27 +129,82 @@ def bucket_order(layers: int) -> list:
     return ["ln_f"] + [f"blocks.{i}" for i in reversed(range(layers))] + ["embeddings"]
 
 
+class _Scaler:
+    """The trainer's dynamic loss scale as the C library holds it (GradScaler's policy)."""
+
+    def __init__(self, trainer):
+        self._trainer = trainer
+
+    @property
+    def scale(self) -> float:
+        return self._trainer.status().loss_scale
+
+    @scale.setter
+    def scale(self, value: float) -> None:
+        self._trainer.set_status(loss_scale=float(value))
+
+    @property
+    def good_steps(self) -> int:
+        return self._trainer.status().good_steps
+
+    @good_steps.setter
+    def good_steps(self, value: int) -> None:
+        self._trainer.set_status(good_steps=int(value))
+
+
 class Trainer:
-    """One rank of a data-parallel GPT-2 training job. `group` is a torch.distributed
-    process group (NCCL) or None for a single GPU."""
+    """One rank of a data-parallel GPT-2 training job: a thin caller of libflint_train.so
+    (``include/flint/flint_train.h``), which owns the model, the optimizer state, the
+    collective stream and, for more than one rank, the NCCL communicator. `group` is a
+    torch.distributed process group of any backend, or None for a single GPU; it is used
+    for one thing only, handing rank 0's NCCL id to the other ranks."""
 
     def __init__(self, flint: Flint, config: TrainerConfig, state: dict = None, group=None,
                  seed: int = 1234):
+        import ctypes
+
+        from .binding import BUCKET_HOOK, TrainerConfigC
+
         self.flint = flint
         self.config = config
         self.group = group
-        self.world = 1
+        self.world, self.rank = 1, 0
         if group is not None:
             import torch.distributed as dist
 
-            self.world = dist.get_world_size(group)
-        model_config = Gpt2Config(config.layers, config.heads, config.width, config.block_size,
-                                  config.vocab, config.padded_vocab, config.sequences,
-                                  config.length, 0, 1)
-        self.model = Gpt2(flint, model_config, flash_attention=config.flash_attention)
-        self.rows = config.sequences * config.length
+            self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.lib = flint.train
         self.stream = torch.cuda.current_stream()
-        self.comm_stream = torch.cuda.Stream() if self.world > 1 else None
+        self.rows = config.sequences * config.length
+
+        nccl_id = None
+        if self.world > 1:
+            import torch.distributed as dist
+
+            holder = [None]
+            if self.rank == 0:
+                buffer = ctypes.create_string_buffer(128)
+                flint.check_train(self.lib.flint_train_nccl_id(buffer))
+                holder[0] = buffer.raw
+            dist.broadcast_object_list(holder, src=dist.get_global_rank(group, 0), group=group)
+            nccl_id = ctypes.create_string_buffer(holder[0], 128)
+        c = TrainerConfigC()
+        c.model = Gpt2Config(config.layers, config.heads, config.width, config.block_size,
+                             config.vocab, config.padded_vocab, config.sequences, config.length, 0, 1)
+        c.flash_attention = int(config.flash_attention)
+        c.lr, c.beta1, c.beta2, c.eps = config.lr, config.beta1, config.beta2, config.eps
+        c.weight_decay = config.weight_decay
+        c.loss_scale, c.growth_interval = config.loss_scale, config.growth_interval
+        c.max_grad_norm = config.max_grad_norm
+        c.world, c.rank = self.world, self.rank
+        c.shard_optimizer = int(config.shard_optimizer)
+        c.overlap_update = int(config.overlap_update)
+        handle = ctypes.c_void_p()
+        flint.check_train(self.lib.flint_trainer_create(ctypes.byref(c), nccl_id, ctypes.byref(handle)))
+        self.handle = handle.value
+        model = ctypes.c_void_p()
+        flint.check_train(self.lib.flint_trainer_model(self.handle, ctypes.byref(model)))
+        self.model = Gpt2(flint, c.model, borrowed=model.value)
 
         state = state if state is not None else initial_weights(config, seed)
         self.model.load({k: v.cuda() for k, v in state.items()})
@@ -161,198 +215,173 @@ class Trainer:
         self.gradient_address = arena
         self.gradient_count = arena_bytes // 4
         self.gradients = device_tensor(arena, self.gradient_count)
-        # Moments share the gradient arena's layout: one allocation each.
-        self.m = torch.zeros(self.gradient_count, device="cuda")
-        self.v = torch.zeros(self.gradient_count, device="cuda")
-        half = self._half_copies()
-        tensors = []
-        # (name, master address, rows, cols, first float in the gradient/moment arenas)
+        # (name, master address, rows, cols, first float in the gradient arena)
         self.layout = [(name, address, rows, cols, (grad - arena) // 4)
                        for (name, address, rows, cols), (_, grad, _, _) in zip(self.parameters, gradients)]
-        for (name, address, rows, cols), (_, grad, _, _) in zip(self.parameters, gradients):
-            offset = grad - arena
-            decay = config.weight_decay if rows > 1 else 0.0
-            tensors.append((address, self.m.data_ptr() + offset, self.v.data_ptr() + offset, grad,
-                            half.get(name), rows * cols, decay))
-        self.plan, self.plan_items = flint.adamw_plan(tensors)
-        # With more than one rank the update is pipelined with the last all-reduce (see
-        # step()): one plan for the embeddings (the last bucket, the first two tensors of
-        # the arena) and one for everything else.
-        self.body_offset = (gradients[2][1] - arena) // 4  # first float after wte and wpe
-        self.split_plans = None
-        if self.world > 1:
-            self.split_plans = (flint.adamw_plan(tensors[:2]), flint.adamw_plan(tensors[2:]))
-        self.found = torch.zeros(1, dtype=torch.int32, device="cuda")
-        self.norm_squared = torch.zeros(1, dtype=torch.float64, device="cuda")
-        self._row_loss = device_tensor(self.model.outputs()[2], self.rows)
-        self._loss_sum = torch.zeros((), dtype=torch.float64, device="cuda")
-        self._micro_batches = 1
-        self.scaler = LossScaler(config.loss_scale, config.growth_interval)
-        self.step_count = 0
-        self.skipped = 0
-        self._events = []
+        m, v, count = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_size_t()
+        flint.check_train(self.lib.flint_trainer_moments(self.handle, ctypes.byref(m), ctypes.byref(v),
+                                                         ctypes.byref(count)))
+        # AdamW's moments. A replicated trainer's arrays share the gradient arena's layout; a
+        # sharded one's hold this rank's ranges back to back (see ranges()).
+        self.m = device_tensor(m.value, count.value)
+        self.v = device_tensor(v.value, count.value)
+        found, norm = ctypes.c_void_p(), ctypes.c_void_p()
+        flint.check_train(self.lib.flint_trainer_flags(self.handle, ctypes.byref(found), ctypes.byref(norm)))
+        self.found = device_tensor(found.value, 1, "<i4")
+        self.norm_squared = device_tensor(norm.value, 1, "<f8")
+        self.scaler = _Scaler(self)
+        self._hook = None
+        self._hook_type = BUCKET_HOOK
         torch.cuda.synchronize()
 
-    def _half_copies(self) -> dict:
-        """{parameter name: address of its FP16 compute copy}. The copies follow the
-        gradients in the model's arena in a fixed order: wte, then each block's four
-        matrices; their addresses come from the model's layout."""
+    def close(self) -> None:
+        if self.handle is not None:
+            self.lib.flint_trainer_destroy(self.handle)
+            self.handle = None
+            self.model.handle = None
+
+    # -- state ----------------------------------------------------------------------------
+
+    def status(self):
+        from .binding import TrainerStatus
         import ctypes
 
-        out = {}
-        lib = self.flint.lib
-        if hasattr(lib, "flint_b200_gpt2_compute_copy"):
-            for index, (name, _, _, _) in enumerate(self.parameters):
-                address = ctypes.c_void_p()
-                self.flint.check(lib.flint_b200_gpt2_compute_copy(self.model.handle, index,
-                                                                  ctypes.byref(address)))
-                if address.value:
-                    out[name] = address.value
+        status = TrainerStatus()
+        self.flint.check_train(self.lib.flint_trainer_get_status(self.handle, ctypes.byref(status)))
+        return status
+
+    def set_status(self, **changes) -> None:
+        import ctypes
+
+        status = self.status()
+        for key, value in changes.items():
+            setattr(status, key, value)
+        self.flint.check_train(self.lib.flint_trainer_set_status(self.handle, ctypes.byref(status)))
+
+    @property
+    def step_count(self) -> int:
+        return self.status().step_count
+
+    @property
+    def skipped(self) -> int:
+        return self.status().skipped
+
+    def ranges(self) -> list:
+        """(first, count, storage, shared) of each range of the gradient arena this rank's
+        optimizer owns: the moments of arena floats [first, first + count) are
+        m[storage:storage + count]; shared ranges are held by every rank alike."""
+        from .binding import TrainerRange
+        import ctypes
+
+        out = []
+        for i in range(self.lib.flint_trainer_shard_count(self.handle)):
+            r = TrainerRange()
+            self.flint.check_train(self.lib.flint_trainer_shard(self.handle, i, ctypes.byref(r)))
+            out.append((r.first, r.count, r.storage, bool(r.shared)))
         return out
 
-    def close(self) -> None:
-        self.model.close()
+    def synchronize(self) -> None:
+        """Waits for the step and for the collective stream (a sharded trainer's weights may
+        still be arriving when finish_step returns)."""
+        self.flint.check_train(self.lib.flint_trainer_synchronize(self.handle, self.stream.cuda_stream))
+
+    def set_bucket_hook(self, hook) -> None:
+        """hook(bucket, address, nbytes), or None: called on the launching thread for each
+        gradient bucket of a step's last micro-batch before its collective is enqueued (ranks
+        > 1); it may enqueue work on the current stream."""
+        if hook is None:
+            self._hook = None
+            self.flint.check_train(self.lib.flint_trainer_set_bucket_hook(self.handle, self._hook_type(0), None))
+            return
+        self._hook = self._hook_type(lambda _user, bucket, address, nbytes, _stream: hook(bucket, address, nbytes))
+        self.flint.check_train(self.lib.flint_trainer_set_bucket_hook(self.handle, self._hook, None))
 
     # -- one optimizer step ---------------------------------------------------------------
 
-    def _pipelined(self) -> bool:
-        """Whether the update overlaps the last all-reduce: more than one rank, and no
-        gradient clipping (the clip coefficient needs the norm of all reduced gradients)."""
-        return self.world > 1 and self.config.overlap_update and self.config.max_grad_norm <= 0
-
-    def _on_bucket(self, bucket: int, address: int, nbytes: int) -> None:
-        import torch.distributed as dist
-
-        last = bucket == self.config.layers + 1  # ln_f, the blocks, then the embeddings
-        view = device_tensor(address, nbytes // 4)
-        if last and self._pipelined():
-            # This rank's embedding gradients are checked before they are summed: a
-            # non-finite value on any rank makes the sum non-finite, so the maximum of the
-            # ranks' flags (a four-byte all-reduce, ahead of the big one) is the flag the
-            # summed gradients would raise.
-            self.flint.check_gradients(view, nbytes // 4, 1.0 / self.scaler.scale, self.found,
-                                       None)
-        ready = torch.cuda.Event()
-        ready.record(self.stream)
-        self.comm_stream.wait_event(ready)
-        with torch.cuda.stream(self.comm_stream):
-            if last and self._pipelined():
-                dist.all_reduce(self.found, op=dist.ReduceOp.MAX, group=self.group)
-                self._flag_ready = torch.cuda.Event()
-                self._flag_ready.record(self.comm_stream)
-            dist.all_reduce(view, op=dist.ReduceOp.SUM, group=self.group)
-
     def step(self, tokens: torch.Tensor, targets: torch.Tensor) -> None:
-        """Enqueues forward, backward (with overlapped all-reduce), the gradient check and
+        """Enqueues forward, backward (with overlapped collectives), the gradient check and
         the AdamW update for one micro-batch of uint16 tokens/targets on this rank."""
         self.step_batches([(tokens, targets)])
 
     def step_batches(self, batches) -> None:
         """One optimizer step over several micro-batches, a list of (tokens, targets), as the
         reference's ``train_step`` takes them (``scripts/gpt2_torch.py:178-192``): each
-        micro-batch's loss is divided by their number and the gradients accumulate in place
-        (``flint_gpt2_backward`` with accumulate set from the second one on). With more
-        than one rank only the last micro-batch's backward starts the all-reduces, on the
-        accumulated gradients."""
-        c = self.config
+        micro-batch's loss is divided by their number and the gradients accumulate in place.
+        With more than one rank only the last micro-batch's backward starts the collectives,
+        on the accumulated gradients."""
+        import ctypes
+
         count = len(batches)
         if count == 0:
             raise ValueError("a step needs at least one micro-batch")
-        scale = cross_entropy_scale(self.scaler.scale, self.rows, self.world) / count
-        inverse = 1.0 / self.scaler.scale
-        pipelined = self._pipelined()
-        self._micro_batches = count
-        if count > 1:
-            self._loss_sum.zero_()
-        if pipelined:
-            self.found.zero_()
-        for index, (tokens, targets) in enumerate(batches):
-            self.model.forward(tokens, targets, scale)
-            if count > 1:
-                self._loss_sum += self._row_loss.sum(dtype=torch.float64)
-            reduce_now = self.world > 1 and index + 1 == count
-            self.model.backward(tokens, index > 0,
-                                callback=self._on_bucket if reduce_now else None)
-        if pipelined:
-            # Every bucket but the last is summed while backward runs; the last one (the
-            # embeddings, a third of the bytes) would otherwise be waited for with nothing
-            # to do. Its non-finite flag is settled early (see _on_bucket), so the rest of
-            # the model is checked and updated while that all-reduce is in flight.
-            done = torch.cuda.Event()
-            done.record(self.comm_stream)
-            self.stream.wait_event(self._flag_ready)
-            body = self.gradients[self.body_offset:]
-            self.flint.check_gradients(body, body.numel(), inverse, self.found, None)
-            self.step_count += 1
-            (embed_plan, embed_items), (body_plan, body_items) = self.split_plans
-            step = self.step_count - self.skipped
-            self.flint.adamw_run(body_plan, body_items, c.lr, c.beta1, c.beta2, c.eps, inverse, step,
-                                 self.found)
-            self.stream.wait_event(done)
-            self.flint.adamw_run(embed_plan, embed_items, c.lr, c.beta1, c.beta2, c.eps, inverse,
-                                 step, self.found)
-            return
-        if self.world > 1:
-            done = torch.cuda.Event()
-            done.record(self.comm_stream)
-            self.stream.wait_event(done)
-        self.apply_update()
+        tokens = (ctypes.c_void_p * count)(*[t.data_ptr() for t, _ in batches])
+        targets = (ctypes.c_void_p * count)(*[y.data_ptr() for _, y in batches])
+        self.flint.check_train(self.lib.flint_trainer_step(self.handle, tokens, targets, count,
+                                                           self.stream.cuda_stream))
 
     def apply_update(self) -> None:
         """The optimizer's half of a step on whatever the gradient arena holds (gradients
-        times the loss scale, already summed over the ranks): the non-finite check, the
-        optional clip of the unscaled gradients' global norm
-        (``scripts/gpt2_torch.py:186-188``: ``unscale_`` then ``clip_grad_norm_``) and one
-        AdamW launch that also writes the FP16 compute copies. A non-finite gradient leaves
-        weights and moments untouched (the kernels read the flag on the device)."""
-        c = self.config
-        inverse = 1.0 / self.scaler.scale
-        self.found.zero_()
-        clip = c.max_grad_norm > 0
-        if clip:
-            self.norm_squared.zero_()
-        self.flint.check_gradients(self.gradients, self.gradient_count, inverse, self.found,
-                                   self.norm_squared if clip else None)
-        grad_scale = inverse
-        if clip:
-            # The clip coefficient needs the norm on the host; clipping is off by default.
-            norm = math.sqrt(self.norm_squared.item())
-            if math.isfinite(norm) and norm > c.max_grad_norm:
-                grad_scale *= c.max_grad_norm / (norm + 1e-6)
-        self.step_count += 1
-        self.flint.adamw_run(self.plan, self.plan_items, c.lr, c.beta1, c.beta2, c.eps, grad_scale,
-                             self.step_count - self.skipped, self.found)
+        times the loss scale): the non-finite check, the optional clip of the unscaled
+        gradients' global norm (``scripts/gpt2_torch.py:186-188``) and one AdamW launch that
+        also writes the FP16 compute copies. Single rank only."""
+        self.flint.check_train(self.lib.flint_trainer_update(self.handle, self.stream.cuda_stream))
 
     def finish_step(self) -> float:
         """Waits for the step, updates the loss scale from the non-finite flag and returns
         this rank's mean loss over the step's micro-batches (a device-to-host read)."""
-        if self._micro_batches > 1:
-            loss = self._loss_sum.item() / (self.rows * self._micro_batches)
-        else:
-            loss = self.model.mean_loss()
-        found = bool(self.found.item())
-        if found:
-            self.skipped += 1
-        self.scaler.update(found)
-        return loss
+        import ctypes
+
+        loss, skipped = ctypes.c_double(), ctypes.c_int()
+        self.flint.check_train(self.lib.flint_trainer_finish(
+            self.handle, self.stream.cuda_stream, ctypes.cast(ctypes.byref(loss), ctypes.c_void_p),
+            ctypes.cast(ctypes.byref(skipped), ctypes.c_void_p)))
+        return loss.value
 
     # -- checkpoints ----------------------------------------------------------------------
 
     MODEL_KEYS = ("layers", "heads", "width", "block_size", "vocab", "padded_vocab")
 
+    def _arena_moments(self):
+        """(m, v) as CPU tensors in the gradient arena's layout. A sharded trainer's ranks
+        each hold a slice of every bucket: the slices are put in place and summed over the
+        ranks (disjoint, so the sum is the union; ranges every rank holds come from rank 0)."""
+        ranges = self.ranges()
+        if self.world == 1 or all(shared for _, _, _, shared in ranges):
+            full_m, full_v = torch.zeros(self.gradient_count), torch.zeros(self.gradient_count)
+            m, v = self.m.cpu(), self.v.cpu()
+            for first, count, storage, _ in ranges:
+                full_m[first:first + count] = m[storage:storage + count]
+                full_v[first:first + count] = v[storage:storage + count]
+            return full_m, full_v
+        import torch.distributed as dist
+
+        out = []
+        for moment in (self.m.cpu(), self.v.cpu()):
+            full = torch.zeros(self.gradient_count)
+            for first, count, storage, shared in ranges:
+                if not shared or self.rank == 0:
+                    full[first:first + count] = moment[storage:storage + count]
+            device = full.cuda() if dist.get_backend(self.group) == "nccl" else full
+            dist.all_reduce(device, group=self.group)
+            out.append(device.cpu())
+        return out
+
     def save(self, path, data_state: dict = None) -> str:
         """Writes the FP32 master weights (under PyTorch's parameter names), both AdamW
         moments, the loss scaler and the step counters to path, with data_state (for
-        instance TokenBatches.state()) alongside. Every rank holds the same state, so one
-        rank writing is enough. Returns the file's sha256."""
-        torch.cuda.synchronize()
+        instance TokenBatches.state()) alongside. The file does not depend on how the
+        optimizer state was spread over ranks: a sharded trainer gathers its moments first
+        (a collective: every rank must call save; rank 0's file is complete). Returns the
+        file's sha256."""
+        self.synchronize()
+        m_full, v_full = self._arena_moments()
         arrays = {}
         for name, address, rows, cols, first in self.layout:
             count = rows * cols
             shape = (cols,) if rows == 1 else (rows, cols)
             arrays["param/" + name] = device_tensor(address, count).cpu().numpy().reshape(shape)
-            arrays["m/" + name] = self.m[first:first + count].cpu().numpy().reshape(shape)
-            arrays["v/" + name] = self.v[first:first + count].cpu().numpy().reshape(shape)
+            arrays["m/" + name] = m_full[first:first + count].numpy().reshape(shape)
+            arrays["v/" + name] = v_full[first:first + count].numpy().reshape(shape)
         meta = {
             "kind": "flint-b200 trainer",
             "config": asdict(self.config),
@@ -365,9 +394,10 @@ class Trainer:
         return write_checkpoint(path, meta, arrays)
 
     def restore(self, path, verify: bool = True):
-        """Loads a checkpoint written by save() into this trainer (same model shape) and
-        returns the data_state stored with it. The FP16 compute copies are refreshed from
-        the restored masters."""
+        """Loads a checkpoint written by save() into this trainer (same model shape, any
+        number of ranks) and returns the data_state stored with it. Each rank takes the
+        moments of the ranges it owns; the FP16 compute copies are refreshed from the
+        restored masters."""
         meta, arrays = read_checkpoint(path, verify=verify)
         if meta.get("kind") != "flint-b200 trainer":
             raise CheckpointError("not a trainer checkpoint")
@@ -377,20 +407,23 @@ class Trainer:
                 raise CheckpointError(
                     f"checkpoint's {key} is {meta['config'].get(key)}, this trainer's {mine[key]}")
         state = {}
+        m_full = torch.zeros(self.gradient_count)
+        v_full = torch.zeros(self.gradient_count)
         for name, _, rows, cols, first in self.layout:
             count = rows * cols
             for prefix in ("param/", "m/", "v/"):
                 if prefix + name not in arrays or arrays[prefix + name].size != count:
                     raise CheckpointError(f"checkpoint lacks {prefix}{name} with {count} values")
             state[name] = torch.from_numpy(np.array(arrays["param/" + name], dtype=np.float32)).cuda()
-            self.m[first:first + count].copy_(
-                torch.from_numpy(np.array(arrays["m/" + name], dtype=np.float32).reshape(-1)))
-            self.v[first:first + count].copy_(
-                torch.from_numpy(np.array(arrays["v/" + name], dtype=np.float32).reshape(-1)))
+            m_full[first:first + count] = torch.from_numpy(
+                np.array(arrays["m/" + name], dtype=np.float32).reshape(-1))
+            v_full[first:first + count] = torch.from_numpy(
+                np.array(arrays["v/" + name], dtype=np.float32).reshape(-1))
+        for first, count, storage, _ in self.ranges():
+            self.m[storage:storage + count].copy_(m_full[first:first + count])
+            self.v[storage:storage + count].copy_(v_full[first:first + count])
         self.model.load(state)
-        self.step_count = int(meta["step_count"])
-        self.skipped = int(meta["skipped"])
-        self.scaler.scale = float(meta["loss_scale"])
-        self.scaler.good_steps = int(meta["good_steps"])
+        self.set_status(step_count=int(meta["step_count"]), skipped=int(meta["skipped"]),
+                        loss_scale=float(meta["loss_scale"]), good_steps=int(meta["good_steps"]))
         torch.cuda.synchronize()
         return meta.get("data")

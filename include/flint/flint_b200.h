@@ -63,6 +63,21 @@ FLINT_API flint_status flint_b200_gpt2_backward_buckets(flint_gpt2* model, const
                                                         flint_b200_bucket_callback callback,
                                                         void* user);
 
+/* Called on the launching host thread from inside flint_b200_gpt2_forward_stages
+ * before the kernels of each stage are enqueued: stage 0 is the embedding,
+ * stages 1..layers the transformer blocks in order, stage layers + 1 the final
+ * LayerNorm with the output layer and the loss. A trainer whose weights arrive
+ * bucket by bucket (a sharded optimizer's all-gather) makes the stream wait
+ * there for that stage's weights only. */
+typedef void (*flint_b200_stage_callback)(void* user, int stage);
+
+/* flint_gpt2_forward plus the callback above (which may be null). */
+FLINT_API flint_status flint_b200_gpt2_forward_stages(flint_gpt2* model, const void* tokens,
+                                                      const void* targets, float scale,
+                                                      flint_stream stream,
+                                                      flint_b200_stage_callback callback,
+                                                      void* user);
+
 /* The contiguous FP32 range that holds every gradient, in parameter order. */
 FLINT_API flint_status flint_b200_gpt2_gradient_arena(const flint_gpt2* model, void** base,
                                                       size_t* bytes);

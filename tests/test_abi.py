@@ -155,3 +155,66 @@ def test_the_kernel_bench_module_lists_its_groups():
 
     assert set(kernel_bench.GROUPS) == {"gemm", "epilogue", "batched", "attention", "rowwise"}
     assert kernel_bench.measured_peaks()[0] > 1000 and kernel_bench.NOMINAL_TFLOPS == 2250.0
+
+
+# ---- libflint_train.so (the training step behind a C ABI) -----------------------------------------
+
+
+def test_training_library_exports_its_header_and_links_no_nccl(flint):
+    lib = flint.train
+    assert len(binding.TRAIN_SIGNATURES) == 18
+    for name in binding.TRAIN_SIGNATURES:
+        assert hasattr(lib, name), name
+    path = flint.path.with_name(binding.TRAIN_LIBRARY_NAME)
+    readelf = shutil.which("readelf")
+    if readelf is not None:
+        out = subprocess.run([readelf, "-d", str(path)], capture_output=True, text=True).stdout
+        needed = re.findall(r"\(NEEDED\)\s+Shared library: \[(.+?)\]", out)
+        assert "libflint.so" in needed
+        # NCCL is opened with dlopen at run time, and only for more than one rank.
+        assert not [n for n in needed if re.search(r"nccl|cublas|cudnn|cudart|torch", n, re.I)]
+
+
+def test_loss_scale_policy_is_gradscalers(flint):
+    from flint_b200.trainer import LossScaler
+
+    lib = flint.train
+    python = LossScaler(65536.0, growth_interval=3)
+    scale, good = 65536.0, 0
+    for found in [0, 0, 1, 0, 0, 0, 0, 1, 1, 0, 0, 0]:
+        next_scale, next_good = ctypes.c_float(), ctypes.c_int()
+        status = lib.flint_train_scale_policy(scale, good, 3, found, ctypes.byref(next_scale),
+                                              ctypes.cast(ctypes.byref(next_good), ctypes.c_void_p))
+        assert status == flint_b200.OK
+        scale, good = next_scale.value, next_good.value
+        python.update(bool(found))
+        assert (scale, good) == (python.scale, python.good_steps)
+    assert scale == 32768.0 and good == 0  # 2^16: /2, x2, /2, /2, x2
+
+
+def test_trainer_configuration_is_validated_before_any_cuda_call(flint):
+    lib = flint.train
+
+    def create(**changes):
+        c = binding.TrainerConfigC()
+        c.model = flint_b200.Gpt2Config(2, 2, 128, 64, 200, 208, 2, 64, 0, 1)
+        c.flash_attention, c.lr, c.beta1, c.beta2, c.eps = 1, 6e-4, 0.9, 0.95, 1e-8
+        c.weight_decay, c.loss_scale, c.growth_interval, c.max_grad_norm = 0.1, 65536.0, 2000, 0.0
+        c.world, c.rank = 1, 0
+        for key, value in changes.items():
+            setattr(c, key, value)
+        handle = ctypes.c_void_p(1)
+        status = lib.flint_trainer_create(ctypes.byref(c), None, ctypes.byref(handle))
+        return status, handle.value, lib.flint_train_last_error().decode()
+
+    for changes, text in [(dict(world=0), "rank (0) must be from 0 to world (0) - 1"),
+                          (dict(world=2, rank=2), "rank (2) must be from 0 to world (2) - 1"),
+                          (dict(beta1=1.0), "betas in [0, 1)"),
+                          (dict(loss_scale=0.0), "loss_scale (0) must be positive"),
+                          (dict(growth_interval=0), "growth_interval (0) must be at least 1"),
+                          (dict(max_grad_norm=-1.0), "max_grad_norm (-1) must be finite")]:
+        status, handle, message = create(**changes)
+        assert status == flint_b200.ERROR_INVALID_ARGUMENT and handle is None, changes
+        assert text in message, (changes, message)
+    assert lib.flint_trainer_step(None, None, None, 1, None) == flint_b200.ERROR_INVALID_ARGUMENT
+    assert "must not be null" in lib.flint_train_last_error().decode()

@@ -26,7 +26,7 @@ def free_port():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_pipelined_update_rank_agreement_and_skipped_steps_on_two_ranks():
+def test_update_modes_rank_agreement_skipped_steps_and_checkpoints_on_two_ranks():
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
     command = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
