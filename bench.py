@@ -102,8 +102,8 @@ def step_gemms(rows: int):
     (flint_b200/csrc/gpt2.cu, forward_block / backward_block and the head)."""
     w, v, layers = 768, 50304, 12
     forward = [("nt_bias", rows, 3 * w, w), ("nt_bias_residual", rows, w, w),
-               ("nt_bias_gelu_grad", rows, 4 * w, w), ("nt_bias_residual", rows, w, 4 * w)]
-    backward = [("tn", w, 4 * w, rows), ("nn_scaled", rows, 4 * w, w), ("tn", 4 * w, w, rows),
+               ("nt_bias_gelu", rows, 4 * w, w), ("nt_bias_residual", rows, w, 4 * w)]
+    backward = [("tn", w, 4 * w, rows), ("nn_dgelu", rows, 4 * w, w), ("tn", 4 * w, w, rows),
                 ("nn", rows, w, 4 * w), ("tn", w, w, rows), ("nn", rows, w, w),
                 ("tn", 3 * w, w, rows), ("nn", rows, w, 3 * w)]
     return layers * (forward + backward) + [("nt", rows, v, w), ("tn", v, w, rows),
@@ -145,14 +145,14 @@ def gemm_roofline(flint, torch, rows: int, reps: int = 3):
                 flint.gemm_nt(y, a, b, m, n, k)
             elif kind == "nt_bias":
                 flint.gemm_nt_bias(y, a, b, bias, m, n, k)
-            elif kind == "nt_bias_gelu_grad":
-                flint.gemm_nt_bias_gelu_grad(y, pre, a, b, bias, m, n, k)
+            elif kind == "nt_bias_gelu":
+                flint.gemm_nt_bias_gelu(y, pre, a, b, bias, m, n, k)
             elif kind == "nt_bias_residual":
                 flint.gemm_nt_bias_residual(y32, a, b, bias, residual, m, n, k)
             elif kind == "nn":
                 flint.gemm_nn(y, a, b, m, n, k)
-            elif kind == "nn_scaled":
-                flint.gemm_nn_scaled(y, a, b, pre, m, n, k)
+            elif kind == "nn_dgelu":
+                flint.gemm_nn_dgelu(y, a, b, pre, m, n, k)
             else:
                 flint.gemm_tn(y32, a, b, m, n, k, True, workspace)
 

@@ -356,12 +356,6 @@ class Flint:
     def gemm_nn_dgelu(self, y, x, w, pre, m, n, k, stream=None) -> None:
         self.call("flint_gemm_nn_dgelu", y, x, w, pre, m, n, k, stream=stream)
 
-    def gemm_nt_bias_gelu_grad(self, y, grad, x, w, bias, m, n, k, stream=None) -> None:
-        self.call("flint_b200_gemm_nt_bias_gelu_grad", y, grad, x, w, bias, m, n, k, stream=stream)
-
-    def gemm_nn_scaled(self, y, x, w, factor, m, n, k, stream=None) -> None:
-        self.call("flint_b200_gemm_nn_scaled", y, x, w, factor, m, n, k, stream=stream)
-
     def gemm_tn_workspace(self, m, n, k) -> int:
         return self._size_query("flint_gemm_tn_workspace", m, n, k)
 

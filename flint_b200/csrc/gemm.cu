@@ -72,15 +72,6 @@ struct GemmParams {
     int batched;
 };
 
-// kBiasGeluGrad and kMulSaved share every code path of kBiasGelu and kDGelu except
-// the arithmetic itself: what is written beside GELU(s), and what the sums are multiplied by.
-__host__ __device__ constexpr bool is_gelu(Epilogue e) {
-    return e == Epilogue::kBiasGelu || e == Epilogue::kBiasGeluGrad;
-}
-__host__ __device__ constexpr bool is_dgelu(Epilogue e) {
-    return e == Epilogue::kDGelu || e == Epilogue::kMulSaved;
-}
-
 // ---- epilogue math ----------------------------------------------------------------
 
 // 2^x on the special-function unit (relative error about 2^-22; flushes denormals).
@@ -158,40 +149,6 @@ __device__ __forceinline__ float gelu_tanh_grad(float x) {
     return lo;
 }
 
-// GELU and its derivative of the same two values, sharing the exponential and the
-// sigmoid: y = x s, g = s + x s (1 - s) 2u'. In place: x becomes y; returns g.
-__device__ __forceinline__ fb::F2 gelu_tanh_with_grad2(fb::F2& x) {
-    constexpr float kScale = -2.302208198144325f;
-    constexpr float k2Rt2OverPi = 1.5957691216057308f;
-    constexpr float k6KappaRt2OverPi = 0.21406444946504453f;
-    const fb::F2 one = fb::f2_pack(1.0f, 1.0f);
-    const fb::F2 x2 = fb::f2_mul(x, x);
-    const fb::F2 t = fb::f2_fma(fb::f2_pack(0.044715f, 0.044715f), x2, one);
-    const fb::F2 arg = fb::f2_mul(fb::f2_mul(fb::f2_pack(kScale, kScale), x), t);
-    float a0, a1, x0, x1;
-    fb::f2_unpack(arg, a0, a1);
-    fb::f2_unpack(x, x0, x1);
-    const fb::F2 e = fb::f2_pack(exp2_fast(a0), exp2_fast(a1));
-    float d0, d1;
-    fb::f2_unpack(fb::f2_add(e, one), d0, d1);
-    const fb::F2 s = fb::f2_pack(rcp_fast(d0), rcp_fast(d1));
-    float n0, n1, p0, p1;
-    fb::f2_unpack(fb::f2_sub(one, s), n0, n1);
-    fb::f2_unpack(fb::f2_mul(e, s), p0, p1);
-    const fb::F2 one_minus_s = fb::f2_pack(x0 < 0.0f ? n0 : p0, x1 < 0.0f ? n1 : p1);
-    const fb::F2 slope = fb::f2_fma(fb::f2_pack(k6KappaRt2OverPi, k6KappaRt2OverPi), x2,
-                                    fb::f2_pack(k2Rt2OverPi, k2Rt2OverPi));
-    const fb::F2 y = fb::f2_mul(x, s);
-    const fb::F2 q = fb::f2_mul(fb::f2_mul(x, one_minus_s), slope);
-    float g0, g1;
-    fb::f2_unpack(fb::f2_fma(s, q, s), g0, g1);
-    // Sums beyond FP16's range: the limits 1 and 0 (x (1 - s) would be inf * 0).
-    g0 = fabsf(x0) > 65504.0f ? (x0 > 0.0f ? 1.0f : 0.0f) : g0;
-    g1 = fabsf(x1) > 65504.0f ? (x1 > 0.0f ? 1.0f : 0.0f) : g1;
-    x = y;
-    return fb::f2_pack(g0, g1);
-}
-
 __device__ __forceinline__ float half_bits_to_float(unsigned short h) {
     return __half2float(__ushort_as_half(h));
 }
@@ -205,7 +162,7 @@ __device__ __forceinline__ void store_segment(const GemmParams& p, size_t batch_
                                               float (&acc)[32], int valid) {
     const size_t n = static_cast<size_t>(p.n);
     const size_t at = batch_offset + row * n + col;
-    if constexpr (E == Epilogue::kBias || is_gelu(E) ||
+    if constexpr (E == Epilogue::kBias || E == Epilogue::kBiasGelu ||
                   E == Epilogue::kBiasResidual) {
         const float* bias = p.bias + col;
 #pragma unroll
@@ -221,7 +178,7 @@ __device__ __forceinline__ void store_segment(const GemmParams& p, size_t batch_
             acc[j] = __fmul_rn(acc[j], p.scale);
         }
     }
-    if constexpr (is_dgelu(E)) {
+    if constexpr (E == Epilogue::kDGelu) {
         const __half* pre = static_cast<const __half*>(p.aux_in) + at;
         // NN's n is a multiple of 8, so 8-column groups are whole and 16-byte aligned.
 #pragma unroll
@@ -233,10 +190,8 @@ __device__ __forceinline__ void store_segment(const GemmParams& p, size_t batch_
                 for (int j = 0; j < 4; ++j) {
                     const float lo = half_bits_to_float(static_cast<unsigned short>(w[j]));
                     const float hi = half_bits_to_float(static_cast<unsigned short>(w[j] >> 16));
-                    const float f0 = E == Epilogue::kMulSaved ? lo : gelu_tanh_grad(lo);
-                    const float f1 = E == Epilogue::kMulSaved ? hi : gelu_tanh_grad(hi);
-                    acc[g * 8 + 2 * j] = __fmul_rn(acc[g * 8 + 2 * j], f0);
-                    acc[g * 8 + 2 * j + 1] = __fmul_rn(acc[g * 8 + 2 * j + 1], f1);
+                    acc[g * 8 + 2 * j] = __fmul_rn(acc[g * 8 + 2 * j], gelu_tanh_grad(lo));
+                    acc[g * 8 + 2 * j + 1] = __fmul_rn(acc[g * 8 + 2 * j + 1], gelu_tanh_grad(hi));
                 }
             }
         }
@@ -288,7 +243,7 @@ __device__ __forceinline__ void store_segment(const GemmParams& p, size_t batch_
         // FP16 outputs; the GELU form writes the pre-activation too.
         __half* out = static_cast<__half*>(p.y) + at;
         __half* pre_out = nullptr;
-        if constexpr (is_gelu(E)) {
+        if constexpr (E == Epilogue::kBiasGelu) {
             pre_out = static_cast<__half*>(p.aux_out) + at;
         }
         if (p.n % 8 == 0) {
@@ -297,17 +252,14 @@ __device__ __forceinline__ void store_segment(const GemmParams& p, size_t batch_
                 if (g * 8 < valid) {
                     uint4 q;
                     unsigned* w = reinterpret_cast<unsigned*>(&q);
-                    if constexpr (is_gelu(E)) {
+                    if constexpr (E == Epilogue::kBiasGelu) {
                         uint4 qp;
                         unsigned* wp = reinterpret_cast<unsigned*>(&qp);
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             const float a = acc[g * 8 + 2 * j];
                             const float b = acc[g * 8 + 2 * j + 1];
-                            const __half2 hp =
-                                E == Epilogue::kBiasGeluGrad
-                                    ? __floats2half2_rn(gelu_tanh_grad(a), gelu_tanh_grad(b))
-                                    : __floats2half2_rn(a, b);
+                            const __half2 hp = __floats2half2_rn(a, b);
                             const __half2 hy = __floats2half2_rn(gelu_tanh(a), gelu_tanh(b));
                             wp[j] = *reinterpret_cast<const unsigned*>(&hp);
                             w[j] = *reinterpret_cast<const unsigned*>(&hy);
@@ -329,9 +281,8 @@ __device__ __forceinline__ void store_segment(const GemmParams& p, size_t batch_
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
                 if (j < valid) {
-                    if constexpr (is_gelu(E)) {
-                        pre_out[j] = __float2half_rn(
-                            E == Epilogue::kBiasGeluGrad ? gelu_tanh_grad(acc[j]) : acc[j]);
+                    if constexpr (E == Epilogue::kBiasGelu) {
+                        pre_out[j] = __float2half_rn(acc[j]);
                         out[j] = __float2half_rn(gelu_tanh(acc[j]));
                     } else {
                         out[j] = __float2half_rn(acc[j]);
@@ -437,7 +388,7 @@ __device__ __forceinline__ void flush_half_chunk(uint32_t stage, __half* out_chu
 template <Epilogue E>
 __host__ __device__ constexpr int aux_slots() {
     return (E == Epilogue::kBiasResidual || E == Epilogue::kTnStore) ? 8
-           : is_dgelu(E)                                   ? 4
+           : E == Epilogue::kDGelu                                   ? 4
                                                                       : 1;
 }
 
@@ -468,7 +419,7 @@ __device__ __forceinline__ void load_aux(Aux<E>& aux, const GemmParams& p, size_
                 aux.q[i] = *reinterpret_cast<const uint4*>(old + static_cast<size_t>(r) * n + c * 4);
             }
         }
-    } else if constexpr (is_dgelu(E)) {
+    } else if constexpr (E == Epilogue::kDGelu) {
         // Each lane fetches its own row's 64 bytes (two whole sectors), so the saved
         // pre-activations need no trip through shared memory.
         const __half* pre = static_cast<const __half*>(p.aux_in) + at0 + static_cast<size_t>(lane) * n;
@@ -486,7 +437,7 @@ __device__ __forceinline__ void load_aux(Aux<E>& aux, const GemmParams& p, size_
 // epilogues and past the last column).
 template <Epilogue E>
 __device__ __forceinline__ float load_bias_lane(const GemmParams& p, int col, int lane) {
-    if constexpr (E == Epilogue::kBias || is_gelu(E) ||
+    if constexpr (E == Epilogue::kBias || E == Epilogue::kBiasGelu ||
                   E == Epilogue::kBiasResidual) {
         return col + lane < p.n ? __ldg(p.bias + col + lane) : 0.0f;
     } else {
@@ -507,7 +458,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t stage,
     const long long rows_long = static_cast<long long>(p.m) - static_cast<long long>(row0);
     const int rows_left = rows_long > 32 ? 32 : static_cast<int>(rows_long);
 
-    if constexpr (E == Epilogue::kBias || is_gelu(E) ||
+    if constexpr (E == Epilogue::kBias || E == Epilogue::kBiasGelu ||
                   E == Epilogue::kBiasResidual) {
         // Lane j holds bias[col + j] (fetched by the caller a chunk ahead, zero past the
         // matrix's edge); every lane needs all 32, so they are passed round by shuffles
@@ -571,7 +522,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t stage,
         return;
     } else {
         __half* out = static_cast<__half*>(p.y) + at0;
-        if constexpr (is_dgelu(E)) {
+        if constexpr (E == Epilogue::kDGelu) {
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const uint4 q = aux.q[c];
@@ -580,10 +531,8 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t stage,
                 for (int j = 0; j < 4; ++j) {
                     const float lo = half_bits_to_float(static_cast<unsigned short>(w[j]));
                     const float hi = half_bits_to_float(static_cast<unsigned short>(w[j] >> 16));
-                    float g0 = lo, g1 = hi;
-                    if constexpr (E == Epilogue::kDGelu) {
-                        fb::f2_unpack(gelu_tanh_grad2(fb::f2_pack(lo, hi)), g0, g1);
-                    }
+                    float g0, g1;
+                    fb::f2_unpack(gelu_tanh_grad2(fb::f2_pack(lo, hi)), g0, g1);
                     acc[c * 8 + 2 * j] = __fmul_rn(acc[c * 8 + 2 * j], g0);
                     acc[c * 8 + 2 * j + 1] = __fmul_rn(acc[c * 8 + 2 * j + 1], g1);
                 }
@@ -595,25 +544,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t stage,
                 store_wait_slots_read();
             }
             __syncwarp();
-            if constexpr (E == Epilogue::kBiasGeluGrad) {
-                // Eight values at a time: the derivatives leave for the first slot as they
-                // are made, the GELUs replace the sums and follow as a whole row.
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint4 q;
-                    unsigned* w = reinterpret_cast<unsigned*>(&q);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        fb::F2 v = fb::f2_pack(acc[8 * c + 2 * j], acc[8 * c + 2 * j + 1]);
-                        float g0, g1;
-                        fb::f2_unpack(gelu_tanh_with_grad2(v), g0, g1);
-                        fb::f2_unpack(v, acc[8 * c + 2 * j], acc[8 * c + 2 * j + 1]);
-                        w[j] = fb::pack2(g0, g1);
-                    }
-                    st_shared_v4(stage + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4), q);
-                }
-                stage_row_for_store(stage + 2048u, lane, acc);
-            } else if constexpr (is_gelu(E)) {
+            if constexpr (E == Epilogue::kBiasGelu) {
                 stage_row_for_store(stage, lane, acc);
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
@@ -627,7 +558,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t stage,
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) {
-                if constexpr (is_gelu(E)) {
+                if constexpr (E == Epilogue::kBiasGelu) {
                     store_chunk_async(&p.map_pre, stage, col, static_cast<int>(row0));
                     store_chunk_async(&p.map_y, stage + 2048u, col, static_cast<int>(row0));
                 } else {
@@ -637,34 +568,17 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t stage,
             }
             return;
         }
-        if constexpr (is_gelu(E)) {
+        if constexpr (E == Epilogue::kBiasGelu) {
             // The pre-activation goes to the slot's first half, GELU of the unrounded
             // sums to the second; one trip through shared memory serves both outputs.
-            if constexpr (E == Epilogue::kBiasGeluGrad) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint4 q;
-                    unsigned* w = reinterpret_cast<unsigned*>(&q);
+            for (int c = 0; c < 4; ++c) {
+                st_shared_v4(stage_slot(stage, lane * 4 + c), pack_half8(acc + 8 * c));
+            }
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        fb::F2 v = fb::f2_pack(acc[8 * c + 2 * j], acc[8 * c + 2 * j + 1]);
-                        float g0, g1;
-                        fb::f2_unpack(gelu_tanh_with_grad2(v), g0, g1);
-                        fb::f2_unpack(v, acc[8 * c + 2 * j], acc[8 * c + 2 * j + 1]);
-                        w[j] = fb::pack2(g0, g1);
-                    }
-                    st_shared_v4(stage_slot(stage, lane * 4 + c), q);
-                }
-            } else {
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    st_shared_v4(stage_slot(stage, lane * 4 + c), pack_half8(acc + 8 * c));
-                }
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    fb::f2_unpack(gelu_tanh2(fb::f2_pack(acc[2 * j], acc[2 * j + 1])), acc[2 * j],
-                                  acc[2 * j + 1]);
-                }
+            for (int j = 0; j < 16; ++j) {
+                fb::f2_unpack(gelu_tanh2(fb::f2_pack(acc[2 * j], acc[2 * j + 1])), acc[2 * j],
+                              acc[2 * j + 1]);
             }
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
@@ -1275,7 +1189,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + 32 * pair_epilo
             // second accumulator set in flight as well would not fit in registers.
             constexpr bool kPipelined =
                 !(E == Epilogue::kBiasResidual || E == Epilogue::kTnStore ||
-                  E == Epilogue::kTnPartial || is_dgelu(E));
+                  E == Epilogue::kTnPartial || E == Epilogue::kDGelu);
             uint32_t raw[2][32];
             auto chunk_column = [&](int i) { return column_part * 32 + i * kColumnStep; };
             auto chunk_valid = [&](int i) { return min(32, p.n - (col0 + chunk_column(i))); };
@@ -1299,7 +1213,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + 32 * pair_epilo
                 }
                 // (Only where the operands are few registers: with the FP32 residual's 32
                 // registers held through the last chunk as well, the kernel was slower.)
-                if (is_dgelu(E) && kAhead && prefetch && last &&
+                if (E == Epilogue::kDGelu && kAhead && prefetch && last &&
                     id + pairs < p.tiles_total) {
                     // The next tile's first chunk.
                     const TileCoord t2 = decode_pair_tile(p, id + pairs);
@@ -1421,24 +1335,22 @@ __global__ void __launch_bounds__(256)
             acc = fmaf(a, c, acc);
         }
         const size_t at = static_cast<size_t>(b) * p.m * p.n + static_cast<size_t>(row) * p.n + col;
-        if (E == Epilogue::kBias || is_gelu(E) || E == Epilogue::kBiasResidual) {
+        if (E == Epilogue::kBias || E == Epilogue::kBiasGelu || E == Epilogue::kBiasResidual) {
             acc = __fadd_rn(acc, p.bias[col]);
         }
         if (E == Epilogue::kScale) {
             acc = __fmul_rn(acc, p.scale);
         }
-        if (is_dgelu(E)) {
-            const float saved = __half2float(static_cast<const __half*>(p.aux_in)[at]);
-            acc = __fmul_rn(acc, E == Epilogue::kMulSaved ? saved : gelu_tanh_grad(saved));
+        if (E == Epilogue::kDGelu) {
+            acc = __fmul_rn(acc, gelu_tanh_grad(__half2float(static_cast<const __half*>(p.aux_in)[at])));
         }
         if (E == Epilogue::kBiasResidual) {
             static_cast<float*>(p.y)[at] = __fadd_rn(static_cast<const float*>(p.aux_in)[at], acc);
         } else if (E == Epilogue::kTnStore) {
             float* out = static_cast<float*>(p.y) + at;
             *out = p.accumulate ? __fadd_rn(*out, acc) : acc;
-        } else if (is_gelu(E)) {
-            static_cast<__half*>(p.aux_out)[at] =
-                __float2half_rn(E == Epilogue::kBiasGeluGrad ? gelu_tanh_grad(acc) : acc);
+        } else if (E == Epilogue::kBiasGelu) {
+            static_cast<__half*>(p.aux_out)[at] = __float2half_rn(acc);
             static_cast<__half*>(p.y)[at] = __float2half_rn(gelu_tanh(acc));
         } else {
             static_cast<__half*>(p.y)[at] = __float2half_rn(acc);
@@ -1606,12 +1518,12 @@ cudaError_t launch_pair(GemmParams& p, const void* x, const void* w, int sms, cu
     // FP16 outputs of unbatched calls leave through TMA stores when the rows are 16-byte
     // multiples (the tensor map's requirement; the same rule as the coalesced path).
     constexpr bool kHalfOut = E == Epilogue::kNone || E == Epilogue::kBias ||
-                              is_gelu(E) || is_dgelu(E) ||
+                              E == Epilogue::kBiasGelu || E == Epilogue::kDGelu ||
                               E == Epilogue::kScale;
     p.tma_out = 0;
     if (kHalfOut && L != Layout::kTN && !batched && p.n % 8 == 0) {
         e = fb::encode_rows_map(&p.map_y, p.y, p.m, p.n, 2, 32, 32, 64);
-        if (e == cudaSuccess && is_gelu(E)) {
+        if (e == cudaSuccess && E == Epilogue::kBiasGelu) {
             e = fb::encode_rows_map(&p.map_pre, p.aux_out, p.m, p.n, 2, 32, 32, 64);
         }
         if (e != cudaSuccess) {
@@ -1727,8 +1639,6 @@ cudaError_t gemm_nt(Epilogue e, void* y, void* pre, const void* x, const void* w
         return launch_any<Layout::kNT, Epilogue::kBias>(p, x, w, stream);
     case Epilogue::kBiasGelu:
         return launch_any<Layout::kNT, Epilogue::kBiasGelu>(p, x, w, stream);
-    case Epilogue::kBiasGeluGrad:
-        return launch_any<Layout::kNT, Epilogue::kBiasGeluGrad>(p, x, w, stream);
     case Epilogue::kBiasResidual:
         return launch_any<Layout::kNT, Epilogue::kBiasResidual>(p, x, w, stream);
     default:
@@ -1742,9 +1652,6 @@ cudaError_t gemm_nn(Epilogue e, void* y, const void* x, const void* w, const voi
     p.aux_in = pre;
     if (e == Epilogue::kDGelu) {
         return launch_any<Layout::kNN, Epilogue::kDGelu>(p, x, w, stream);
-    }
-    if (e == Epilogue::kMulSaved) {
-        return launch_any<Layout::kNN, Epilogue::kMulSaved>(p, x, w, stream);
     }
     return launch_any<Layout::kNN, Epilogue::kNone>(p, x, w, stream);
 }

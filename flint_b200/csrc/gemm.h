@@ -19,12 +19,7 @@ enum class Epilogue {
     kBiasResidual,  // FP32: residual + (acc + bias)
     kScale,         // * scale
     kTnStore,       // FP32 store or old + acc
-    kTnPartial,     // FP32 store into the split's slice of the workspace
-    // The two below serve the model built on the fused attention kernels (not the public
-    // entry points): the forward GEMM saves GELU'(s) where kBiasGelu saves s, so that the
-    // backward GEMM multiplies by the saved factor instead of evaluating the derivative.
-    kBiasGeluGrad,  // + bias, store GELU'(s) (FP16) and GELU(s)
-    kMulSaved       // * the saved FP16 factor
+    kTnPartial      // FP32 store into the split's slice of the workspace
 };
 
 // How flint_gemm_tn divides k: `count` CTAs per output tile, each taking

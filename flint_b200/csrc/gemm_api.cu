@@ -4,7 +4,6 @@
 #include <cmath>
 
 #include "common.h"
-#include "flint/flint_b200.h"
 #include "gemm.h"
 
 namespace {
@@ -222,48 +221,6 @@ flint_status flint_gemm_nn_dgelu(void* y, const void* x, const void* w, const vo
     FB_TRY(check_nt_nn(name, true, y, x, w, m, n, k));
     FB_TRY(check_extra(name, "pre", y, m * n * 2, pre, m * n * 2));
     FB_CUDA(fb::gemm_nn(fb::Epilogue::kDGelu, y, x, w, pre, m, n, k, stream));
-    return FLINT_OK;
-}
-
-// ---- extension: the GELU pair that saves the derivative ------------------------------------------
-//
-// flint_gemm_nt_bias_gelu and flint_gemm_nn_dgelu with the same checks and messages; what
-// differs is the second output / third input: GELU'(s) in FP16 instead of s.
-
-flint_status flint_b200_gemm_nt_bias_gelu_grad(void* y, void* grad, const void* x, const void* w,
-                                               const void* bias, size_t m, size_t n, size_t k,
-                                               flint_stream stream) {
-    if (m == 0 || n == 0) {
-        return FLINT_OK;
-    }
-    constexpr const char* name = "flint_b200_gemm_nt_bias_gelu_grad";
-    FB_TRY(check_nt_nn(name, false, y, x, w, m, n, k));
-    FB_TRY(check_extra(name, "bias", y, m * n * 2, bias, n * 4));
-    FB_TRY(check_extra(name, "grad", y, m * n * 2, grad, m * n * 2));
-    const size_t grad_bytes = m * n * 2;
-    if (overlap(grad, grad_bytes, x, m * k * 2)) {
-        return fail(kInvalid, "%s: grad and x overlap", name);
-    }
-    if (overlap(grad, grad_bytes, w, n * k * 2)) {
-        return fail(kInvalid, "%s: grad and w overlap", name);
-    }
-    if (overlap(grad, grad_bytes, bias, n * 4)) {
-        return fail(kInvalid, "%s: grad and bias overlap", name);
-    }
-    FB_CUDA(fb::gemm_nt(fb::Epilogue::kBiasGeluGrad, y, grad, x, w, bias, nullptr, m, n, k,
-                        stream));
-    return FLINT_OK;
-}
-
-flint_status flint_b200_gemm_nn_scaled(void* y, const void* x, const void* w, const void* factor,
-                                       size_t m, size_t n, size_t k, flint_stream stream) {
-    if (m == 0 || n == 0) {
-        return FLINT_OK;
-    }
-    constexpr const char* name = "flint_b200_gemm_nn_scaled";
-    FB_TRY(check_nt_nn(name, true, y, x, w, m, n, k));
-    FB_TRY(check_extra(name, "factor", y, m * n * 2, factor, m * n * 2));
-    FB_CUDA(fb::gemm_nn(fb::Epilogue::kMulSaved, y, x, w, factor, m, n, k, stream));
     return FLINT_OK;
 }
 

@@ -23,7 +23,6 @@
 #include "attention.h"
 #include "common.h"
 #include "flint/flint_b200.h"
-#include "gemm.h"
 #include "gpt2.h"
 
 namespace {
@@ -383,15 +382,8 @@ flint_status forward_block(const flint_gpt2& m, size_t i, flint_stream s) {
     FB_TRY(flint_gemm_nt_bias_residual(a.x_mid, a.attn, wt.proj_w->half, wt.proj_b->data, a.x_in,
                                        rows, w, w, s));
     FB_TRY(layernorm(m, wt.ln2_w, wt.ln2_b, a.x_mid, a.h2, a.mean2, a.rstd2, s));
-    if (m.flash) {
-        // The extension model keeps GELU'(s) where the reference keeps s (a.pre): the backward
-        // GEMM then multiplies by the saved factor instead of evaluating the derivative.
-        FB_CUDA(fb::gemm_nt(fb::Epilogue::kBiasGeluGrad, a.gelu, a.pre, a.h2, wt.fc_w->half,
-                            wt.fc_b->data, nullptr, rows, 4 * w, w, s));
-    } else {
-        FB_TRY(flint_gemm_nt_bias_gelu(a.gelu, a.pre, a.h2, wt.fc_w->half, wt.fc_b->data, rows,
-                                       4 * w, w, s));
-    }
+    FB_TRY(flint_gemm_nt_bias_gelu(a.gelu, a.pre, a.h2, wt.fc_w->half, wt.fc_b->data, rows, 4 * w,
+                                   w, s));
     return flint_gemm_nt_bias_residual(a.x_out, a.gelu, wt.fcproj_w->half, wt.fcproj_b->data,
                                        a.x_mid, rows, w, 4 * w, s);
 }
@@ -442,13 +434,7 @@ flint_status backward_block(const flint_gpt2& m, size_t i, int accumulate, flint
     // MLP. dres_half already holds dres in FP16 (written by the LayerNorm backward before).
     FB_TRY(weight_gradient(m, wt.fcproj_w, m.dres_half, a.gelu, accumulate, s));
     FB_TRY(bias_gradient(m, wt.fcproj_b, m.dres_half, accumulate, s));
-    if (m.flash) {
-        FB_CUDA(fb::gemm_nn(fb::Epilogue::kMulSaved, m.dpre, m.dres_half, wt.fcproj_w->half, a.pre,
-                            rows, 4 * w, w, s));
-    } else {
-        FB_TRY(flint_gemm_nn_dgelu(m.dpre, m.dres_half, wt.fcproj_w->half, a.pre, rows, 4 * w, w,
-                                   s));
-    }
+    FB_TRY(flint_gemm_nn_dgelu(m.dpre, m.dres_half, wt.fcproj_w->half, a.pre, rows, 4 * w, w, s));
     FB_TRY(weight_gradient(m, wt.fc_w, m.dpre, a.h2, accumulate, s));
     FB_TRY(bias_gradient(m, wt.fc_b, m.dpre, accumulate, s));
     FB_TRY(flint_gemm_nn(m.dh, m.dpre, wt.fc_w->half, rows, w, 4 * w, s));

@@ -345,40 +345,6 @@ def dgelu_case(f: Flint, rows: int, once: bool, gen):
         layout="NN", epilogue="dgelu", m=m, n=n, k=k)
 
 
-def gelu_saved_cases(f: Flint, rows: int, once: bool, gen):
-    """The derivative-saving pair used by the model built on the fused attention kernels."""
-    m, n, k = rows, 4 * WIDTH, WIDTH
-    sets = rotation_sets((m * k + n * k + 2 * m * n) * 2, once)
-    x = [half(m, k, gen=gen) for _ in range(sets)]
-    wt = [half(n, k, scale=0.02, gen=gen) for _ in range(sets)]
-    wn = [half(k, n, scale=0.02, gen=gen) for _ in range(sets)]
-    y = [torch.empty(m, n, dtype=torch.half, device=DEV) for _ in range(sets)]
-    grad = [half(m, n, scale=0.5, gen=gen) for _ in range(sets)]
-    dh = [torch.empty(m, n, dtype=torch.half, device=DEV) for _ in range(sets)]
-    bias = torch.randn(n, device=DEV, generator=gen) * 0.02
-    bias16 = bias.half()
-    tmp = torch.empty(m, n, dtype=torch.half, device=DEV)
-
-    def baseline_backward(i):
-        torch.mm(x[i], wn[i], out=tmp)
-        return tmp.mul_(grad[i])
-
-    return [
-        Case("epilogue", f"nt+bias+gelu, saves GELU' {m}x{n}x{k}", "TFLOP/s", flop(m, n, k), sets,
-             lambda i: f.gemm_nt_bias_gelu_grad(y[i], grad[i], x[i], wt[i], bias, m, n, k),
-             lambda i: torch._addmm_activation(bias16, x[i], wt[i].t(), use_gelu=True),
-             "cuBLASLt GELU_BIAS epilogue (one output)",
-             note="flint writes GELU and its derivative, the baseline GELU only",
-             layout="NT", epilogue="bias+gelu+grad", m=m, n=n, k=k),
-        Case("epilogue", f"nn * saved GELU' {m}x{n}x{k}", "TFLOP/s", flop(m, n, k), sets,
-             lambda i: f.gemm_nn_scaled(dh[i], x[i], wn[i], grad[i], m, n, k), baseline_backward,
-             "cuBLAS GEMM + ATen mul: two kernels",
-             lambda: (f.gemm_nn_scaled(dh[0], x[0], wn[0], grad[0], m, n, k),
-                      rel_l2(dh[0], baseline_backward(0)))[1],
-             layout="NN", epilogue="* saved factor", m=m, n=n, k=k),
-    ]
-
-
 def epilogue_cases(f: Flint, rows: int, once: bool):
     w, w4 = WIDTH, 4 * WIDTH
     gen = torch.Generator(device=DEV).manual_seed(0x5EED0002)
@@ -406,7 +372,6 @@ def epilogue_cases(f: Flint, rows: int, once: bool):
 
     cases.append(gelu_case(f, rows, once, gen))
     cases.append(dgelu_case(f, rows, once, gen))
-    cases.extend(gelu_saved_cases(f, rows, once, gen))
 
     # bias + FP32 residual, FP32 out: attention projection and MLP down
     for label, (m, n, k) in {"projection": (rows, w, w), "mlp down": (rows, w, w4)}.items():

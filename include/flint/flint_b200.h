@@ -43,23 +43,6 @@ FLINT_API flint_status flint_b200_attention_backward(void* dq, void* dk, void* d
                                                      size_t head_width, float scale,
                                                      flint_stream stream);
 
-/* flint_gemm_nt_bias_gelu (ref: flint.h:74-83) that saves the derivative instead
- * of the pre-activation: s = x w^T + bias in FP32, y = half(GELU(s)) and
- * grad = half(GELU'(s)) (tanh form, limits 1 and 0 beyond FP16's range). Same
- * argument rules and messages, with `grad` in the place of `pre`. Paired with
- * flint_b200_gemm_nn_scaled below it replaces bias+GELU / GELU-backward in a
- * model that is free to choose what it keeps for the backward pass: the
- * backward GEMM's epilogue becomes one multiplication. */
-FLINT_API flint_status flint_b200_gemm_nt_bias_gelu_grad(void* y, void* grad, const void* x,
-                                                         const void* w, const void* bias, size_t m,
-                                                         size_t n, size_t k, flint_stream stream);
-
-/* y = half((x w) * factor): flint_gemm_nn_dgelu (ref: flint.h:104-114) given the
- * saved derivative as `factor` (FP16 [m, n]) instead of the pre-activation. */
-FLINT_API flint_status flint_b200_gemm_nn_scaled(void* y, const void* x, const void* w,
-                                                 const void* factor, size_t m, size_t n, size_t k,
-                                                 flint_stream stream);
-
 /* flint_gpt2_create with a choice of attention: flash_attention non-zero builds
  * the model on the fused kernels above (no T x T buffers, so far less memory);
  * zero is flint_gpt2_create. */

@@ -405,70 +405,3 @@ def test_gelu_derivative_is_within_one_ulp_and_correctly_rounded_where_that_is_d
     assert safe.sum() > 0.95 * safe.numel()
     wrong = safe & (oracle.half_ordered(y) != oracle.half_ordered(exact))
     assert not wrong.any(), int(wrong.sum())
-
-
-# ---- the GELU pair that saves the derivative (extension) ---------------------------------------
-
-
-@pytest.mark.parametrize("m, n, k", [(GPT2_ROWS, 3072, 768), (100, 56, 72), (300, 64, 8)])
-def test_gelu_grad_pair_matches_the_oracle_and_the_reference_pair(flint, m, n, k):
-    """flint_b200_gemm_nt_bias_gelu_grad writes GELU(s) and GELU'(s); flint_b200_gemm_nn_scaled
-    multiplies by a saved factor. Together they compute what flint_gemm_nt_bias_gelu +
-    flint_gemm_nn_dgelu compute, with the derivative rounded to FP16 once more on the way."""
-    x, w = inputs((m, k), (n, k), 11 + m, sigma_w=0.05)
-    bias = torch.randn(n, generator=torch.Generator().manual_seed(12)) * 0.5
-    y = torch.zeros(m, n, dtype=torch.half, device=DEV)
-    grad = torch.zeros_like(y)
-    flint.gemm_nt_bias_gelu_grad(y, grad, x.to(DEV), w.to(DEV), bias.to(DEV), m, n, k)
-    y_ref = torch.zeros_like(y)
-    pre = torch.zeros_like(y)
-    flint.gemm_nt_bias_gelu(y_ref, pre, x.to(DEV), w.to(DEV), bias.to(DEV), m, n, k)
-    no_fault(flint)
-    assert torch.equal(y.view(torch.int16), y_ref.view(torch.int16))       # the same GELU bits
-    s = oracle.gemm_nt(x, w, bias)
-    want_grad, _ = oracle.gelu_tanh_derivative(s)
-    exact = oracle.round_to_half(want_grad)
-    distance = (oracle.half_ordered(grad.cpu()) - oracle.half_ordered(exact)).abs()
-    # Within one FP16 ulp of the derivative of the exact sum, or within the FP32 sum's own
-    # error (2e-3 relative Frobenius) where the derivative is steep.
-    assert (distance <= 1).float().mean().item() > 0.999
-    assert rel_error(grad, want_grad) <= 2e-3
-
-    # Backward: dy @ w2 times the saved factor against the reference pair's result.
-    g = torch.Generator().manual_seed(13)
-    dy = torch.randn(m, k, generator=g).half()
-    w2 = (torch.randn(k, n, generator=g) * 0.05).half()
-    got = torch.zeros(m, n, dtype=torch.half, device=DEV)
-    flint.gemm_nn_scaled(got, dy.to(DEV), w2.to(DEV), grad, m, n, k)
-    ref = torch.zeros_like(got)
-    flint.gemm_nn_dgelu(ref, dy.to(DEV), w2.to(DEV), pre, m, n, k)
-    no_fault(flint)
-    want = oracle.gemm_nn(dy, w2) * want_grad
-    assert rel_error(got, want) <= 2e-3
-    assert rel_error(ref, want) <= 2e-3
-    assert rel_error(got, ref.double().cpu()) <= 1.5e-3
-    # A factor of exactly 1 leaves the plain product's bits.
-    ones = torch.ones(m, n, dtype=torch.half, device=DEV)
-    plain = torch.zeros_like(got)
-    flint.gemm_nn(plain, dy.to(DEV), w2.to(DEV), m, n, k)
-    flint.gemm_nn_scaled(got, dy.to(DEV), w2.to(DEV), ones, m, n, k)
-    no_fault(flint)
-    assert torch.equal(got.view(torch.int16), plain.view(torch.int16))
-
-
-def test_gelu_grad_pair_argument_errors(flint):
-    a = torch.zeros(64, 64, dtype=torch.half, device=DEV)
-    b = torch.zeros(64, 64, dtype=torch.half, device=DEV)
-    c = torch.zeros(64, 64, dtype=torch.half, device=DEV)
-    bias = torch.zeros(64, device=DEV)
-    for call, text in [
-        (lambda: flint.gemm_nt_bias_gelu_grad(c, None, a, b, bias, 8, 8, 8), "grad is null"),
-        (lambda: flint.gemm_nt_bias_gelu_grad(c, a, a, b, bias, 8, 8, 8), "grad and x overlap"),
-        (lambda: flint.gemm_nt_bias_gelu_grad(c, c, a, b, bias, 8, 8, 8), "y and grad overlap"),
-        (lambda: flint.gemm_nn_scaled(c, a, b, None, 8, 8, 8), "factor is null"),
-        (lambda: flint.gemm_nn_scaled(c, a, b, a, 8, 12, 8), "n (12) must be a multiple of 8"),
-    ]:
-        with pytest.raises(flint_b200.FlintError) as error:
-            call()
-        assert text in str(error.value), (text, str(error.value))
-    flint.gemm_nn_scaled(None, None, None, None, 0, 8, 8)
