@@ -146,6 +146,9 @@ _C_TYPES = {
     "int**": ctypes.POINTER(ctypes.c_void_p),
     "double**": ctypes.POINTER(ctypes.c_void_p),
     "const void* const*": ctypes.POINTER(ctypes.c_void_p),
+    "flint_b200_generator*": ctypes.c_void_p,
+    "const flint_b200_generator*": ctypes.c_void_p,
+    "flint_b200_generator**": ctypes.POINTER(ctypes.c_void_p),
     "flint_trainer*": ctypes.c_void_p,
     "const flint_trainer*": ctypes.c_void_p,
     "flint_trainer**": ctypes.POINTER(ctypes.c_void_p),

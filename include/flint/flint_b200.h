@@ -153,6 +153,57 @@ FLINT_API flint_status flint_b200_bias_gradient_static(void* dbias, const void* 
                                                        size_t cols, int accumulate,
                                                        flint_stream stream);
 
+/* ---- decoding with a KV cache (the reference's inference milestone, README.md:148; it has
+ * no code for it, so nothing here has a counterpart in its header) ----
+ *
+ * A generator decodes with the weights of `model` (whose FP16 copies must be in
+ * sync): `sequences` sequences (1..64) side by side, each up to `max_length`
+ * positions (a multiple of 8, at most min(block_size, 1024)). It owns the cache
+ * [layer][K|V][sequence][head][position][64] in FP16 and its scratch; with
+ * int8_weights it also owns an int8 copy of every matrix with one FP32 scale per
+ * output row (w[n, :] ~ q[n, :] * scale[n], q = round(w / scale), scale = max|w| / 127),
+ * halving the bytes a decode step reads. Heads must be 64 wide. */
+typedef struct flint_b200_generator flint_b200_generator;
+
+FLINT_API flint_status flint_b200_generator_create(const flint_gpt2* model, size_t sequences,
+                                                   size_t max_length, int int8_weights,
+                                                   flint_b200_generator** generator);
+FLINT_API void flint_b200_generator_destroy(flint_b200_generator* generator);
+
+/* Re-derives the int8 copies after the model's weights changed. */
+FLINT_API flint_status flint_b200_generator_refresh(flint_b200_generator* generator,
+                                                    flint_stream stream);
+
+/* Starts over: tokens is uint16 [sequences, length], length a multiple of 8 up
+ * to max_length. Runs the prompt through the tensor-core GEMMs and the fused
+ * causal attention kernel, stores every position's keys and values in the
+ * cache and leaves the logits of each sequence's last position. */
+FLINT_API flint_status flint_b200_generator_prefill(flint_b200_generator* generator,
+                                                    const void* tokens, size_t length,
+                                                    flint_stream stream);
+
+/* Appends one token per sequence (uint16 [sequences]) at the next position:
+ * leaves its logits and writes each sequence's most likely next token (lowest
+ * index among equals, padded columns excluded) to next_tokens (uint16
+ * [sequences] on the device; null keeps it internal). With use_graph non-zero
+ * the step's launches are captured into a CUDA graph on the first call and
+ * replayed afterwards (the position lives in device memory); tokens and
+ * next_tokens must then be the same buffers on every call. */
+FLINT_API flint_status flint_b200_generator_step(flint_b200_generator* generator,
+                                                 const void* tokens, void* next_tokens,
+                                                 int use_graph, flint_stream stream);
+
+/* FP32 logits [sequences, padded_vocab] of the last position processed, and how
+ * many positions each sequence holds. */
+FLINT_API flint_status flint_b200_generator_logits(const flint_b200_generator* generator,
+                                                   const void** logits, size_t* position);
+
+/* Bytes the next decode step must read from HBM: the weights (each matrix once;
+ * the output layer once per group of eight sequences) and the cache. */
+FLINT_API flint_status flint_b200_generator_bytes_per_step(const flint_b200_generator* generator,
+                                                           size_t* weight_bytes,
+                                                           size_t* cache_bytes);
+
 /* Sets *found_nonfinite (device int) to 1 if any of the count FP32 values is
  * inf or NaN; leaves it unchanged otherwise, so several calls can share it.
  * When sum_squares (device double, may be null) is given, adds the sum of

@@ -495,11 +495,9 @@ def gpt2_round_to_half(params):
     return {k: v.half().float() for k, v in params.items()}
 
 
-def gpt2_logits(cfg, params, idx, dtype=torch.float32):
-    """Logits [batch * length, vocab_size] (padded columns dropped) of the model on idx
-    [batch, length] (int64), with explicit causal-softmax attention; differentiable in
-    params."""
-    p = {k: v.to(dtype) for k, v in params.items()} if dtype != torch.float32 else params
+def _gpt2_hidden(cfg, p, idx):
+    """The final LayerNorm's output [batch, length, width] of the model on idx [batch, length]
+    (int64), with explicit causal-softmax attention; differentiable in the parameters."""
     batch, length = idx.shape
     w, h = cfg["n_embd"], cfg["n_head"]
     hw = w // h
@@ -517,8 +515,15 @@ def gpt2_logits(cfg, params, idx, dtype=torch.float32):
         y = torch.nn.functional.layer_norm(x, (w,), p[b + "ln_2.weight"], p[b + "ln_2.bias"], 1e-5)
         y = gelu_tanh(torch.nn.functional.linear(y, p[b + "mlp.c_fc.weight"], p[b + "mlp.c_fc.bias"]))
         x = x + torch.nn.functional.linear(y, p[b + "mlp.c_proj.weight"], p[b + "mlp.c_proj.bias"])
-    x = torch.nn.functional.layer_norm(x, (w,), p["ln_f.weight"], p["ln_f.bias"], 1e-5)
-    return torch.nn.functional.linear(x.reshape(-1, w), p["wte.weight"])[:, :cfg["vocab_size"]]
+    return torch.nn.functional.layer_norm(x, (w,), p["ln_f.weight"], p["ln_f.bias"], 1e-5)
+
+
+def gpt2_logits(cfg, params, idx, dtype=torch.float32):
+    """Logits [batch * length, vocab_size] (padded columns dropped) of the model on idx
+    [batch, length] (int64); differentiable in params."""
+    p = {k: v.to(dtype) for k, v in params.items()} if dtype != torch.float32 else params
+    x = _gpt2_hidden(cfg, p, idx)
+    return torch.nn.functional.linear(x.reshape(-1, cfg["n_embd"]), p["wte.weight"])[:, :cfg["vocab_size"]]
 
 
 def gpt2_loss(cfg, params, idx, targets, dtype=torch.float32):
@@ -592,3 +597,49 @@ def synthetic_tokens(sequences, length, vocab, seed):
     gen = torch.Generator("cpu").manual_seed(seed)
     ids = torch.randint(0, vocab, (sequences * length + 1,), generator=gen)
     return ids[:-1].view(sequences, length), ids[1:].view(sequences, length)
+
+
+# ---------------------------------------------------------------------------------------
+# Decoding (the reference's inference milestone, README.md:148, has no code; the model is
+# scripts/gpt2_torch.py's, so the logits of a position must be the full model's logits there)
+# ---------------------------------------------------------------------------------------
+
+def int8_rows(w):
+    """Per-row symmetric int8 quantisation as the decoder applies it to the FP16 weights:
+    scale = max|w[n, :]| / 127 (1 for an all-zero row) computed in float32, q = round-half-even
+    (w / scale) clamped to [-127, 127]. Returns (q int8, scale float32, q * scale float32)."""
+    w = torch.as_tensor(np.asarray(w)).to(torch.float16).float()
+    top = w.abs().amax(1)
+    scale = torch.where(top > 0, top / 127.0, torch.ones_like(top))
+    inverse = (1.0 / scale)[:, None]
+    q = torch.clamp(torch.round(w * inverse), -127, 127).to(torch.int8)
+    return q, scale, q.float() * scale[:, None]
+
+
+def decoder_weights(params, int8=False):
+    """The weights a decoder computes with: every matrix rounded to FP16 (its compute copy),
+    and with int8 replaced by its int8 approximation; the FP32 tables, biases and LayerNorm
+    parameters as they are. The embedding lookup reads the FP32 table; the output layer the
+    matrix copy."""
+    out = {}
+    for name, p in params.items():
+        if p.dim() == 2 and name != "wpe.weight":
+            half = p.half().float()
+            out[name] = int8_rows(half)[2] if int8 else half
+        else:
+            out[name] = p
+    return out
+
+
+def gpt2_decode_logits(cfg, params, tokens, int8=False):
+    """Logits [batch, length, vocab_size] of every position for tokens [batch, length], from
+    the model with the decoder's weights (the token table stays FP32 for the lookup)."""
+    weights = decoder_weights(params, int8)
+    lookup = dict(weights)
+    lookup["wte.weight"] = params["wte.weight"]
+    batch, length = tokens.shape
+    w = cfg["n_embd"]
+    # gpt2_logits with two tables: the FP32 one for the embedding, the matrix copy for the head.
+    hidden = _gpt2_hidden(cfg, lookup, tokens)
+    logits = torch.nn.functional.linear(hidden.reshape(-1, w), weights["wte.weight"])
+    return logits[:, :cfg["vocab_size"]].view(batch, length, -1)
