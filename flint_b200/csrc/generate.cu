@@ -310,36 +310,49 @@ __global__ void __launch_bounds__(256)
     }
 }
 
-// One query per (sequence, head) against the cache's positions 0 .. *position (the new
-// token's own key and value were stored before the call).
-__global__ void __launch_bounds__(256)
+// One query per (sequence, head) against the cache's positions 0 .. *position. The new
+// token's own key and value come straight from its qkv row; the CTA also stores them in the
+// cache for the steps to come (no other CTA reads that position during this launch).
+constexpr int kDecodeThreads = 512;
+
+__global__ void __launch_bounds__(kDecodeThreads)
     fb_decode_attention(__half* __restrict__ out, const __half* __restrict__ qkv,
-                        const __half* __restrict__ cache_k, const __half* __restrict__ cache_v,
+                        __half* __restrict__ cache_k, __half* __restrict__ cache_v,
                         const int* __restrict__ position, int heads, int max_length, float scale) {
     extern __shared__ float scores[];      // [max_length]
-    constexpr int kThreads = 256;
-    constexpr int kGroups = kThreads / 8;
+    constexpr int kGroups = kDecodeThreads / 8;
     __shared__ float q[kHeadWidth];
-    __shared__ float red[kThreads / 32];
+    __shared__ float red[kDecodeThreads / 32];
     __shared__ float partial[kGroups][kHeadWidth];
     const int head = blockIdx.x % heads;
     const int sequence = blockIdx.x / heads;
     const int width = heads * kHeadWidth;
-    const int length = *position + 1;
+    const int newest = *position;
+    const int length = newest + 1;
     const int tid = threadIdx.x;
     const int lane = tid % 32;
     const int warp = tid / 32;
+    const __half* row_q = qkv + static_cast<size_t>(sequence) * 3 * width + head * kHeadWidth;
+    const __half* new_k = row_q + width;
+    const __half* new_v = row_q + 2 * width;
+    __half* keys = cache_k + (static_cast<size_t>(sequence) * heads + head) * max_length * kHeadWidth;
+    __half* values = cache_v + (static_cast<size_t>(sequence) * heads + head) * max_length * kHeadWidth;
     if (tid < kHeadWidth) {
-        q[tid] = __half2float(qkv[static_cast<size_t>(sequence) * 3 * width + head * kHeadWidth + tid]) *
-                 scale * kLog2e;
+        q[tid] = __half2float(row_q[tid]) * scale * kLog2e;
+    } else if (tid < kHeadWidth + 8) {
+        const int piece = tid - kHeadWidth;
+        reinterpret_cast<uint4*>(keys + static_cast<size_t>(newest) * kHeadWidth)[piece] =
+            reinterpret_cast<const uint4*>(new_k)[piece];
+    } else if (tid < kHeadWidth + 16) {
+        const int piece = tid - kHeadWidth - 8;
+        reinterpret_cast<uint4*>(values + static_cast<size_t>(newest) * kHeadWidth)[piece] =
+            reinterpret_cast<const uint4*>(new_v)[piece];
     }
     __syncthreads();
-    const __half* keys = cache_k + (static_cast<size_t>(sequence) * heads + head) * max_length * kHeadWidth;
-    const __half* values = cache_v + (static_cast<size_t>(sequence) * heads + head) * max_length * kHeadWidth;
     float top = -INFINITY;
-#pragma unroll 2
-    for (int t = tid; t < length; t += kThreads) {
-        const uint4* row = reinterpret_cast<const uint4*>(keys + static_cast<size_t>(t) * kHeadWidth);
+    for (int t = tid; t < length; t += kDecodeThreads) {
+        const uint4* row = reinterpret_cast<const uint4*>(
+            t == newest ? new_k : keys + static_cast<size_t>(t) * kHeadWidth);
         uint4 raw[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -365,12 +378,12 @@ __global__ void __launch_bounds__(256)
     __syncthreads();
     top = red[0];
 #pragma unroll
-    for (int i = 1; i < kThreads / 32; ++i) {
+    for (int i = 1; i < kDecodeThreads / 32; ++i) {
         top = fmaxf(top, red[i]);
     }
     __syncthreads();
     float sum = 0.0f;
-    for (int t = tid; t < length; t += kThreads) {
+    for (int t = tid; t < length; t += kDecodeThreads) {
         const float p = exp2f(scores[t] - top);
         scores[t] = p;
         sum += p;
@@ -382,17 +395,17 @@ __global__ void __launch_bounds__(256)
     __syncthreads();
     sum = red[0];
 #pragma unroll
-    for (int i = 1; i < kThreads / 32; ++i) {
+    for (int i = 1; i < kDecodeThreads / 32; ++i) {
         sum += red[i];
     }
-    // Thread (group, piece): positions group, group + 32, ...; eight output columns.
+    // Thread (group, piece): positions group, group + 64, ...; eight output columns.
     const int piece = tid % 8;
     const int group = tid / 8;
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#pragma unroll 4
+#pragma unroll 8
     for (int t = group; t < length; t += kGroups) {
-        const uint4 raw = load_streaming(
-            reinterpret_cast<const uint4*>(values + static_cast<size_t>(t) * kHeadWidth) + piece);
+        const __half* row = t == newest ? new_v : values + static_cast<size_t>(t) * kHeadWidth;
+        const uint4 raw = load_streaming(reinterpret_cast<const uint4*>(row) + piece);
         float v[8];
         fb::unpack8(v, raw);
         const float p = scores[t];
@@ -408,7 +421,7 @@ __global__ void __launch_bounds__(256)
     __syncthreads();
     if (tid < kHeadWidth) {
         float total = 0.0f;
-#pragma unroll
+#pragma unroll 8
         for (int g2 = 0; g2 < kGroups; ++g2) {
             total += partial[g2][tid];
         }
@@ -637,18 +650,19 @@ flint_status run_blocks(flint_b200_generator& g, size_t count, bool decode, cuda
         const Layer& l = g.blocks[i];
         FB_TRY(layernorm(g, l.ln1_w, l.ln1_b, x, rows, stream));
         FB_TRY(linear<Act::kNone>(g, l.attn, g.qkv, g.h, nullptr, rows, decode, stream));
-        fb_cache_store<<<static_cast<unsigned>(rows), 256, 0, stream>>>(
-            g.keys(i), g.values(i), g.qkv, decode ? g.position : nullptr,
-            static_cast<int>(g.host_position), static_cast<int>(count), static_cast<int>(g.heads),
-            static_cast<int>(g.max_length));
-        FB_CUDA(fb::after_launch());
         if (decode) {
+            // (The kernel also stores the new token's key and value in the cache.)
             const int smem = static_cast<int>(g.max_length * sizeof(float));
-            fb_decode_attention<<<static_cast<unsigned>(g.sequences * g.heads), 256, smem, stream>>>(
+            fb_decode_attention<<<static_cast<unsigned>(g.sequences * g.heads), kDecodeThreads, smem,
+                                  stream>>>(
                 g.attn, g.qkv, g.keys(i), g.values(i), g.position, static_cast<int>(g.heads),
                 static_cast<int>(g.max_length), scale);
             FB_CUDA(fb::after_launch());
         } else {
+            fb_cache_store<<<static_cast<unsigned>(rows), 256, 0, stream>>>(
+                g.keys(i), g.values(i), g.qkv, nullptr, static_cast<int>(g.host_position),
+                static_cast<int>(count), static_cast<int>(g.heads), static_cast<int>(g.max_length));
+            FB_CUDA(fb::after_launch());
             const size_t w3 = 3 * g.width;
             auto view = [&](const void* base, size_t first, size_t row_width) {
                 return fb::AttentionView{static_cast<const __half*>(base) + first,
