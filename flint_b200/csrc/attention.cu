@@ -7,9 +7,11 @@
 // tensor memory), each working on 128 x 128 (query x key) tiles:
 //   forward   one CTA per (head, 128 queries): S = Q K^T into TMEM, online
 //             softmax in registers, P (FP16) back to shared memory in the
-//             operand layout, O_block = P V into TMEM, running rescale of O in
-//             registers; two CTAs share an SM so one's softmax overlaps the
-//             other's MMAs
+//             operand layout, O += P V accumulated in TMEM over the row of key
+//             tiles; the exponent the probabilities are taken against moves only
+//             when a tile's maximum exceeds it by more than 2^8, and only then
+//             is O read back, rescaled and rewritten; two CTAs share an SM so
+//             one's softmax overlaps the other's MMAs
 //   dK/dV     one CTA per (head, 128 keys), looping over the query tiles at or
 //             below the diagonal: S and dP = dO V^T recomputed, P and dS written
 //             to shared memory, dV += P^T dO and dK += dS^T Q accumulated in TMEM
@@ -92,29 +94,21 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// How far (in base-2 exponent units) a tile's maximum may exceed the reference exponent
+// before the forward kernel moves the reference and rescales its accumulator:
+// probabilities then stay below 2^8, well inside FP16.
+constexpr float kLazyShift = 8.0f;
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
 // Named barrier between the two warps that share a TMEM lane quadrant (the two
 // halves of the same 32 rows); barrier 0 is __syncthreads, 1..4 are the quadrants'.
 __device__ __forceinline__ void quadrant_sync(int quadrant) {
     asm volatile("bar.sync %0, 64;" ::"r"(quadrant + 1) : "memory");
-}
-
-// Writes 32 FP16 values (columns [col, col+32) of row `row`) of a 128 x 128
-// tile into the two-panel, 128-byte-swizzled operand layout.
-__device__ __forceinline__ void store_operand_row(uint32_t tile_base, int row, int col,
-                                                  const float (&v)[32]) {
-    const uint32_t panel = tile_base + (col >> 6) * kPanelBytes + row * 128;
-    const int first_chunk = (col & 63) >> 3;
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-        const uint32_t at = panel + (((first_chunk + c) ^ (row & 7)) << 4);
-        const unsigned w0 = fb::pack2(v[8 * c], v[8 * c + 1]);
-        const unsigned w1 = fb::pack2(v[8 * c + 2], v[8 * c + 3]);
-        const unsigned w2 = fb::pack2(v[8 * c + 4], v[8 * c + 5]);
-        const unsigned w3 = fb::pack2(v[8 * c + 6], v[8 * c + 7]);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(at), "r"(w0), "r"(w1),
-                     "r"(w2), "r"(w3)
-                     : "memory");
-    }
 }
 
 // Descriptors for the three ways a tile is read.
@@ -185,7 +179,7 @@ __global__ void __launch_bounds__(kFwdThreads, 2)
         abort_flag = 0;
         sm100::mbar_init(q_full, 1);
         sm100::mbar_init(s_full, 1);
-        sm100::mbar_init(p_ready, 256);
+        sm100::mbar_init(p_ready, 8);   // one arrival per softmax warp
         sm100::mbar_init(o_full, 1);
         for (int s = 0; s < 3; ++s) {
             sm100::mbar_init(slot_full(s), 1);
@@ -270,28 +264,30 @@ __global__ void __launch_bounds__(kFwdThreads, 2)
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
                     sm100::mma_f16_ss(tmem_o, desc_kmajor_wide(p_tile, ks),
-                                      desc_mnmajor(v_tile, ks, 16), kIdescPV, ks > 0);
+                                      desc_mnmajor(v_tile, ks, 16), kIdescPV, j > 0 || ks > 0);
                 }
                 sm100::mma_commit(slot_empty(vslot));
-                sm100::mma_commit(o_full);
+                if (j == qb) {
+                    sm100::mma_commit(o_full);
+                }
             }
         }
     } else {
         // Two threads per query row: this one owns score columns [64 half, 64 half + 64)
-        // and output columns [32 half, 32 half + 32).
+        // and output columns [32 half, 32 half + 32). The output tile accumulates in tensor
+        // memory over the whole row of key tiles; the running maximum that the
+        // probabilities are taken against only moves when a tile exceeds it by more than
+        // 2^kLazyShift, and only then is the accumulator read, rescaled and written back.
         const int quadrant = warp % 4;
         const int half = (warp - 2) / 4;
         const int row = quadrant * 32 + lane;
         const int q_index = qb * kTile + row;
         const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
         const float scale2 = p.scale * kLog2e;
-        float m = -INFINITY;   // running row maximum (base-2 exponent units), shared by the pair
-        float l = 0.0f;        // this thread's share of the row sum
-        float o[32];
-#pragma unroll
-        for (int d = 0; d < 32; ++d) {
-            o[d] = 0.0f;
-        }
+        const fb::F2 scale_pair = fb::f2_pack(scale2, scale2);
+        const uint32_t p_row = p_tile + half * kPanelBytes + row * 128;
+        float m = -INFINITY;        // reference exponent of the row (base 2), shared by the pair
+        fb::F2 l = 0;               // this thread's share of the row sum, in two partial sums
         bool ok = true;
         for (int j = 0; ok && j <= qb; ++j) {
             if (!sm100::mbar_wait(s_full, j & 1, abort)) {
@@ -299,78 +295,118 @@ __global__ void __launch_bounds__(kFwdThreads, 2)
                 break;
             }
             sm100::tc_fence_after_sync();
-            const bool diagonal = j == qb;
-            float local = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-                const int col = half * 64 + c * 32;
-                uint32_t raw[32];
-                sm100::tmem_ld_32x32(tmem_s + lane_base + col, raw);
-                sm100::tmem_ld_wait();
-                if (diagonal) {
+            uint32_t raw[64];
+            sm100::tmem_ld_32x32(tmem_s + lane_base + half * 64,
+                                 reinterpret_cast<uint32_t(&)[32]>(raw[0]));
+            sm100::tmem_ld_32x32(tmem_s + lane_base + half * 64 + 32,
+                                 reinterpret_cast<uint32_t(&)[32]>(raw[32]));
+            sm100::tmem_ld_wait();
+            if (j == qb) {
+                // The diagonal tile: keys after the query count as minus infinity.
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const float t = __uint_as_float(raw[i]) * scale2;
-                        local = (col + i <= row) ? fmaxf(local, t) : local;
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        local = fmaxf(local, __uint_as_float(raw[i]) * scale2);
-                    }
+                for (int i = 0; i < 64; ++i) {
+                    raw[i] = (half * 64 + i <= row) ? raw[i] : 0xff800000u;
                 }
             }
+            float top[4];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                top[t] = max3(__uint_as_float(raw[t]), __uint_as_float(raw[4 + t]),
+                              __uint_as_float(raw[8 + t]));
+            }
+#pragma unroll
+            for (int i = 12; i < 60; i += 8) {
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    top[t] = max3(top[t], __uint_as_float(raw[i + t]), __uint_as_float(raw[i + 4 + t]));
+                }
+            }
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                top[t] = fmaxf(top[t], __uint_as_float(raw[60 + t]));
+            }
+            // The scale is positive, so the maximum may be scaled after it is taken.
+            const float local = fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3])) * scale2;
             pair_max[j & 1][half][row] = local;
             quadrant_sync(quadrant);
             const float mx = fmaxf(m, fmaxf(local, pair_max[j & 1][half ^ 1][row]));
-            const float alpha = fast_exp2(m - mx);
-            l *= alpha;
-#pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-                const int col = half * 64 + c * 32;
-                uint32_t raw[32];
-                sm100::tmem_ld_32x32(tmem_s + lane_base + col, raw);
-                sm100::tmem_ld_wait();
-                float v[32];
-                if (diagonal) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const float e = fast_exp2(fmaf(__uint_as_float(raw[i]), scale2, -mx));
-                        v[i] = (col + i <= row) ? e : 0.0f;
-                        l += v[i];
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        v[i] = fast_exp2(fmaf(__uint_as_float(raw[i]), scale2, -mx));
-                        l += v[i];
-                    }
-                }
-                store_operand_row(p_tile, row, col, v);
+            const bool moved = mx - m > kLazyShift;   // always on the first tile (m = -inf)
+            float alpha = 1.0f;
+            if (moved) {
+                alpha = fast_exp2(m - mx);
+                m = mx;
+                l = fb::f2_mul(l, fb::f2_pack(alpha, alpha));
             }
-            m = mx;
+            if (j > 0 && __any_sync(0xffffffffu, moved)) {
+                // The previous tile's P V has finished: the score commit that was just waited
+                // for covers every earlier MMA of the issuing thread.
+                const fb::F2 a2 = fb::f2_pack(alpha, alpha);
+#pragma unroll 1
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t acc[16];
+                    const uint32_t at = tmem_o + lane_base + half * 32 + c * 16;
+                    sm100::tmem_ld_32x16(at, acc);
+                    sm100::tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 16; i += 2) {
+                        float lo, hi;
+                        fb::f2_unpack(fb::f2_mul(fb::f2_pack(__uint_as_float(acc[i]),
+                                                             __uint_as_float(acc[i + 1])), a2), lo, hi);
+                        acc[i] = __float_as_uint(lo);
+                        acc[i + 1] = __float_as_uint(hi);
+                    }
+                    sm100::tmem_st_32x16(at, acc);
+                }
+                sm100::tmem_st_wait();
+            }
+            const fb::F2 shift = fb::f2_pack(-m, -m);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                unsigned w[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float lo, hi;
+                    fb::f2_unpack(fb::f2_fma(fb::f2_pack(__uint_as_float(raw[8 * c + 2 * i]),
+                                                         __uint_as_float(raw[8 * c + 2 * i + 1])),
+                                             scale_pair, shift), lo, hi);
+                    lo = fast_exp2(lo);
+                    hi = fast_exp2(hi);
+                    l = fb::f2_add(l, fb::f2_pack(lo, hi));
+                    w[i] = fb::pack2(lo, hi);
+                }
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(
+                                 p_row + ((c ^ (row & 7)) << 4)), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+                             "r"(w[3])
+                             : "memory");
+            }
             fence_async_shared();
             sm100::tc_fence_before_sync();
-            sm100::mbar_arrive(p_ready);
-
-            if (!sm100::mbar_wait(o_full, j & 1, abort)) {
-                ok = false;
-                break;
+            __syncwarp();
+            if (lane == 0) {
+                sm100::mbar_arrive(p_ready);
             }
-            sm100::tc_fence_after_sync();
-            uint32_t raw[32];
-            sm100::tmem_ld_32x32(tmem_o + lane_base + half * 32, raw);
+        }
+        if (ok && !sm100::mbar_wait(o_full, 0, abort)) {
+            ok = false;
+        }
+        sm100::tc_fence_after_sync();
+        float o[32];
+        {
+            uint32_t acc[32];
+            sm100::tmem_ld_32x32(tmem_o + lane_base + half * 32, acc);
             sm100::tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-                o[i] = fmaf(o[i], alpha, __uint_as_float(raw[i]));
+                o[i] = __uint_as_float(acc[i]);
             }
-            sm100::tc_fence_before_sync();
         }
+        float l_lo, l_hi;
+        fb::f2_unpack(l, l_lo, l_hi);
+        const float mine = l_lo + l_hi;
         // The row sum is the two threads' shares added together.
-        pair_max[0][half][row] = l;
+        pair_max[0][half][row] = mine;
         quadrant_sync(quadrant);
-        const float total = l + pair_max[0][half ^ 1][row];
+        const float total = mine + pair_max[0][half ^ 1][row];
         if (ok && q_index < p.length) {
             const float inv = 1.0f / total;
             __half* out = static_cast<__half*>(p.out0) + seq * p.out_seq + head * p.out_head +
@@ -1294,8 +1330,9 @@ flint_status check_attention_dims(const char* name, size_t batches, size_t lengt
     if (batches > 65535) {
         return fb::fail(kBad, "%s: batches (%zu) can be up to 65535", name, batches);
     }
-    if (!std::isfinite(scale)) {
-        return fb::fail(kBad, "%s: scale (%g) must be finite", name, static_cast<double>(scale));
+    if (!std::isfinite(scale) || scale <= 0.0f) {
+        return fb::fail(kBad, "%s: scale (%g) must be finite and positive", name,
+                        static_cast<double>(scale));
     }
     return FLINT_OK;
 }

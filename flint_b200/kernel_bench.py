@@ -32,7 +32,9 @@ Each case prints one JSON object: microseconds per call (median over rounds, min
 TFLOP/s or GB/s from the algorithmic work, the fraction of the nominal peak (2,250 TFLOP/s
 dense FP16; 8,000 GB/s) and of the peak measured on this pool (MEASURED_PEAKS.json: cuBLAS
 burst, copy bandwidth), the baseline's figures, flint's speed relative to the baseline, the
-median SM clock sampled while the case ran, and whether the two arms' outputs agree.
+median SM clock sampled while the case ran, whether the two arms' outputs agree, and for the
+bandwidth-bound kernels the time a plain copy of the same number of bytes takes (kernels of
+10 us are bound by launch and ramp-up: a 33 MB copy reaches about 0.6 of the peak itself).
 ``--once`` makes one call per kernel and prints nothing but a completion line: the form to
 run under a profiler, with ``--rows`` reduced so that a capture stays small.
 """
@@ -156,7 +158,7 @@ def warm(fn, sets, seconds):
     return time_calls(fn, sets, calls)
 
 
-def run_case(case: Case, protocol: Protocol, clocks: Clocks, peaks) -> dict:
+def run_case(case: Case, protocol: Protocol, clocks: Clocks, peaks, copy_reference=None) -> dict:
     arms = {"flint": case.flint}
     if case.baseline is not None:
         arms["baseline"] = case.baseline
@@ -198,6 +200,12 @@ def run_case(case: Case, protocol: Protocol, clocks: Clocks, peaks) -> dict:
         ratios = [b / f for f, b in zip(samples["flint"], samples["baseline"])]
         out["flint_over_baseline"] = {"median": round(statistics.median(ratios), 4),
                                       "min": round(min(ratios), 4), "max": round(max(ratios), 4)}
+    if case.unit == "GB/s" and copy_reference is not None:
+        # What a plain copy moving the same number of bytes achieves at this size: small kernels
+        # are bound by launch and ramp-up, not by the memory system, and this shows by how much.
+        copy_us = copy_reference(case.work)
+        out["copy_same_bytes_us"] = round(copy_us, 2)
+        out["flint_over_copy"] = round(copy_us / out["flint"]["us"], 4)
     if failed:
         out["baseline_error"] = failed.get("baseline")
     if case.note:
@@ -208,6 +216,28 @@ def run_case(case: Case, protocol: Protocol, clocks: Clocks, peaks) -> dict:
         except Exception as error:
             out["outputs_rel_l2"] = f"{type(error).__name__}: {str(error).splitlines()[0][:120]}"
     return out
+
+
+class CopyReference:
+    """Times flint_copy moving `bytes_moved` bytes (half read, half written) over rotating
+    buffers larger than four times the L2, with the protocol's sample length; cached per size."""
+
+    def __init__(self, flint: Flint, protocol: Protocol):
+        self.flint, self.protocol, self.cache = flint, protocol, {}
+
+    def __call__(self, bytes_moved: float) -> float:
+        size = max(16, int(bytes_moved / 2) // 16 * 16)
+        if size not in self.cache:
+            sets = rotation_sets(2.0 * size, False)
+            src = [torch.empty(size, dtype=torch.uint8, device=DEV) for _ in range(sets)]
+            dst = [torch.empty(size, dtype=torch.uint8, device=DEV) for _ in range(sets)]
+            fn = lambda i: self.flint.copy(dst[i], src[i], size)  # noqa: E731
+            estimate = warm(fn, sets, min(self.protocol.warmup_s, 0.2))
+            samples = [time_calls(fn, sets, int(max(3, self.protocol.sample_ms / estimate)), first=r)
+                       for r in range(self.protocol.rounds)]
+            self.cache[size] = statistics.median(samples) * 1e3
+            del src, dst
+        return self.cache[size]
 
 
 # ---- operand helpers ---------------------------------------------------------------------------
@@ -660,17 +690,19 @@ def cpu_timings(rows: int, budget_s: float = 60.0):
 
 
 def table(results) -> str:
-    lines = ["| case | flint us | rate | of nominal | of measured | baseline us | flint / baseline | SM MHz |",
-             "| --- | ---: | ---: | ---: | ---: | ---: | ---: | ---: |"]
+    lines = ["| case | flint us | rate | of nominal | of measured | baseline us | flint / baseline | "
+             "same-bytes copy us | SM MHz |",
+             "| --- | ---: | ---: | ---: | ---: | ---: | ---: | ---: | ---: |"]
     for r in results:
         if r.get("group") == "cpu":
-            lines.append(f"| CPU: {r['case']} | {r['us']} | {r['rate']} {r['unit']} | | | | | |")
+            lines.append(f"| CPU: {r['case']} | {r['us']} | {r['rate']} {r['unit']} | | | | | | |")
             continue
         fl, base, ratio = r["flint"], r["baseline"], r["flint_over_baseline"]
         lines.append(
             f"| {r['case']} | {fl['us']} | {fl['rate']} {r['unit']} | {fl['frac_nominal']:.3f} | "
             f"{fl['frac_measured']:.3f} | {base['us'] if base else '-'} | "
-            f"{ratio['median'] if ratio else '-'} | {r['sm_mhz_median'] or '-'} |")
+            f"{ratio['median'] if ratio else '-'} | {r.get('copy_same_bytes_us', '-')} | "
+            f"{r['sm_mhz_median'] or '-'} |")
     return "\n".join(lines)
 
 
@@ -681,6 +713,7 @@ def run(flint: Flint, groups, rows: int, quick: bool, once: bool = False, sigma_
     protocol = Protocol(quick)
     clocks = Clocks(torch.cuda.current_device())
     peaks = measured_peaks()
+    copy_reference = None if once else CopyReference(flint, protocol)
     results = []
     for name in groups:
         builder = GROUPS[name]
@@ -691,7 +724,7 @@ def run(flint: Flint, groups, rows: int, quick: bool, once: bool = False, sigma_
                 torch.cuda.synchronize()
                 print(f"{case.name}: done", flush=True)
                 continue
-            result = run_case(case, protocol, clocks, peaks)
+            result = run_case(case, protocol, clocks, peaks, copy_reference)
             results.append(result)
             if emit is not None:
                 emit(result)

@@ -28,7 +28,7 @@ FLINT_API flint_status flint_b200_launch_count(unsigned long long* launches);
  * (sequence, head) pairs, all FP16 [batches, length, head_width] contiguous;
  * lse[batches, length] FP32 receives log-sum-exp of the scaled scores (natural
  * log), which the backward pass needs. head_width must be 64, length a
- * multiple of 8 up to 1,024. */
+ * multiple of 8 up to 1,024, scale finite and positive. */
 FLINT_API flint_status flint_b200_attention_forward(void* o, void* lse, const void* q,
                                                     const void* k, const void* v, size_t batches,
                                                     size_t length, size_t head_width, float scale,
