@@ -4,18 +4,19 @@
 //
 // Three kernels, all warp-specialised like the GEMM (warp 0 = TMA producer,
 // warp 1 = tcgen05.mma issuer, the rest compute on accumulators read from
-// tensor memory), each working on 128 x 128 (query x key) tiles:
-//   forward   one CTA per (head, 128 queries): S = Q K^T into TMEM, online
-//             softmax in registers, P (FP16) back to shared memory in the
-//             operand layout, O += P V accumulated in TMEM over the row of key
-//             tiles; the exponent the probabilities are taken against moves only
-//             when a tile's maximum exceeds it by more than 2^8, and only then
-//             is O read back, rescaled and rewritten; two CTAs share an SM so
-//             one's softmax overlaps the other's MMAs
-//   dK/dV     one CTA per (head, 128 keys), looping over the query tiles at or
-//             below the diagonal: S and dP = dO V^T recomputed, P and dS written
-//             to shared memory, dV += P^T dO and dK += dS^T Q accumulated in TMEM
-//   dQ        one CTA per (head, 128 queries), looping over key tiles:
+// tensor memory), all persistent (one CTA per SM over a work-ordered item list):
+//   forward   items of (head, two adjacent 128-query tiles) sharing the K and V
+//             tiles that stream through a ring: S = Q K^T into TMEM, base-2
+//             softmax in registers, P written back over S as FP16 pairs and read
+//             from tensor memory as the A operand of O += P V, which accumulates
+//             in TMEM over the row of key tiles (rescaled only when the running
+//             maximum moves by more than 2^8); the two query tiles alternate on
+//             the tensor pipe, one's softmax under the other's MMAs
+//   dK/dV     items of (head, 128 keys) over 64-query sub-steps from the diagonal
+//             on: S^T and dP^T = V dO^T recomputed with K and V in tensor memory,
+//             P^T and dS^T written back over them, dV += P^T dO and
+//             dK += dS^T Q accumulated in TMEM
+//   dQ        items of (head, 128 queries) over 64-key sub-steps:
 //             dQ += dS K accumulated in TMEM
 // dQ has its own kernel so that no gradient needs atomics: every output element
 // is produced by one CTA in a fixed order, so results are deterministic.
@@ -45,7 +46,6 @@ namespace {
 constexpr int kTile = 128;     // queries and keys per tile
 constexpr int kHead = 64;      // head width
 constexpr int kTileBytes = kTile * kHead * 2;  // 16 KB: one Q/K/V/dO tile
-constexpr int kPanelBytes = kTile * 128;       // 16 KB: 64 FP16 columns of a 128-row P/dS tile
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -83,10 +83,6 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
         : "memory");
 }
 
-__device__ __forceinline__ void fence_async_shared() {
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-
 // 2^x on the special-function unit (relative error about 2^-22, flushes denormals).
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
@@ -98,6 +94,36 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // before the forward kernel moves the reference and rescales its accumulator:
 // probabilities then stay below 2^8, well inside FP16.
 constexpr float kLazyShift = 8.0f;
+
+// 2^x for two values at once on the FMA pipe, for the share of the forward kernel's
+// exponentials that the special-function unit has no time for: x = n + f with n the
+// nearest integer (taken from the low mantissa bits of x + 1.5 * 2^23), 2^f by a
+// degree-4 polynomial on [-0.5, 0.5] (relative error 2.7e-6, two orders below the FP16
+// rounding of the probabilities), n added into the exponent field. x must be at most
+// 127 - 1; anything below -120 counts as -120 (2^-120 is zero in FP16).
+__device__ __forceinline__ void exp2_pair_fma(fb::F2 x, float& lo, float& hi) {
+    float x0, x1;
+    fb::f2_unpack(x, x0, x1);
+    const fb::F2 clamped = fb::f2_pack(fmaxf(x0, -120.0f), fmaxf(x1, -120.0f));
+    const fb::F2 magic = fb::f2_pack(12582912.0f, 12582912.0f);
+    const fb::F2 z = fb::f2_add(clamped, magic);
+    const fb::F2 f = fb::f2_sub(clamped, fb::f2_sub(z, magic));
+    fb::F2 poly = fb::f2_fma(f, fb::f2_pack(0.009570090100169182f, 0.009570090100169182f),
+                             fb::f2_pack(0.05591785907745361f, 0.05591785907745361f));
+    poly = fb::f2_fma(poly, f, fb::f2_pack(0.2402474582195282f, 0.2402474582195282f));
+    poly = fb::f2_fma(poly, f, fb::f2_pack(0.6931217908859253f, 0.6931217908859253f));
+    poly = fb::f2_fma(poly, f, fb::f2_pack(0.9999992847442627f, 0.9999992847442627f));
+    float p0, p1, z0, z1;
+    fb::f2_unpack(poly, p0, p1);
+    fb::f2_unpack(z, z0, z1);
+    lo = __int_as_float(__float_as_int(p0) + (__float_as_int(z0) << 23));
+    hi = __int_as_float(__float_as_int(p1) + (__float_as_int(z1) << 23));
+}
+
+// Of every four pairs of exponentials in the forward kernel, how many take the FMA pipe.
+#ifndef FB_ATTN_FMA_EXP_OF_4
+#define FB_ATTN_FMA_EXP_OF_4 1
+#endif
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float r;
@@ -115,10 +141,6 @@ __device__ __forceinline__ void quadrant_sync(int quadrant) {
 // K-major tile [128 rows][64 cols] (rows = M or N index): 16-column step = 32 bytes.
 __device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile, int kstep) {
     return sm100::smem_desc_sw128(tile + kstep * 32, 16, 1024);
-}
-// A two-panel K-major tile [128 rows][128 cols] (P or dS as the A operand, K = key).
-__device__ __forceinline__ uint64_t desc_kmajor_wide(uint32_t tile, int kstep) {
-    return sm100::smem_desc_sw128(tile + (kstep >> 2) * kPanelBytes + (kstep & 3) * 32, 16, 1024);
 }
 // MN-major view of the same memory: rows are the K index, 16 rows = 2,048 bytes;
 // 64-column blocks (panels) are `lbo` bytes apart.
@@ -148,284 +170,448 @@ __device__ __forceinline__ void finish(int abort_value, uint32_t tmem_base, uint
 }
 
 // ---- forward ---------------------------------------------------------------------------
+//
+// Persistent CTAs, one per SM, each taking (head, two adjacent 128-query tiles) items in
+// rounds from a list ordered by work (the last tile pair, which sees the most keys,
+// first). The two query tiles share every K and V tile that comes through the ring and
+// take turns on the tensor pipe: while one tile's eight softmax warps work on its
+// scores, the other tile's P V and next Q K^T run. Per query tile: S = Q K^T into
+// 128 accumulator columns; two threads per row read 64 scores each, take the row
+// maximum, form the probabilities in base 2 and write them back as FP16 pairs over the
+// first 32 columns they read, where they are the A operand (from tensor memory) of
+// O += P V; O accumulates in 64 more columns over the whole row of key tiles. The
+// exponent the probabilities are taken against moves only when a tile's maximum exceeds
+// it by more than 2^kLazyShift, and only then is O read back, rescaled and rewritten.
+// The tensor pipe runs one thread's MMAs in issue order, which is what lets S(j+1)
+// overwrite the columns that P(j) occupies: it is issued after the P V that reads them.
+// Tensor memory: S/P of tile 0 at 0, of tile 1 at 128, O of tile 0 at 256, of tile 1 at 320.
 
-constexpr int kFwdThreads = 320;  // TMA warp, MMA warp, 8 softmax warps (2 threads per row)
-constexpr int kFwdSmem = 1024 + kTileBytes * 4 + 2 * kPanelBytes + 128;  // Q, 3-slot ring, P
+constexpr int kFwdThreads = 576;  // TMA warp, MMA warp, 2 x 8 softmax warps
+constexpr int kFwdSlots = 6;      // ring of K and V tiles
+constexpr int kFwdSmem = 1024 + kTileBytes * (2 + kFwdSlots) + 256;
 
-__global__ void __launch_bounds__(kFwdThreads, 2)
+struct FwdBarriers {
+    uint32_t base;
+    __device__ uint32_t q_full() const { return base; }
+    __device__ uint32_t q_empty() const { return base + 8; }
+    __device__ uint32_t s_full(int t) const { return base + 16 + 8u * t; }
+    __device__ uint32_t p_ready(int t) const { return base + 32 + 8u * t; }
+    __device__ uint32_t o_full(int t) const { return base + 48 + 8u * t; }
+    __device__ uint32_t o_empty(int t) const { return base + 64 + 8u * t; }
+    __device__ uint32_t slot_full(int s) const { return base + 80 + 8u * s; }
+    __device__ uint32_t slot_empty(int s) const { return base + 80 + 8u * (kFwdSlots + s); }
+};
+
+__global__ void __launch_bounds__(kFwdThreads, 1)
     fb_attention_forward(const __grid_constant__ AttnParams p) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base = (sm100::smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t q_tile = base;
-    const uint32_t ring = base + kTileBytes;
-    const uint32_t p_tile = ring + 3 * kTileBytes;
-    const uint32_t bars = p_tile + 2 * kPanelBytes;
-    const uint32_t q_full = bars, s_full = bars + 8, p_ready = bars + 16, o_full = bars + 24;
-    auto slot_full = [&](int s) { return bars + 32 + 8u * s; };
-    auto slot_empty = [&](int s) { return bars + 56 + 8u * s; };
+    const uint32_t q_tiles = base;                       // tile 0 then tile 1
+    const uint32_t ring = base + 2 * kTileBytes;
+    const FwdBarriers bar{ring + kFwdSlots * kTileBytes};
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
-    __shared__ float pair_max[2][2][kTile];  // [iteration parity][column half][row]
+    __shared__ float pair_max[2][2][2][kTile];  // [query tile][iteration parity][column half][row]
 
-    const int warp = threadIdx.x / 32;
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x / 32), 0);
     const int lane = threadIdx.x % 32;
     const int bh_count = p.heads * p.seqs;
-    const int qb = p.blocks - 1 - static_cast<int>(blockIdx.x / bh_count);  // heavy tiles first
-    const int bh = static_cast<int>(blockIdx.x % bh_count);
-    const int head = bh % p.heads;
-    const int seq = bh / p.heads;
+    const int pairs = (p.blocks + 1) / 2;
+    const int items = bh_count * pairs;
+    const int first_item = static_cast<int>(blockIdx.x);
+    const int stride = static_cast<int>(gridDim.x);
+    // Rounds of gridDim.x items, dealt alternately in ascending and descending CTA order.
+    auto item_of = [&](int round) {
+        const int slot = (round & 1) != 0 ? stride - 1 - first_item : first_item;
+        return round * stride + slot;
+    };
+    // An item's first query tile; its second one is the next tile, if the sequence has it.
+    auto first_tile = [&](int item) { return 2 * (pairs - 1 - item / bh_count); };
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
-        sm100::mbar_init(q_full, 1);
-        sm100::mbar_init(s_full, 1);
-        sm100::mbar_init(p_ready, 8);   // one arrival per softmax warp
-        sm100::mbar_init(o_full, 1);
-        for (int s = 0; s < 3; ++s) {
-            sm100::mbar_init(slot_full(s), 1);
-            sm100::mbar_init(slot_empty(s), 1);
+        sm100::mbar_init(bar.q_full(), 1);
+        sm100::mbar_init(bar.q_empty(), 1);
+        for (int t = 0; t < 2; ++t) {
+            sm100::mbar_init(bar.s_full(t), 1);
+            sm100::mbar_init(bar.p_ready(t), 8);   // one arrival per softmax warp
+            sm100::mbar_init(bar.o_full(t), 1);
+            sm100::mbar_init(bar.o_empty(t), 8);
+        }
+        for (int s = 0; s < kFwdSlots; ++s) {
+            sm100::mbar_init(bar.slot_full(s), 1);
+            sm100::mbar_init(bar.slot_empty(s), 1);
         }
         sm100::mbar_fence_init();
     }
     if (warp == 1) {
-        sm100::tmem_alloc(sm100::smem_u32(&tmem_slot), 256);
+        sm100::tmem_alloc(sm100::smem_u32(&tmem_slot), 512);
     }
     sm100::tc_fence_before_sync();
     __syncthreads();
     sm100::tc_fence_after_sync();
     const uint32_t tmem = tmem_slot;
-    const uint32_t tmem_s = tmem;
-    const uint32_t tmem_o = tmem + 128;
+    auto tmem_s = [&](int t) { return tmem + 128u * t; };
+    auto tmem_o = [&](int t) { return tmem + 256u + 64u * t; };
     volatile int* abort = &abort_flag;
     fb::dependency_wait();
-    if (threadIdx.x == 0) {
-        fb::dependency_release();
-    }
 
     if (warp == 0) {
         if (lane == 0) {
-            sm100::mbar_expect_tx(q_full, kTileBytes);
-            tma_load_4d(q_tile, &p.map_q, q_full, 0, qb * kTile, head, seq);
             int slot = 0;
             uint32_t phase = 0;
-            for (int j = 0; j <= qb; ++j) {
-                for (int which = 0; which < 2; ++which) {
-                    if (!sm100::mbar_wait(slot_empty(slot), phase ^ 1u, abort)) {
-                        j = qb + 1;
-                        break;
-                    }
-                    sm100::mbar_expect_tx(slot_full(slot), kTileBytes);
-                    tma_load_4d(ring + slot * kTileBytes, which == 0 ? &p.map_k : &p.map_v,
-                                slot_full(slot), 0, j * kTile, head, seq);
-                    if (++slot == 3) {
-                        slot = 0;
-                        phase ^= 1u;
+            bool ok = true;
+            int round = 0;
+            for (int item = item_of(0); ok && item < items; item = item_of(++round)) {
+                const int bh = item % bh_count;
+                const int head = bh % p.heads;
+                const int seq = bh / p.heads;
+                const int qb = first_tile(item);
+                const bool second = qb + 1 < p.blocks;
+                const int steps = second ? qb + 2 : qb + 1;
+                if (round > 0 && !sm100::mbar_wait(bar.q_empty(), (round - 1) & 1, abort)) {
+                    break;
+                }
+                sm100::mbar_expect_tx(bar.q_full(), second ? 2 * kTileBytes : kTileBytes);
+                tma_load_4d(q_tiles, &p.map_q, bar.q_full(), 0, qb * kTile, head, seq);
+                if (second) {
+                    tma_load_4d(q_tiles + kTileBytes, &p.map_q, bar.q_full(), 0, (qb + 1) * kTile,
+                                head, seq);
+                }
+                for (int j = 0; ok && j < steps; ++j) {
+                    for (int which = 0; which < 2; ++which) {
+                        if (!sm100::mbar_wait(bar.slot_empty(slot), phase ^ 1u, abort)) {
+                            ok = false;
+                            break;
+                        }
+                        sm100::mbar_expect_tx(bar.slot_full(slot), kTileBytes);
+                        tma_load_4d(ring + slot * kTileBytes, which == 0 ? &p.map_k : &p.map_v,
+                                    bar.slot_full(slot), 0, j * kTile, head, seq);
+                        if (++slot == kFwdSlots) {
+                            slot = 0;
+                            phase ^= 1u;
+                        }
                     }
                 }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            bool ok = sm100::mbar_wait(q_full, 0, abort);
+        // The whole warp runs this loop, so that its state stays warp-uniform (the MMA's
+        // descriptors then need no per-thread to uniform register moves); one elected lane
+        // issues.
+        {
             int slot = 0;
             uint32_t phase = 0;
-            for (int j = 0; ok && j <= qb; ++j) {
-                const int kslot = slot;
-                if (!sm100::mbar_wait(slot_full(kslot), phase, abort)) {
-                    break;
+            uint32_t scored[2] = {0, 0};   // key tiles processed per query tile, over all items
+            uint32_t drained[2] = {0, 0};  // items finished per query tile
+            bool ok = true;
+            // Waits for the ring's next tile and returns its address (0 after an abort).
+            auto next_tile = [&]() -> uint32_t {
+                if (!sm100::mbar_wait(bar.slot_full(slot), phase, abort)) {
+                    return 0u;
                 }
-                if (++slot == 3) {
+                sm100::tc_fence_after_sync();
+                return ring + slot * kTileBytes;
+            };
+            auto release_tile = [&]() {
+                if (sm100::elect_one()) {
+                    sm100::mma_commit(bar.slot_empty(slot));
+                }
+                __syncwarp();
+                if (++slot == kFwdSlots) {
                     slot = 0;
                     phase ^= 1u;
                 }
-                sm100::tc_fence_after_sync();
-                const uint32_t k_tile = ring + kslot * kTileBytes;
-#pragma unroll
-                for (int ks = 0; ks < 4; ++ks) {
-                    sm100::mma_f16_ss(tmem_s, desc_kmajor(q_tile, ks), desc_kmajor(k_tile, ks),
-                                      kIdescS, ks > 0);
+            };
+            const uint64_t q_desc[2] = {desc_kmajor(q_tiles, 0), desc_kmajor(q_tiles + kTileBytes, 0)};
+            const uint32_t s_at[2] = {tmem_s(0), tmem_s(1)};
+            const uint32_t o_at[2] = {tmem_o(0), tmem_o(1)};
+            auto scores = [&](int t, uint32_t k_tile) {
+                const uint64_t k_desc = desc_kmajor(k_tile, 0);
+                if (sm100::elect_one()) {
+                    sm100::mma_f16_ss_at<0>(s_at[t], q_desc[t], 0, k_desc, 0, kIdescS);
+                    sm100::mma_f16_ss_at<1>(s_at[t], q_desc[t], 2, k_desc, 2, kIdescS);
+                    sm100::mma_f16_ss_at<1>(s_at[t], q_desc[t], 4, k_desc, 4, kIdescS);
+                    sm100::mma_f16_ss_at<1>(s_at[t], q_desc[t], 6, k_desc, 6, kIdescS);
+                    sm100::mma_commit(bar.s_full(t));
                 }
-                sm100::mma_commit(slot_empty(kslot));
-                sm100::mma_commit(s_full);
-
-                const int vslot = slot;
-                if (!sm100::mbar_wait(slot_full(vslot), phase, abort)) {
+                __syncwarp();
+            };
+            // O_t (+)= P_t V once the tile's probabilities are in tensor memory; keys
+            // 64 half + [0, 64) sit in columns 64 half + [0, 32) of the score accumulator.
+            auto weighted = [&](int t, uint32_t v_tile, int j, bool last) -> bool {
+                if (!sm100::mbar_wait(bar.p_ready(t), scored[t] & 1, abort)) {
+                    return false;
+                }
+                ++scored[t];
+                if (j == 0 && drained[t] > 0 &&
+                    !sm100::mbar_wait(bar.o_empty(t), (drained[t] - 1) & 1, abort)) {
+                    return false;
+                }
+                sm100::tc_fence_after_sync();
+                // An MN-major step of 16 keys is 2,048 bytes.
+                const uint64_t v_desc = desc_mnmajor(v_tile, 0, 16);
+                if (sm100::elect_one()) {
+                    sm100::mma_f16_ts_at<-1>(o_at[t], s_at[t], v_desc, 0, kIdescPV, j > 0);
+#pragma unroll
+                    for (int ks = 1; ks < 8; ++ks) {
+                        sm100::mma_f16_ts_at<1>(o_at[t], s_at[t] + (ks >> 2) * 64 + (ks & 3) * 8,
+                                                v_desc, ks * 128, kIdescPV);
+                    }
+                    if (last) {
+                        sm100::mma_commit(bar.o_full(t));
+                    }
+                }
+                __syncwarp();
+                if (last) {
+                    ++drained[t];
+                }
+                return true;
+            };
+            int round = 0;
+            for (int item = item_of(0); ok && item < items; item = item_of(++round)) {
+                const int qb = first_tile(item);
+                const bool second = qb + 1 < p.blocks;
+                const int steps0 = qb + 1;
+                const int steps = second ? qb + 2 : qb + 1;
+                if (!sm100::mbar_wait(bar.q_full(), round & 1, abort)) {
                     break;
                 }
-                if (++slot == 3) {
-                    slot = 0;
-                    phase ^= 1u;
-                }
-                if (!sm100::mbar_wait(p_ready, j & 1, abort)) {
+                uint32_t k_tile = next_tile();
+                if (k_tile == 0) {
                     break;
                 }
-                sm100::tc_fence_after_sync();
-                const uint32_t v_tile = ring + vslot * kTileBytes;
-#pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    sm100::mma_f16_ss(tmem_o, desc_kmajor_wide(p_tile, ks),
-                                      desc_mnmajor(v_tile, ks, 16), kIdescPV, j > 0 || ks > 0);
+                scores(0, k_tile);
+                if (second) {
+                    scores(1, k_tile);
                 }
-                sm100::mma_commit(slot_empty(vslot));
-                if (j == qb) {
-                    sm100::mma_commit(o_full);
+                release_tile();
+                for (int j = 0; ok && j < steps; ++j) {
+                    const uint32_t v_tile = next_tile();
+                    if (v_tile == 0) {
+                        ok = false;
+                        break;
+                    }
+                    const int v_slot = slot;
+                    // The V tile is released after both tiles' P V; the ring's cursor moves
+                    // on to the next K tile meanwhile.
+                    if (++slot == kFwdSlots) {
+                        slot = 0;
+                        phase ^= 1u;
+                    }
+                    if (j < steps0 && !weighted(0, v_tile, j, j + 1 == steps0)) {
+                        ok = false;
+                        break;
+                    }
+                    k_tile = 0;
+                    if (j + 1 < steps) {
+                        k_tile = next_tile();
+                        if (k_tile == 0) {
+                            ok = false;
+                            break;
+                        }
+                        if (j + 1 < steps0) {
+                            scores(0, k_tile);
+                        }
+                    }
+                    if (second && !weighted(1, v_tile, j, j + 1 == steps)) {
+                        ok = false;
+                        break;
+                    }
+                    if (sm100::elect_one()) {
+                        sm100::mma_commit(bar.slot_empty(v_slot));
+                    }
+                    __syncwarp();
+                    if (j + 1 < steps) {
+                        if (second) {
+                            scores(1, k_tile);
+                        }
+                        release_tile();
+                    }
                 }
+                // Every MMA that reads the query tiles has been issued.
+                if (sm100::elect_one()) {
+                    sm100::mma_commit(bar.q_empty());
+                }
+                __syncwarp();
             }
         }
     } else {
         // Two threads per query row: this one owns score columns [64 half, 64 half + 64)
-        // and output columns [32 half, 32 half + 32). The output tile accumulates in tensor
-        // memory over the whole row of key tiles; the running maximum that the
-        // probabilities are taken against only moves when a tile exceeds it by more than
-        // 2^kLazyShift, and only then is the accumulator read, rescaled and written back.
+        // and output columns [32 half, 32 half + 32) of query tile `tile`.
+        const int tile = (warp - 2) / 8;
         const int quadrant = warp % 4;
-        const int half = (warp - 2) / 4;
+        const int half = ((warp - 2) % 8) / 4;
         const int row = quadrant * 32 + lane;
-        const int q_index = qb * kTile + row;
         const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
+        const uint32_t my_scores = tmem_s(tile) + lane_base + half * 64;
+        const uint32_t my_output = tmem_o(tile) + lane_base + half * 32;
+        const int pair_barrier = tile * 4 + quadrant;
         const float scale2 = p.scale * kLog2e;
         const fb::F2 scale_pair = fb::f2_pack(scale2, scale2);
-        const uint32_t p_row = p_tile + half * kPanelBytes + row * 128;
-        float m = -INFINITY;        // reference exponent of the row (base 2), shared by the pair
-        fb::F2 l = 0;               // this thread's share of the row sum, in two partial sums
+        uint32_t scored = 0;   // key tiles processed, over all items
+        uint32_t drained = 0;  // items finished
         bool ok = true;
-        for (int j = 0; ok && j <= qb; ++j) {
-            if (!sm100::mbar_wait(s_full, j & 1, abort)) {
+        int round = 0;
+        for (int item = item_of(0); ok && item < items; item = item_of(++round)) {
+            const int bh = item % bh_count;
+            const int head = bh % p.heads;
+            const int seq = bh / p.heads;
+            const int qb = first_tile(item) + tile;
+            if (qb >= p.blocks) {
+                continue;   // the sequence has no second tile in its last pair
+            }
+            const int q_index = qb * kTile + row;
+            float m = -INFINITY;  // reference exponent of the row (base 2), shared by the pair
+            fb::F2 l = 0;         // this thread's share of the row sum, in two partial sums
+            for (int j = 0; ok && j <= qb; ++j) {
+                if (!sm100::mbar_wait(bar.s_full(tile), scored & 1, abort)) {
+                    ok = false;
+                    break;
+                }
+                const int parity = scored & 1;
+                ++scored;
+                sm100::tc_fence_after_sync();
+                uint32_t raw[64];
+                sm100::tmem_ld_32x32(my_scores, reinterpret_cast<uint32_t(&)[32]>(raw[0]));
+                sm100::tmem_ld_32x32(my_scores + 32, reinterpret_cast<uint32_t(&)[32]>(raw[32]));
+                sm100::tmem_ld_wait();
+                if (j == qb) {
+                    // The diagonal tile: keys after the query count as minus infinity.
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) {
+                        raw[i] = (half * 64 + i <= row) ? raw[i] : 0xff800000u;
+                    }
+                }
+                float top[4];
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    top[t] = max3(__uint_as_float(raw[t]), __uint_as_float(raw[4 + t]),
+                                  __uint_as_float(raw[8 + t]));
+                }
+#pragma unroll
+                for (int i = 12; i < 60; i += 8) {
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        top[t] = max3(top[t], __uint_as_float(raw[i + t]),
+                                      __uint_as_float(raw[i + 4 + t]));
+                    }
+                }
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    top[t] = fmaxf(top[t], __uint_as_float(raw[60 + t]));
+                }
+                // The scale is positive, so the maximum may be scaled after it is taken.
+                const float local = fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3])) * scale2;
+                pair_max[tile][parity][half][row] = local;
+                quadrant_sync(pair_barrier);
+                const float mx = fmaxf(m, fmaxf(local, pair_max[tile][parity][half ^ 1][row]));
+                const bool moved = mx - m > kLazyShift;   // always on the first tile (m = -inf)
+                float alpha = 1.0f;
+                if (moved) {
+                    alpha = fast_exp2(m - mx);
+                    m = mx;
+                    l = fb::f2_mul(l, fb::f2_pack(alpha, alpha));
+                }
+                if (j > 0 && __any_sync(0xffffffffu, moved)) {
+                    // The previous key tile's P V has finished: the score commit that was
+                    // just waited for covers every earlier MMA of the issuing thread.
+                    const fb::F2 a2 = fb::f2_pack(alpha, alpha);
+#pragma unroll 1
+                    for (int c = 0; c < 2; ++c) {
+                        uint32_t acc[16];
+                        sm100::tmem_ld_32x16(my_output + c * 16, acc);
+                        sm100::tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 16; i += 2) {
+                            float lo, hi;
+                            fb::f2_unpack(fb::f2_mul(fb::f2_pack(__uint_as_float(acc[i]),
+                                                                 __uint_as_float(acc[i + 1])), a2),
+                                          lo, hi);
+                            acc[i] = __float_as_uint(lo);
+                            acc[i + 1] = __float_as_uint(hi);
+                        }
+                        sm100::tmem_st_32x16(my_output + c * 16, acc);
+                    }
+                }
+                const fb::F2 shift = fb::f2_pack(-m, -m);
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        float lo, hi;
+                        const fb::F2 x =
+                            fb::f2_fma(fb::f2_pack(__uint_as_float(raw[32 * c + 2 * i]),
+                                                   __uint_as_float(raw[32 * c + 2 * i + 1])),
+                                       scale_pair, shift);
+                        if ((i & 3) < FB_ATTN_FMA_EXP_OF_4) {
+                            exp2_pair_fma(x, lo, hi);
+                        } else {
+                            fb::f2_unpack(x, lo, hi);
+                            lo = fast_exp2(lo);
+                            hi = fast_exp2(hi);
+                        }
+                        l = fb::f2_add(l, fb::f2_pack(lo, hi));
+                        packed[i] = fb::pack2(lo, hi);
+                    }
+                    sm100::tmem_st_32x16(my_scores + c * 16, packed);
+                }
+                sm100::tmem_st_wait();
+                sm100::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    sm100::mbar_arrive(bar.p_ready(tile));
+                }
+            }
+            if (!ok || !sm100::mbar_wait(bar.o_full(tile), drained & 1, abort)) {
                 ok = false;
                 break;
             }
+            ++drained;
             sm100::tc_fence_after_sync();
-            uint32_t raw[64];
-            sm100::tmem_ld_32x32(tmem_s + lane_base + half * 64,
-                                 reinterpret_cast<uint32_t(&)[32]>(raw[0]));
-            sm100::tmem_ld_32x32(tmem_s + lane_base + half * 64 + 32,
-                                 reinterpret_cast<uint32_t(&)[32]>(raw[32]));
+            uint32_t acc[32];
+            sm100::tmem_ld_32x32(my_output, acc);
             sm100::tmem_ld_wait();
-            if (j == qb) {
-                // The diagonal tile: keys after the query count as minus infinity.
-#pragma unroll
-                for (int i = 0; i < 64; ++i) {
-                    raw[i] = (half * 64 + i <= row) ? raw[i] : 0xff800000u;
-                }
-            }
-            float top[4];
-#pragma unroll
-            for (int t = 0; t < 4; ++t) {
-                top[t] = max3(__uint_as_float(raw[t]), __uint_as_float(raw[4 + t]),
-                              __uint_as_float(raw[8 + t]));
-            }
-#pragma unroll
-            for (int i = 12; i < 60; i += 8) {
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    top[t] = max3(top[t], __uint_as_float(raw[i + t]), __uint_as_float(raw[i + 4 + t]));
-                }
-            }
-#pragma unroll
-            for (int t = 0; t < 4; ++t) {
-                top[t] = fmaxf(top[t], __uint_as_float(raw[60 + t]));
-            }
-            // The scale is positive, so the maximum may be scaled after it is taken.
-            const float local = fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3])) * scale2;
-            pair_max[j & 1][half][row] = local;
-            quadrant_sync(quadrant);
-            const float mx = fmaxf(m, fmaxf(local, pair_max[j & 1][half ^ 1][row]));
-            const bool moved = mx - m > kLazyShift;   // always on the first tile (m = -inf)
-            float alpha = 1.0f;
-            if (moved) {
-                alpha = fast_exp2(m - mx);
-                m = mx;
-                l = fb::f2_mul(l, fb::f2_pack(alpha, alpha));
-            }
-            if (j > 0 && __any_sync(0xffffffffu, moved)) {
-                // The previous tile's P V has finished: the score commit that was just waited
-                // for covers every earlier MMA of the issuing thread.
-                const fb::F2 a2 = fb::f2_pack(alpha, alpha);
-#pragma unroll 1
-                for (int c = 0; c < 2; ++c) {
-                    uint32_t acc[16];
-                    const uint32_t at = tmem_o + lane_base + half * 32 + c * 16;
-                    sm100::tmem_ld_32x16(at, acc);
-                    sm100::tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 16; i += 2) {
-                        float lo, hi;
-                        fb::f2_unpack(fb::f2_mul(fb::f2_pack(__uint_as_float(acc[i]),
-                                                             __uint_as_float(acc[i + 1])), a2), lo, hi);
-                        acc[i] = __float_as_uint(lo);
-                        acc[i + 1] = __float_as_uint(hi);
-                    }
-                    sm100::tmem_st_32x16(at, acc);
-                }
-                sm100::tmem_st_wait();
-            }
-            const fb::F2 shift = fb::f2_pack(-m, -m);
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                unsigned w[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    float lo, hi;
-                    fb::f2_unpack(fb::f2_fma(fb::f2_pack(__uint_as_float(raw[8 * c + 2 * i]),
-                                                         __uint_as_float(raw[8 * c + 2 * i + 1])),
-                                             scale_pair, shift), lo, hi);
-                    lo = fast_exp2(lo);
-                    hi = fast_exp2(hi);
-                    l = fb::f2_add(l, fb::f2_pack(lo, hi));
-                    w[i] = fb::pack2(lo, hi);
-                }
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(
-                                 p_row + ((c ^ (row & 7)) << 4)), "r"(w[0]), "r"(w[1]), "r"(w[2]),
-                             "r"(w[3])
-                             : "memory");
-            }
-            fence_async_shared();
+            // The accumulator is free for the next item's first P V.
             sm100::tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) {
-                sm100::mbar_arrive(p_ready);
+                sm100::mbar_arrive(bar.o_empty(tile));
             }
-        }
-        if (ok && !sm100::mbar_wait(o_full, 0, abort)) {
-            ok = false;
-        }
-        sm100::tc_fence_after_sync();
-        float o[32];
-        {
-            uint32_t acc[32];
-            sm100::tmem_ld_32x32(tmem_o + lane_base + half * 32, acc);
-            sm100::tmem_ld_wait();
+            // The row sum is the two threads' shares added together.
+            float l_lo, l_hi;
+            fb::f2_unpack(l, l_lo, l_hi);
+            const float mine = l_lo + l_hi;
+            const int parity = scored & 1;   // the slot the next key tile will use is idle now
+            pair_max[tile][parity][half][row] = mine;
+            quadrant_sync(pair_barrier);
+            const float total = mine + pair_max[tile][parity][half ^ 1][row];
+            quadrant_sync(pair_barrier);     // both have read before either writes a maximum there
+            if (q_index < p.length) {
+                const float inv = 1.0f / total;
+                __half* out = static_cast<__half*>(p.out0) + seq * p.out_seq + head * p.out_head +
+                              static_cast<long long>(q_index) * p.out_row + half * 32;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                o[i] = __uint_as_float(acc[i]);
-            }
-        }
-        float l_lo, l_hi;
-        fb::f2_unpack(l, l_lo, l_hi);
-        const float mine = l_lo + l_hi;
-        // The row sum is the two threads' shares added together.
-        pair_max[0][half][row] = mine;
-        quadrant_sync(quadrant);
-        const float total = mine + pair_max[0][half ^ 1][row];
-        if (ok && q_index < p.length) {
-            const float inv = 1.0f / total;
-            __half* out = static_cast<__half*>(p.out0) + seq * p.out_seq + head * p.out_head +
-                          static_cast<long long>(q_index) * p.out_row + half * 32;
+                for (int c = 0; c < 4; ++c) {
+                    float v[8];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                float v[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    v[i] = o[c * 8 + i] * inv;
+                    for (int i = 0; i < 8; ++i) {
+                        v[i] = __uint_as_float(acc[c * 8 + i]) * inv;
+                    }
+                    *reinterpret_cast<uint4*>(out + c * 8) = fb::pack8(v);
                 }
-                *reinterpret_cast<uint4*>(out + c * 8) = fb::pack8(v);
-            }
-            if (half == 0) {
-                p.lse[static_cast<size_t>(bh) * p.length + q_index] = (m + log2f(total)) * kLn2;
+                if (half == 0) {
+                    p.lse[static_cast<size_t>(bh) * p.length + q_index] = (m + log2f(total)) * kLn2;
+                }
             }
         }
     }
-    finish(abort_flag, tmem, 256, warp);
+    // A persistent CTA lets the next kernel in only when its own work is done.
+    if (threadIdx.x == 0) {
+        fb::dependency_release();
+    }
+    finish(abort_flag, tmem, 512, warp);
 }
 
 // ---- backward: delta = rowsum(dO * O) ----------------------------------------------------------
@@ -583,7 +769,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
-    const int warp = threadIdx.x / 32;
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x / 32), 0);
     const int lane = threadIdx.x % 32;
     const int bh_count = p.heads * p.seqs;
     const int items = bh_count * p.blocks;
@@ -666,7 +852,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        // The whole warp runs this loop so that its state stays warp-uniform; one elected
+        // lane issues the MMAs and commits.
+        {
             // Descriptors of stage 0's tiles; a stage is 16 KB further, a K-major k-step 32
             // bytes, an MN-major one 2,048.
             const uint64_t q_desc = sm100::smem_desc_sw128(ring, 16, 1024);
@@ -688,17 +876,19 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                     sm100::tc_fence_after_sync();
                     const uint64_t q_sub = desc_advance(q_desc, stage * 2 * kSubBytes);
                     const uint64_t do_sub = desc_advance(do_desc, stage * 2 * kSubBytes);
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        sm100::mma_f16_ts(tmem_st(g & 1), tmem_k + ks * 8,
-                                          desc_advance(q_sub, ks * 32), kIdescSub, ks > 0);
+                    if (sm100::elect_one()) {
+                        const uint32_t st_at = tmem_st(g & 1), dpt_at = tmem_dpt(g & 1);
+                        sm100::mma_f16_ts_at<0>(st_at, tmem_k, q_sub, 0, kIdescSub);
+                        sm100::mma_f16_ts_at<1>(st_at, tmem_k + 8, q_sub, 2, kIdescSub);
+                        sm100::mma_f16_ts_at<1>(st_at, tmem_k + 16, q_sub, 4, kIdescSub);
+                        sm100::mma_f16_ts_at<1>(st_at, tmem_k + 24, q_sub, 6, kIdescSub);
+                        sm100::mma_f16_ts_at<0>(dpt_at, tmem_v, do_sub, 0, kIdescSub);
+                        sm100::mma_f16_ts_at<1>(dpt_at, tmem_v + 8, do_sub, 2, kIdescSub);
+                        sm100::mma_f16_ts_at<1>(dpt_at, tmem_v + 16, do_sub, 4, kIdescSub);
+                        sm100::mma_f16_ts_at<1>(dpt_at, tmem_v + 24, do_sub, 6, kIdescSub);
+                        sm100::mma_commit(bar.scores_full(g & 1));
                     }
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        sm100::mma_f16_ts(tmem_dpt(g & 1), tmem_v + ks * 8,
-                                          desc_advance(do_sub, ks * 32), kIdescSub, ks > 0);
-                    }
-                    sm100::mma_commit(bar.scores_full(g & 1));
+                    __syncwarp();
                     return true;
                 };
                 ok = ok && issue_scores(0);
@@ -719,21 +909,22 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                     const uint64_t do_sub = desc_advance(do_desc, stage * 2 * kSubBytes);
                     // dV += P^T dO and dK += dS^T Q over this sub-step's 64 queries; queries
                     // 32 part + [0, 32) sit in columns 32 part + [0, 16) of the accumulator.
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        sm100::mma_f16_ts(tmem_dv, tmem_st(b) + (ks >> 1) * 32 + (ks & 1) * 8,
-                                          desc_advance(do_sub, ks * 2048), kIdescPV,
-                                          (h | ks) != 0);
+                    if (sm100::elect_one()) {
+                        const uint32_t st_at = tmem_st(b), dpt_at = tmem_dpt(b);
+                        sm100::mma_f16_ts_at<-1>(tmem_dv, st_at, do_sub, 0, kIdescPV, h != 0);
+                        sm100::mma_f16_ts_at<1>(tmem_dv, st_at + 8, do_sub, 128, kIdescPV);
+                        sm100::mma_f16_ts_at<1>(tmem_dv, st_at + 32, do_sub, 256, kIdescPV);
+                        sm100::mma_f16_ts_at<1>(tmem_dv, st_at + 40, do_sub, 384, kIdescPV);
+                        sm100::mma_f16_ts_at<-1>(tmem_dk, dpt_at, q_sub, 0, kIdescPV, h != 0);
+                        sm100::mma_f16_ts_at<1>(tmem_dk, dpt_at + 8, q_sub, 128, kIdescPV);
+                        sm100::mma_f16_ts_at<1>(tmem_dk, dpt_at + 32, q_sub, 256, kIdescPV);
+                        sm100::mma_f16_ts_at<1>(tmem_dk, dpt_at + 40, q_sub, 384, kIdescPV);
+                        sm100::mma_commit(bar.stage_empty(stage));
+                        if (h + 1 == steps) {
+                            sm100::mma_commit(bar.done());
+                        }
                     }
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        sm100::mma_f16_ts(tmem_dk, tmem_dpt(b) + (ks >> 1) * 32 + (ks & 1) * 8,
-                                          desc_advance(q_sub, ks * 2048), kIdescPV, (h | ks) != 0);
-                    }
-                    sm100::mma_commit(bar.stage_empty(stage));
-                    if (h + 1 == steps) {
-                        sm100::mma_commit(bar.done());
-                    }
+                    __syncwarp();
                 }
                 before += steps;
             }
@@ -908,7 +1099,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
-    const int warp = threadIdx.x / 32;
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x / 32), 0);
     const int lane = threadIdx.x % 32;
     const int bh_count = p.heads * p.seqs;
     const int items = bh_count * p.blocks;
@@ -977,7 +1168,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        // The whole warp runs this loop; one elected lane issues the MMAs and commits.
+        {
             const uint64_t k_desc = sm100::smem_desc_sw128(ring, 16, 1024);
             const uint64_t v_desc = sm100::smem_desc_sw128(ring + kSubBytes, 16, 1024);
             uint32_t before = 0;  // sub-steps of earlier items (always even)
@@ -996,17 +1188,19 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                     sm100::tc_fence_after_sync();
                     const uint64_t k_sub = desc_advance(k_desc, stage * 2 * kSubBytes);
                     const uint64_t v_sub = desc_advance(v_desc, stage * 2 * kSubBytes);
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        sm100::mma_f16_ts(tmem_s(g & 1), tmem_q + ks * 8,
-                                          desc_advance(k_sub, ks * 32), kIdescSub, ks > 0);
+                    if (sm100::elect_one()) {
+                        const uint32_t s_at = tmem_s(g & 1), dp_at = tmem_dp(g & 1);
+                        sm100::mma_f16_ts_at<0>(s_at, tmem_q, k_sub, 0, kIdescSub);
+                        sm100::mma_f16_ts_at<1>(s_at, tmem_q + 8, k_sub, 2, kIdescSub);
+                        sm100::mma_f16_ts_at<1>(s_at, tmem_q + 16, k_sub, 4, kIdescSub);
+                        sm100::mma_f16_ts_at<1>(s_at, tmem_q + 24, k_sub, 6, kIdescSub);
+                        sm100::mma_f16_ts_at<0>(dp_at, tmem_do, v_sub, 0, kIdescSub);
+                        sm100::mma_f16_ts_at<1>(dp_at, tmem_do + 8, v_sub, 2, kIdescSub);
+                        sm100::mma_f16_ts_at<1>(dp_at, tmem_do + 16, v_sub, 4, kIdescSub);
+                        sm100::mma_f16_ts_at<1>(dp_at, tmem_do + 24, v_sub, 6, kIdescSub);
+                        sm100::mma_commit(bar.scores_full(g & 1));
                     }
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        sm100::mma_f16_ts(tmem_dp(g & 1), tmem_do + ks * 8,
-                                          desc_advance(v_sub, ks * 32), kIdescSub, ks > 0);
-                    }
-                    sm100::mma_commit(bar.scores_full(g & 1));
+                    __syncwarp();
                     return true;
                 };
                 ok = ok && issue_scores(0);
@@ -1025,15 +1219,18 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                     const int stage = count % kBwdStages;
                     const uint64_t k_sub = desc_advance(k_desc, stage * 2 * kSubBytes);
                     // dQ += dS K over this sub-step's 64 keys (the K tile read MN-major).
-#pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        sm100::mma_f16_ts(tmem_dq, tmem_dp(b) + (ks >> 1) * 32 + (ks & 1) * 8,
-                                          desc_advance(k_sub, ks * 2048), kIdescPV, (g | ks) != 0);
+                    if (sm100::elect_one()) {
+                        const uint32_t dp_at = tmem_dp(b);
+                        sm100::mma_f16_ts_at<-1>(tmem_dq, dp_at, k_sub, 0, kIdescPV, g != 0);
+                        sm100::mma_f16_ts_at<1>(tmem_dq, dp_at + 8, k_sub, 128, kIdescPV);
+                        sm100::mma_f16_ts_at<1>(tmem_dq, dp_at + 32, k_sub, 256, kIdescPV);
+                        sm100::mma_f16_ts_at<1>(tmem_dq, dp_at + 40, k_sub, 384, kIdescPV);
+                        sm100::mma_commit(bar.stage_empty(stage));
+                        if (g + 1 == steps) {
+                            sm100::mma_commit(bar.done());
+                        }
                     }
-                    sm100::mma_commit(bar.stage_empty(stage));
-                    if (g + 1 == steps) {
-                        sm100::mma_commit(bar.done());
-                    }
+                    __syncwarp();
                 }
                 before += steps;
             }
@@ -1231,7 +1428,10 @@ cudaError_t attention_forward(const AttentionView& o, float* lse, const Attentio
     if (e != cudaSuccess) {
         return e;
     }
-    const unsigned grid = static_cast<unsigned>(shape.sequences * shape.heads * p.blocks);
+    int sms = 148;
+    sm_count(&sms);
+    const long long items = static_cast<long long>(shape.sequences * shape.heads) * ((p.blocks + 1) / 2);
+    const unsigned grid = static_cast<unsigned>(std::min<long long>(items, sms));
     return fb::launch_dependent(fb_attention_forward, dim3(grid), dim3(kFwdThreads), kFwdSmem, stream,
                                 p);
 }
@@ -1318,6 +1518,7 @@ cudaError_t attention_error_flag(int* value, bool reset) {
 namespace {
 
 constexpr flint_status kBad = FLINT_ERROR_INVALID_ARGUMENT;
+
 
 flint_status check_attention_dims(const char* name, size_t batches, size_t length,
                                   size_t head_width, float scale) {

@@ -199,6 +199,51 @@ __device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uin
         : "memory");
 }
 
+// The same two instructions with the descriptors given as (low word + `step`, high word) and
+// the accumulate flag fixed at compile time unless kAccumulate is negative (then `accumulate`
+// decides): one integer addition per MMA in the issuing thread, which shares its scheduler
+// with compute warps. `step` is in 16-byte units and must not carry out of the address field.
+template <int kAccumulate>
+__device__ __forceinline__ void mma_f16_ss_at(uint32_t d_tmem, uint64_t a_desc, uint32_t a_step,
+                                              uint64_t b_desc, uint32_t b_step, uint32_t idesc,
+                                              uint32_t accumulate = 0) {
+    const uint32_t a_lo = static_cast<uint32_t>(a_desc) + a_step;
+    const uint32_t b_lo = static_cast<uint32_t>(b_desc) + b_step;
+    const uint32_t a_hi = static_cast<uint32_t>(a_desc >> 32);
+    const uint32_t b_hi = static_cast<uint32_t>(b_desc >> 32);
+    const uint32_t flag = kAccumulate < 0 ? accumulate : static_cast<uint32_t>(kAccumulate);
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        ".reg .b64 a, b;\n"
+        "mov.b64 a, {%1, %2};\n"
+        "mov.b64 b, {%3, %4};\n"
+        "setp.ne.b32 p, %6, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %5, p;\n"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(flag)
+        : "memory");
+}
+
+template <int kAccumulate>
+__device__ __forceinline__ void mma_f16_ts_at(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                              uint32_t b_step, uint32_t idesc,
+                                              uint32_t accumulate = 0) {
+    const uint32_t b_lo = static_cast<uint32_t>(b_desc) + b_step;
+    const uint32_t b_hi = static_cast<uint32_t>(b_desc >> 32);
+    const uint32_t flag = kAccumulate < 0 ? accumulate : static_cast<uint32_t>(kAccumulate);
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        ".reg .b64 b;\n"
+        "mov.b64 b, {%2, %3};\n"
+        "setp.ne.b32 p, %5, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], b, %4, p;\n"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(flag)
+        : "memory");
+}
+
 // The mbarrier gets one arrival when every tcgen05.mma issued so far by this
 // thread has finished (including its reads of shared memory).
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
