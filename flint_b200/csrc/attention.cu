@@ -171,43 +171,58 @@ __device__ __forceinline__ void finish(int abort_value, uint32_t tmem_base, uint
 
 // ---- forward ---------------------------------------------------------------------------
 //
-// Persistent CTAs, one per SM, each taking (head, two adjacent 128-query tiles) items in
-// rounds from a list ordered by work (the last tile pair, which sees the most keys,
-// first). The two query tiles share every K and V tile that comes through the ring and
-// take turns on the tensor pipe: while one tile's eight softmax warps work on its
-// scores, the other tile's P V and next Q K^T run. Per query tile: S = Q K^T into
-// 128 accumulator columns; two threads per row read 64 scores each, take the row
-// maximum, form the probabilities in base 2 and write them back as FP16 pairs over the
-// first 32 columns they read, where they are the A operand (from tensor memory) of
-// O += P V; O accumulates in 64 more columns over the whole row of key tiles. The
-// exponent the probabilities are taken against moves only when a tile's maximum exceeds
-// it by more than 2^kLazyShift, and only then is O read back, rescaled and rewritten.
-// The tensor pipe runs one thread's MMAs in issue order, which is what lets S(j+1)
-// overwrite the columns that P(j) occupies: it is issued after the P V that reads them.
-// Tensor memory: S/P of tile 0 at 0, of tile 1 at 128, O of tile 0 at 256, of tile 1 at 320.
+// Persistent CTAs, one per SM, each taking items of (128-query tile, two heads) in rounds
+// from a list ordered by work (the last query tile, which sees the most keys, first). The
+// two heads' tiles ("tile 0" and "tile 1" below) have the same number of key tiles and take
+// turns on everything, so the CTA's work is one sequence of steps n = 0, 1, 2, ... that runs
+// on across items: step n belongs to tile n & 1.
+//   tensor pipe   S(n) = Q K^T into score buffer n % 3 (three 128-column buffers), issued
+//                 three steps ahead of the P V that frees the buffer: O(tile) += P(n) V.
+//   softmax       eight warps per tile, two threads per row: read 64 scores each, take the
+//                 row maximum, form the probabilities in base 2 and write them back as FP16
+//                 pairs over the first 32 columns they read, where they are the A operand
+//                 (from tensor memory) of P V. A quarter of the exponentials run as a
+//                 polynomial on the FMA pipe, the rest on the special-function unit.
+// A tile's softmax therefore never waits for its own P V: the next scores are already
+// there, and the two tiles' softmax phases overlap each other and the MMAs. O accumulates
+// in tensor memory over the whole row of key tiles; the exponent the probabilities are
+// taken against moves only when a tile's maximum exceeds it by more than 2^kLazyShift, and
+// only then does the thread wait for the previous P V, read O back, rescale and rewrite it.
+// The tensor pipe runs one thread's MMAs in issue order, which is what lets S(n + 3)
+// overwrite the columns that P(n) occupies: it is issued after the P V that reads them.
+// Every K and V tile passes through one ring in the order the MMAs use them: K(0), K(1),
+// K(2), then V(n), K(n + 3) alternately. The query tiles are double-buffered by item.
+// Tensor memory: score buffers at 0, 128, 256; O of tile 0 at 384, of tile 1 at 448.
 
 constexpr int kFwdThreads = 576;  // TMA warp, MMA warp, 2 x 8 softmax warps
 constexpr int kFwdSlots = 6;      // ring of K and V tiles
-constexpr int kFwdSmem = 1024 + kTileBytes * (2 + kFwdSlots) + 256;
+constexpr int kFwdSmem = 1024 + kTileBytes * (4 + kFwdSlots) + 256;
 
 struct FwdBarriers {
     uint32_t base;
-    __device__ uint32_t q_full() const { return base; }
-    __device__ uint32_t q_empty() const { return base + 8; }
-    __device__ uint32_t s_full(int t) const { return base + 16 + 8u * t; }
-    __device__ uint32_t p_ready(int t) const { return base + 32 + 8u * t; }
-    __device__ uint32_t o_full(int t) const { return base + 48 + 8u * t; }
-    __device__ uint32_t o_empty(int t) const { return base + 64 + 8u * t; }
-    __device__ uint32_t slot_full(int s) const { return base + 80 + 8u * s; }
-    __device__ uint32_t slot_empty(int s) const { return base + 80 + 8u * (kFwdSlots + s); }
+    __device__ uint32_t q_full(int b) const { return base + 8u * b; }
+    __device__ uint32_t q_empty(int b) const { return base + 16 + 8u * b; }
+    __device__ uint32_t s_full(int b) const { return base + 32 + 8u * b; }
+    __device__ uint32_t p_ready(int b) const { return base + 56 + 8u * b; }
+    __device__ uint32_t pv_done(int t) const { return base + 80 + 8u * t; }
+    __device__ uint32_t slot_full(int s) const { return base + 96 + 8u * s; }
+    __device__ uint32_t slot_empty(int s) const { return base + 96 + 8u * (kFwdSlots + s); }
+};
+
+// Where a role stands in the CTA's sequence of steps: item number `round` of this CTA,
+// key tile j of the item, query tile t.
+struct FwdCursor {
+    int round, j, t;
+    int qb;      // the item's query tile (it has qb + 1 key tiles); -1 past the last item
+    int pair;    // which pair of heads
 };
 
 __global__ void __launch_bounds__(kFwdThreads, 1)
     fb_attention_forward(const __grid_constant__ AttnParams p) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base = (sm100::smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t q_tiles = base;                       // tile 0 then tile 1
-    const uint32_t ring = base + 2 * kTileBytes;
+    const uint32_t q_tiles = base;                       // [item parity][tile]
+    const uint32_t ring = base + 4 * kTileBytes;
     const FwdBarriers bar{ring + kFwdSlots * kTileBytes};
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
@@ -216,8 +231,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x / 32), 0);
     const int lane = threadIdx.x % 32;
     const int bh_count = p.heads * p.seqs;
-    const int pairs = (p.blocks + 1) / 2;
-    const int items = bh_count * pairs;
+    const int head_pairs = (bh_count + 1) / 2;
+    const int items = p.blocks * head_pairs;
     const int first_item = static_cast<int>(blockIdx.x);
     const int stride = static_cast<int>(gridDim.x);
     // Rounds of gridDim.x items, dealt alternately in ascending and descending CTA order.
@@ -225,18 +240,38 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
         const int slot = (round & 1) != 0 ? stride - 1 - first_item : first_item;
         return round * stride + slot;
     };
-    // An item's first query tile; its second one is the next tile, if the sequence has it.
-    auto first_tile = [&](int item) { return 2 * (pairs - 1 - item / bh_count); };
+    // The cursor at the first step of this CTA's item number `round` (the divisions are
+    // done here, once per item, not in the roles' inner loops).
+    auto enter = [&](int round) {
+        const int item = item_of(round);
+        FwdCursor c{round, 0, 0, -1, 0};
+        if (item < items) {
+            c.qb = p.blocks - 1 - item / head_pairs;
+            c.pair = item % head_pairs;
+        }
+        return c;
+    };
+    auto valid = [](const FwdCursor& c) { return c.qb >= 0; };
+    // The (sequence, head) a tile of the item works on. With an odd number of heads in all,
+    // the last item's second tile repeats the first one's head and stores nothing.
+    auto head_of = [&](const FwdCursor& c, int t) { return min(2 * c.pair + t, bh_count - 1); };
+    auto advance = [&](FwdCursor& c) {
+        c.t ^= 1;
+        if (c.t == 0 && ++c.j > c.qb) {
+            c = enter(c.round + 1);
+        }
+    };
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
-        sm100::mbar_init(bar.q_full(), 1);
-        sm100::mbar_init(bar.q_empty(), 1);
-        for (int t = 0; t < 2; ++t) {
-            sm100::mbar_init(bar.s_full(t), 1);
-            sm100::mbar_init(bar.p_ready(t), 8);   // one arrival per softmax warp
-            sm100::mbar_init(bar.o_full(t), 1);
-            sm100::mbar_init(bar.o_empty(t), 8);
+        for (int b = 0; b < 2; ++b) {
+            sm100::mbar_init(bar.q_full(b), 1);
+            sm100::mbar_init(bar.q_empty(b), 1);
+            sm100::mbar_init(bar.pv_done(b), 1);
+        }
+        for (int b = 0; b < 3; ++b) {
+            sm100::mbar_init(bar.s_full(b), 1);
+            sm100::mbar_init(bar.p_ready(b), 8);   // one arrival per softmax warp of the tile
         }
         for (int s = 0; s < kFwdSlots; ++s) {
             sm100::mbar_init(bar.slot_full(s), 1);
@@ -251,8 +286,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     __syncthreads();
     sm100::tc_fence_after_sync();
     const uint32_t tmem = tmem_slot;
-    auto tmem_s = [&](int t) { return tmem + 128u * t; };
-    auto tmem_o = [&](int t) { return tmem + 256u + 64u * t; };
+    const uint32_t tmem_o = tmem + 384;   // + 64 t
     volatile int* abort = &abort_flag;
     fb::dependency_wait();
 
@@ -261,37 +295,45 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
             int slot = 0;
             uint32_t phase = 0;
             bool ok = true;
-            int round = 0;
-            for (int item = item_of(0); ok && item < items; item = item_of(++round)) {
-                const int bh = item % bh_count;
-                const int head = bh % p.heads;
-                const int seq = bh / p.heads;
-                const int qb = first_tile(item);
-                const bool second = qb + 1 < p.blocks;
-                const int steps = second ? qb + 2 : qb + 1;
-                if (round > 0 && !sm100::mbar_wait(bar.q_empty(), (round - 1) & 1, abort)) {
-                    break;
+            auto load = [&](const CUtensorMap* map, const FwdCursor& c) {
+                if (!sm100::mbar_wait(bar.slot_empty(slot), phase ^ 1u, abort)) {
+                    ok = false;
+                    return;
                 }
-                sm100::mbar_expect_tx(bar.q_full(), second ? 2 * kTileBytes : kTileBytes);
-                tma_load_4d(q_tiles, &p.map_q, bar.q_full(), 0, qb * kTile, head, seq);
-                if (second) {
-                    tma_load_4d(q_tiles + kTileBytes, &p.map_q, bar.q_full(), 0, (qb + 1) * kTile,
-                                head, seq);
+                const int bh = head_of(c, c.t);
+                sm100::mbar_expect_tx(bar.slot_full(slot), kTileBytes);
+                tma_load_4d(ring + slot * kTileBytes, map, bar.slot_full(slot), 0, c.j * kTile,
+                            bh % p.heads, bh / p.heads);
+                if (++slot == kFwdSlots) {
+                    slot = 0;
+                    phase ^= 1u;
                 }
-                for (int j = 0; ok && j < steps; ++j) {
-                    for (int which = 0; which < 2; ++which) {
-                        if (!sm100::mbar_wait(bar.slot_empty(slot), phase ^ 1u, abort)) {
-                            ok = false;
+            };
+            FwdCursor keys = enter(0);     // the next K tile to fetch
+            FwdCursor values = enter(0);   // the next V tile, three steps behind
+            for (int ahead = 0; ok && valid(values); ++ahead) {
+                if (ahead >= 3) {
+                    load(&p.map_v, values);
+                    advance(values);
+                }
+                if (ok && valid(keys)) {
+                    if (keys.j == 0 && keys.t == 0) {
+                        // A new item: its two query tiles go into the buffer of its parity,
+                        // free once the item two rounds back has issued its last scores.
+                        const int b = keys.round & 1;
+                        if (keys.round >= 2 &&
+                            !sm100::mbar_wait(bar.q_empty(b), ((keys.round >> 1) - 1) & 1, abort)) {
                             break;
                         }
-                        sm100::mbar_expect_tx(bar.slot_full(slot), kTileBytes);
-                        tma_load_4d(ring + slot * kTileBytes, which == 0 ? &p.map_k : &p.map_v,
-                                    bar.slot_full(slot), 0, j * kTile, head, seq);
-                        if (++slot == kFwdSlots) {
-                            slot = 0;
-                            phase ^= 1u;
+                        sm100::mbar_expect_tx(bar.q_full(b), 2 * kTileBytes);
+                        for (int t = 0; t < 2; ++t) {
+                            const int bh = head_of(keys, t);
+                            tma_load_4d(q_tiles + (2 * b + t) * kTileBytes, &p.map_q, bar.q_full(b), 0,
+                                        keys.qb * kTile, bh % p.heads, bh / p.heads);
                         }
                     }
+                    load(&p.map_k, keys);
+                    advance(keys);
                 }
             }
         }
@@ -299,142 +341,92 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
         // The whole warp runs this loop, so that its state stays warp-uniform (the MMA's
         // descriptors then need no per-thread to uniform register moves); one elected lane
         // issues.
-        {
-            int slot = 0;
-            uint32_t phase = 0;
-            uint32_t scored[2] = {0, 0};   // key tiles processed per query tile, over all items
-            uint32_t drained[2] = {0, 0};  // items finished per query tile
-            bool ok = true;
-            // Waits for the ring's next tile and returns its address (0 after an abort).
-            auto next_tile = [&]() -> uint32_t {
-                if (!sm100::mbar_wait(bar.slot_full(slot), phase, abort)) {
-                    return 0u;
-                }
-                sm100::tc_fence_after_sync();
-                return ring + slot * kTileBytes;
-            };
-            auto release_tile = [&]() {
-                if (sm100::elect_one()) {
-                    sm100::mma_commit(bar.slot_empty(slot));
-                }
-                __syncwarp();
-                if (++slot == kFwdSlots) {
-                    slot = 0;
-                    phase ^= 1u;
-                }
-            };
-            const uint64_t q_desc[2] = {desc_kmajor(q_tiles, 0), desc_kmajor(q_tiles + kTileBytes, 0)};
-            const uint32_t s_at[2] = {tmem_s(0), tmem_s(1)};
-            const uint32_t o_at[2] = {tmem_o(0), tmem_o(1)};
-            auto scores = [&](int t, uint32_t k_tile) {
-                const uint64_t k_desc = desc_kmajor(k_tile, 0);
-                if (sm100::elect_one()) {
-                    sm100::mma_f16_ss_at<0>(s_at[t], q_desc[t], 0, k_desc, 0, kIdescS);
-                    sm100::mma_f16_ss_at<1>(s_at[t], q_desc[t], 2, k_desc, 2, kIdescS);
-                    sm100::mma_f16_ss_at<1>(s_at[t], q_desc[t], 4, k_desc, 4, kIdescS);
-                    sm100::mma_f16_ss_at<1>(s_at[t], q_desc[t], 6, k_desc, 6, kIdescS);
-                    sm100::mma_commit(bar.s_full(t));
-                }
-                __syncwarp();
-            };
-            // O_t (+)= P_t V once the tile's probabilities are in tensor memory; keys
-            // 64 half + [0, 64) sit in columns 64 half + [0, 32) of the score accumulator.
-            auto weighted = [&](int t, uint32_t v_tile, int j, bool last) -> bool {
-                if (!sm100::mbar_wait(bar.p_ready(t), scored[t] & 1, abort)) {
-                    return false;
-                }
-                ++scored[t];
-                if (j == 0 && drained[t] > 0 &&
-                    !sm100::mbar_wait(bar.o_empty(t), (drained[t] - 1) & 1, abort)) {
-                    return false;
-                }
-                sm100::tc_fence_after_sync();
-                // An MN-major step of 16 keys is 2,048 bytes.
-                const uint64_t v_desc = desc_mnmajor(v_tile, 0, 16);
-                if (sm100::elect_one()) {
-                    sm100::mma_f16_ts_at<-1>(o_at[t], s_at[t], v_desc, 0, kIdescPV, j > 0);
-#pragma unroll
-                    for (int ks = 1; ks < 8; ++ks) {
-                        sm100::mma_f16_ts_at<1>(o_at[t], s_at[t] + (ks >> 2) * 64 + (ks & 3) * 8,
-                                                v_desc, ks * 128, kIdescPV);
-                    }
-                    if (last) {
-                        sm100::mma_commit(bar.o_full(t));
-                    }
-                }
-                __syncwarp();
-                if (last) {
-                    ++drained[t];
-                }
-                return true;
-            };
-            int round = 0;
-            for (int item = item_of(0); ok && item < items; item = item_of(++round)) {
-                const int qb = first_tile(item);
-                const bool second = qb + 1 < p.blocks;
-                const int steps0 = qb + 1;
-                const int steps = second ? qb + 2 : qb + 1;
-                if (!sm100::mbar_wait(bar.q_full(), round & 1, abort)) {
-                    break;
-                }
-                uint32_t k_tile = next_tile();
-                if (k_tile == 0) {
-                    break;
-                }
-                scores(0, k_tile);
-                if (second) {
-                    scores(1, k_tile);
-                }
-                release_tile();
-                for (int j = 0; ok && j < steps; ++j) {
-                    const uint32_t v_tile = next_tile();
-                    if (v_tile == 0) {
-                        ok = false;
-                        break;
-                    }
-                    const int v_slot = slot;
-                    // The V tile is released after both tiles' P V; the ring's cursor moves
-                    // on to the next K tile meanwhile.
-                    if (++slot == kFwdSlots) {
-                        slot = 0;
-                        phase ^= 1u;
-                    }
-                    if (j < steps0 && !weighted(0, v_tile, j, j + 1 == steps0)) {
-                        ok = false;
-                        break;
-                    }
-                    k_tile = 0;
-                    if (j + 1 < steps) {
-                        k_tile = next_tile();
-                        if (k_tile == 0) {
-                            ok = false;
-                            break;
-                        }
-                        if (j + 1 < steps0) {
-                            scores(0, k_tile);
-                        }
-                    }
-                    if (second && !weighted(1, v_tile, j, j + 1 == steps)) {
-                        ok = false;
-                        break;
-                    }
-                    if (sm100::elect_one()) {
-                        sm100::mma_commit(bar.slot_empty(v_slot));
-                    }
-                    __syncwarp();
-                    if (j + 1 < steps) {
-                        if (second) {
-                            scores(1, k_tile);
-                        }
-                        release_tile();
-                    }
-                }
-                // Every MMA that reads the query tiles has been issued.
-                if (sm100::elect_one()) {
-                    sm100::mma_commit(bar.q_empty());
-                }
-                __syncwarp();
+        int slot = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        // Waits for the ring's next tile and returns its address (0 after an abort).
+        auto next_tile = [&]() -> uint32_t {
+            if (!sm100::mbar_wait(bar.slot_full(slot), phase, abort)) {
+                ok = false;
+                return 0u;
             }
+            sm100::tc_fence_after_sync();
+            return ring + slot * kTileBytes;
+        };
+        // To be called by the elected lane after the MMAs that read the tile.
+        auto release_tile = [&]() { sm100::mma_commit(bar.slot_empty(slot)); };
+        auto step_ring = [&]() {
+            if (++slot == kFwdSlots) {
+                slot = 0;
+                phase ^= 1u;
+            }
+        };
+        FwdCursor ahead = enter(0);   // the next scores to issue
+        uint32_t issued = 0;        // their step number
+        auto issue_scores = [&]() {
+            if (!ok || !valid(ahead)) {
+                return;
+            }
+            const int b = ahead.round & 1;
+            if (ahead.j == 0 && ahead.t == 0 &&
+                !sm100::mbar_wait(bar.q_full(b), (ahead.round >> 1) & 1, abort)) {
+                ok = false;
+                return;
+            }
+            const uint32_t k_tile = next_tile();
+            if (k_tile == 0) {
+                return;
+            }
+            const uint64_t q_desc = desc_kmajor(q_tiles + (2 * b + ahead.t) * kTileBytes, 0);
+            const uint64_t k_desc = desc_kmajor(k_tile, 0);
+            const uint32_t s_at = tmem + 128u * (issued % 3);
+            const bool last_of_item = ahead.t == 1 && ahead.j == ahead.qb;
+            if (sm100::elect_one()) {
+                sm100::mma_f16_ss_at<0>(s_at, q_desc, 0, k_desc, 0, kIdescS);
+                sm100::mma_f16_ss_at<1>(s_at, q_desc, 2, k_desc, 2, kIdescS);
+                sm100::mma_f16_ss_at<1>(s_at, q_desc, 4, k_desc, 4, kIdescS);
+                sm100::mma_f16_ss_at<1>(s_at, q_desc, 6, k_desc, 6, kIdescS);
+                sm100::mma_commit(bar.s_full(issued % 3));
+                release_tile();
+                if (last_of_item) {
+                    sm100::mma_commit(bar.q_empty(b));
+                }
+            }
+            __syncwarp();
+            step_ring();
+            ++issued;
+            advance(ahead);
+        };
+        issue_scores();
+        issue_scores();
+        issue_scores();
+        uint32_t n = 0;
+        for (FwdCursor at = enter(0); ok && valid(at); advance(at), ++n) {
+            if (!sm100::mbar_wait(bar.p_ready(n % 3), (n / 3) & 1, abort)) {
+                break;
+            }
+            const uint32_t v_tile = next_tile();
+            if (v_tile == 0) {
+                break;
+            }
+            // O(tile) (+)= P V; keys 64 half + [0, 64) sit in columns 64 half + [0, 32) of
+            // the score buffer. An MN-major step of 16 keys is 2,048 bytes.
+            const uint64_t v_desc = desc_mnmajor(v_tile, 0, 16);
+            const uint32_t p_at = tmem + 128u * (n % 3);
+            const uint32_t o_at = tmem_o + 64u * at.t;
+            if (sm100::elect_one()) {
+                sm100::mma_f16_ts_at<-1>(o_at, p_at, v_desc, 0, kIdescPV, at.j > 0);
+#pragma unroll
+                for (int ks = 1; ks < 8; ++ks) {
+                    sm100::mma_f16_ts_at<1>(o_at, p_at + (ks >> 2) * 64 + (ks & 3) * 8, v_desc,
+                                            ks * 128, kIdescPV);
+                }
+                sm100::mma_commit(bar.pv_done(at.t));
+                release_tile();
+            }
+            __syncwarp();
+            step_ring();
+            issue_scores();   // into the buffer this P V frees
         }
     } else {
         // Two threads per query row: this one owns score columns [64 half, 64 half + 64)
@@ -444,33 +436,27 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
         const int half = ((warp - 2) % 8) / 4;
         const int row = quadrant * 32 + lane;
         const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
-        const uint32_t my_scores = tmem_s(tile) + lane_base + half * 64;
-        const uint32_t my_output = tmem_o(tile) + lane_base + half * 32;
+        const uint32_t my_output = tmem_o + 64u * tile + lane_base + half * 32;
         const int pair_barrier = tile * 4 + quadrant;
         const float scale2 = p.scale * kLog2e;
         const fb::F2 scale_pair = fb::f2_pack(scale2, scale2);
-        uint32_t scored = 0;   // key tiles processed, over all items
-        uint32_t drained = 0;  // items finished
+        uint32_t before = 0;   // key tiles of this CTA's earlier items
         bool ok = true;
-        int round = 0;
-        for (int item = item_of(0); ok && item < items; item = item_of(++round)) {
-            const int bh = item % bh_count;
-            const int head = bh % p.heads;
-            const int seq = bh / p.heads;
-            const int qb = first_tile(item) + tile;
-            if (qb >= p.blocks) {
-                continue;   // the sequence has no second tile in its last pair
-            }
+        for (FwdCursor item = enter(0); ok && valid(item); item = enter(item.round + 1)) {
+            const int qb = item.qb;
+            const int bh = head_of(item, tile);
+            const bool stores = 2 * item.pair + tile < bh_count;
             const int q_index = qb * kTile + row;
             float m = -INFINITY;  // reference exponent of the row (base 2), shared by the pair
             fb::F2 l = 0;         // this thread's share of the row sum, in two partial sums
             for (int j = 0; ok && j <= qb; ++j) {
-                if (!sm100::mbar_wait(bar.s_full(tile), scored & 1, abort)) {
+                const uint32_t n = 2 * (before + j) + tile;   // this step's number
+                if (!sm100::mbar_wait(bar.s_full(n % 3), (n / 3) & 1, abort)) {
                     ok = false;
                     break;
                 }
-                const int parity = scored & 1;
-                ++scored;
+                const int parity = j & 1;
+                const uint32_t my_scores = tmem + 128u * (n % 3) + lane_base + half * 64;
                 sm100::tc_fence_after_sync();
                 uint32_t raw[64];
                 sm100::tmem_ld_32x32(my_scores, reinterpret_cast<uint32_t(&)[32]>(raw[0]));
@@ -514,8 +500,13 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
                     l = fb::f2_mul(l, fb::f2_pack(alpha, alpha));
                 }
                 if (j > 0 && __any_sync(0xffffffffu, moved)) {
-                    // The previous key tile's P V has finished: the score commit that was
-                    // just waited for covers every earlier MMA of the issuing thread.
+                    // The previous key tile's P V must have finished (it cannot be more than
+                    // one behind: the next one needs this step's probabilities).
+                    if (!sm100::mbar_wait(bar.pv_done(tile), (before + j - 1) & 1, abort)) {
+                        ok = false;
+                        break;
+                    }
+                    sm100::tc_fence_after_sync();
                     const fb::F2 a2 = fb::f2_pack(alpha, alpha);
 #pragma unroll 1
                     for (int c = 0; c < 2; ++c) {
@@ -561,35 +552,34 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
                 sm100::tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) {
-                    sm100::mbar_arrive(bar.p_ready(tile));
+                    sm100::mbar_arrive(bar.p_ready(n % 3));
                 }
             }
-            if (!ok || !sm100::mbar_wait(bar.o_full(tile), drained & 1, abort)) {
+            if (!ok || !sm100::mbar_wait(bar.pv_done(tile), (before + qb) & 1, abort)) {
                 ok = false;
                 break;
             }
-            ++drained;
+            before += qb + 1;
             sm100::tc_fence_after_sync();
             uint32_t acc[32];
             sm100::tmem_ld_32x32(my_output, acc);
             sm100::tmem_ld_wait();
-            // The accumulator is free for the next item's first P V.
+            // The accumulator is overwritten by the next item's first P V, which needs the
+            // probabilities this thread writes after it has got here.
             sm100::tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) {
-                sm100::mbar_arrive(bar.o_empty(tile));
-            }
             // The row sum is the two threads' shares added together.
             float l_lo, l_hi;
             fb::f2_unpack(l, l_lo, l_hi);
             const float mine = l_lo + l_hi;
-            const int parity = scored & 1;   // the slot the next key tile will use is idle now
+            const int parity = (qb + 1) & 1;   // not the slot the last key tile used
             pair_max[tile][parity][half][row] = mine;
             quadrant_sync(pair_barrier);
             const float total = mine + pair_max[tile][parity][half ^ 1][row];
             quadrant_sync(pair_barrier);     // both have read before either writes a maximum there
-            if (q_index < p.length) {
+            if (stores && q_index < p.length) {
                 const float inv = 1.0f / total;
+                const int head = bh % p.heads;
+                const int seq = bh / p.heads;
                 __half* out = static_cast<__half*>(p.out0) + seq * p.out_seq + head * p.out_head +
                               static_cast<long long>(q_index) * p.out_row + half * 32;
 #pragma unroll
@@ -1430,7 +1420,7 @@ cudaError_t attention_forward(const AttentionView& o, float* lse, const Attentio
     }
     int sms = 148;
     sm_count(&sms);
-    const long long items = static_cast<long long>(shape.sequences * shape.heads) * ((p.blocks + 1) / 2);
+    const long long items = static_cast<long long>((shape.sequences * shape.heads + 1) / 2) * p.blocks;
     const unsigned grid = static_cast<unsigned>(std::min<long long>(items, sms));
     return fb::launch_dependent(fb_attention_forward, dim3(grid), dim3(kFwdThreads), kFwdSmem, stream,
                                 p);
