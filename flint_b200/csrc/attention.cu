@@ -195,7 +195,7 @@ __device__ __forceinline__ void finish(int abort_value, uint32_t tmem_base, uint
 // Tensor memory: score buffers at 0, 128, 256; O of tile 0 at 384, of tile 1 at 448.
 
 constexpr int kFwdThreads = 576;  // TMA warp, MMA warp, 2 x 8 softmax warps
-constexpr int kFwdSlots = 6;      // ring of K and V tiles
+constexpr int kFwdSlots = 8;      // ring of K and V tiles
 constexpr int kFwdSmem = 1024 + kTileBytes * (4 + kFwdSlots) + 256;
 
 struct FwdBarriers {
@@ -555,7 +555,10 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
                     sm100::mbar_arrive(bar.p_ready(n % 3));
                 }
             }
-            if (!ok || !sm100::mbar_wait(bar.pv_done(tile), (before + qb) & 1, abort)) {
+            // A parity wait is only right when at most one phase is outstanding, and the MMA
+            // warp may be two P V behind here: wait for the last but one first.
+            if (!ok || (qb > 0 && !sm100::mbar_wait(bar.pv_done(tile), (before + qb - 1) & 1, abort)) ||
+                !sm100::mbar_wait(bar.pv_done(tile), (before + qb) & 1, abort)) {
                 ok = false;
                 break;
             }
