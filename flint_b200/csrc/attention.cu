@@ -664,7 +664,9 @@ __global__ void __launch_bounds__(256)
 // operands per instruction and is bound by the shared-memory rate (measured 49
 // clocks against 32 of tensor work), and the P/dS stores shared the same banks.
 
-constexpr int kBwdThreads = 320;  // TMA warp, MMA warp, 8 compute warps
+constexpr int kBwdThreads = 576;  // TMA warp, MMA warp, 16 compute warps
+constexpr int kPart = 16;         // accumulator columns per compute thread and sub-step
+constexpr int kBwdComputeWarps = 16;
 constexpr int kSub = 64;          // streamed rows (queries for dK/dV, keys for dQ) per sub-step
 constexpr int kSubBytes = kSub * kHead * 2;  // 8 KB: one streamed tile
 constexpr int kBwdStages = 4;
@@ -690,13 +692,14 @@ struct BwdBarriers {
     __device__ uint32_t stage_empty(int s) const { return base + 96 + 8u * s; }
 };
 
-__device__ __forceinline__ void init_bwd_barriers(const BwdBarriers& b, int compute_threads) {
+// The compute warps arrive once per warp (after __syncwarp, by lane 0).
+__device__ __forceinline__ void init_bwd_barriers(const BwdBarriers& b) {
     sm100::mbar_init(b.resident(), 1);
     sm100::mbar_init(b.done(), 1);
-    sm100::mbar_init(b.a_ready(), compute_threads);
+    sm100::mbar_init(b.a_ready(), kBwdComputeWarps);
     for (int i = 0; i < 2; ++i) {
         sm100::mbar_init(b.scores_full(i), 1);
-        sm100::mbar_init(b.operands_ready(i), compute_threads);
+        sm100::mbar_init(b.operands_ready(i), kBwdComputeWarps);
     }
     for (int s = 0; s < kBwdStages; ++s) {
         sm100::mbar_init(b.stage_full(s), 1);
@@ -705,26 +708,36 @@ __device__ __forceinline__ void init_bwd_barriers(const BwdBarriers& b, int comp
     sm100::mbar_fence_init();
 }
 
-// Copies this thread's row of a resident 128 x 64 FP16 tile (swizzled as TMA wrote it)
-// into tensor memory as an A operand: the 32 head columns [32 part, 32 part + 32)
-// become 16 columns of FP16 pairs at `dst` + 16 part.
+// Copies this thread's share of a row of a resident 128 x 64 FP16 tile (swizzled as TMA
+// wrote it) into tensor memory as an A operand: the 16 head columns [16 part, 16 part + 16)
+// become 8 columns of FP16 pairs at `dst` + 8 part.
 __device__ __forceinline__ void tile_row_to_tmem(uint32_t dst, uint32_t tile, int row, int part) {
-    uint32_t r[16];
+    uint32_t r[8];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int chunk = part * 4 + i;
+    for (int i = 0; i < 2; ++i) {
+        const int chunk = part * 2 + i;
         asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
                      : "=r"(r[4 * i]), "=r"(r[4 * i + 1]), "=r"(r[4 * i + 2]), "=r"(r[4 * i + 3])
                      : "r"(tile + row * 128 + ((chunk ^ (row & 7)) << 4)));
     }
-    sm100::tmem_st_32x16(dst + 16 * part, r);
+    sm100::tmem_st_32x8(dst + 8 * part, r);
 }
 
-// 32 FP32 values -> 16 words of FP16 pairs (the lower-indexed value in the low half).
-__device__ __forceinline__ void pack_pairs(uint32_t (&w)[16], const float (&v)[32]) {
+// 16 FP32 values -> 8 words of FP16 pairs (the lower-indexed value in the low half).
+__device__ __forceinline__ void pack_pairs(uint32_t (&w)[8], const float (&v)[kPart]) {
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
+    for (int i = 0; i < 8; ++i) {
         w[i] = fb::pack2(v[2 * i], v[2 * i + 1]);
+    }
+}
+
+// One arrival for the warp, after every lane's tensor-memory stores have completed.
+__device__ __forceinline__ void warp_arrive_after_stores(uint32_t bar, int lane) {
+    sm100::tmem_st_wait();
+    sm100::tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) {
+        sm100::mbar_arrive(bar);
     }
 }
 
@@ -747,7 +760,7 @@ __device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) 
 // their last sub-step, and the MMA warp issues the next item's first score MMAs while the
 // compute warps write this item's dK/dV out. Barrier phases and the tile ring simply
 // continue from item to item (an item has an even number of sub-steps).
-// Tensor memory: S^T at 0/64, dP^T at 128/192 (P^T and dS^T overwrite 16 + 16 columns of
+// Tensor memory: S^T at 0/64, dP^T at 128/192 (P^T and dS^T overwrite 4 x 8 columns of
 // each), dV 256, dK 320, K 384, V 416.
 
 __global__ void __launch_bounds__(kBwdThreads, 1)
@@ -778,7 +791,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
-        init_bwd_barriers(bar, 256);
+        init_bwd_barriers(bar);
     }
     if (warp == 1) {
         sm100::tmem_alloc(sm100::smem_u32(&tmem_slot), 512);
@@ -901,17 +914,17 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                     const uint64_t q_sub = desc_advance(q_desc, stage * 2 * kSubBytes);
                     const uint64_t do_sub = desc_advance(do_desc, stage * 2 * kSubBytes);
                     // dV += P^T dO and dK += dS^T Q over this sub-step's 64 queries; queries
-                    // 32 part + [0, 32) sit in columns 32 part + [0, 16) of the accumulator.
+                    // 16 part + [0, 16) sit in columns 16 part + [0, 8) of the accumulator.
                     if (sm100::elect_one()) {
                         const uint32_t st_at = tmem_st(b), dpt_at = tmem_dpt(b);
                         sm100::mma_f16_ts_at<-1>(tmem_dv, st_at, do_sub, 0, kIdescPV, h != 0);
-                        sm100::mma_f16_ts_at<1>(tmem_dv, st_at + 8, do_sub, 128, kIdescPV);
+                        sm100::mma_f16_ts_at<1>(tmem_dv, st_at + 16, do_sub, 128, kIdescPV);
                         sm100::mma_f16_ts_at<1>(tmem_dv, st_at + 32, do_sub, 256, kIdescPV);
-                        sm100::mma_f16_ts_at<1>(tmem_dv, st_at + 40, do_sub, 384, kIdescPV);
+                        sm100::mma_f16_ts_at<1>(tmem_dv, st_at + 48, do_sub, 384, kIdescPV);
                         sm100::mma_f16_ts_at<-1>(tmem_dk, dpt_at, q_sub, 0, kIdescPV, h != 0);
-                        sm100::mma_f16_ts_at<1>(tmem_dk, dpt_at + 8, q_sub, 128, kIdescPV);
+                        sm100::mma_f16_ts_at<1>(tmem_dk, dpt_at + 16, q_sub, 128, kIdescPV);
                         sm100::mma_f16_ts_at<1>(tmem_dk, dpt_at + 32, q_sub, 256, kIdescPV);
-                        sm100::mma_f16_ts_at<1>(tmem_dk, dpt_at + 40, q_sub, 384, kIdescPV);
+                        sm100::mma_f16_ts_at<1>(tmem_dk, dpt_at + 48, q_sub, 384, kIdescPV);
                         sm100::mma_commit(bar.stage_empty(stage));
                         if (h + 1 == steps) {
                             sm100::mma_commit(bar.done());
@@ -924,7 +937,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         }
     } else {
         const int quadrant = warp % 4;
-        const int part = (warp - 2) / 4;                 // which 32 of the 64 query columns
+        const int part = (warp - 2) / 4;                 // which 16 of the 64 query columns
         const int row = quadrant * 32 + lane;            // key row inside the tile
         const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
         const float scale2 = p.scale * kLog2e;
@@ -936,9 +949,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             }
             tile_row_to_tmem(tmem_k + lane_base, k_tile, row, part);
             tile_row_to_tmem(tmem_v + lane_base, v_tile, row, part);
-            sm100::tmem_st_wait();
-            sm100::tc_fence_before_sync();
-            sm100::mbar_arrive(bar.a_ready());
+            warp_arrive_after_stores(bar.a_ready(), lane);
             return true;
         };
         uint32_t before = 0;
@@ -955,7 +966,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                 const int b = h & 1;
                 const uint32_t count = before + h;
                 const int stage = count % kBwdStages;
-                const int q0 = kb * kTile + h * kSub + part * 32;  // first query of my columns
+                const int q0 = kb * kTile + h * kSub + part * kPart;  // first query of my columns
                 // stage_full covers the statistics; scores_full the two accumulators (and,
                 // the tensor pipe being in order, that the MMAs which read this pair's
                 // previous P^T and dS^T have finished).
@@ -965,16 +976,18 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                     break;
                 }
                 sm100::tc_fence_after_sync();
-                uint32_t s_raw[32];
-                uint32_t dp_raw[32];
-                sm100::tmem_ld_32x32(tmem_st(b) + lane_base + part * 32, s_raw);
-                sm100::tmem_ld_32x32(tmem_dpt(b) + lane_base + part * 32, dp_raw);
-                // My 32 queries' statistics: every lane reads the same addresses (broadcast).
-                const uint32_t stat = stats + stage * 2 * kStatBytes + part * 128;
-                float lse2[32];
-                float dlt[32];
+                const uint32_t my_scores = tmem_st(b) + lane_base + part * kPart;
+                const uint32_t my_weights = tmem_dpt(b) + lane_base + part * kPart;
+                uint32_t s_raw[kPart];
+                uint32_t dp_raw[kPart];
+                sm100::tmem_ld_32x16(my_scores, s_raw);
+                sm100::tmem_ld_32x16(my_weights, dp_raw);
+                // My 16 queries' statistics: every lane reads the same addresses (broadcast).
+                const uint32_t stat = stats + stage * 2 * kStatBytes + part * kPart * 4;
+                float lse2[kPart];
+                float dlt[kPart];
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
+                for (int c = 0; c < kPart / 4; ++c) {
                     float a0, a1, a2, a3;
                     asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
                                  : "=f"(a0), "=f"(a1), "=f"(a2), "=f"(a3)
@@ -989,15 +1002,15 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                                  : "r"(stat + kStatBytes + c * 16));
                 }
                 sm100::tmem_ld_wait();
-                float pv[32];
-                float dsv[32];
+                float pv[kPart];
+                float dsv[kPart];
                 if (h < 2 || kb * kTile + (h + 1) * kSub > p.length) {
                     // The diagonal tile (a key is visible to the queries at or after it) or
                     // a sub-step with absent queries, whose statistics slots were not
                     // filled: both tests select rather than multiply.
                     const int first_visible = h < 2 ? k_index : 0;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
+                    for (int i = 0; i < kPart; ++i) {
                         const bool visible = first_visible <= q0 + i && q0 + i < p.length;
                         const float e =
                             fast_exp2(fmaf(__uint_as_float(s_raw[i]), scale2, -lse2[i]));
@@ -1006,20 +1019,18 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                     }
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
+                    for (int i = 0; i < kPart; ++i) {
                         pv[i] = fast_exp2(fmaf(__uint_as_float(s_raw[i]), scale2, -lse2[i]));
                         dsv[i] = pv[i] * (__uint_as_float(dp_raw[i]) - dlt[i]);
                     }
                 }
-                // P^T and dS^T go back over the first 16 of the 32 columns this warp read.
-                uint32_t packed[16];
+                // P^T and dS^T go back over the first 8 of the 16 columns this thread read.
+                uint32_t packed[8];
                 pack_pairs(packed, pv);
-                sm100::tmem_st_32x16(tmem_st(b) + lane_base + part * 32, packed);
+                sm100::tmem_st_32x8(my_scores, packed);
                 pack_pairs(packed, dsv);
-                sm100::tmem_st_32x16(tmem_dpt(b) + lane_base + part * 32, packed);
-                sm100::tmem_st_wait();
-                sm100::tc_fence_before_sync();
-                sm100::mbar_arrive(bar.operands_ready(b));
+                sm100::tmem_st_32x8(my_weights, packed);
+                warp_arrive_after_stores(bar.operands_ready(b), lane);
             }
             before += steps;
             if (!ok) {
@@ -1036,20 +1047,20 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                 break;
             }
             sm100::tc_fence_after_sync();
-            // Rows of dV/dK are keys; this warp writes 32 of the 64 columns. dS was kept
+            // Rows of dV/dK are keys; this thread writes 16 of the 64 columns. dS was kept
             // unscaled, so the score scale is applied to dK here.
-            uint32_t dv_raw[32];
-            uint32_t dk_raw[32];
-            sm100::tmem_ld_32x32(tmem_dv + lane_base + part * 32, dv_raw);
-            sm100::tmem_ld_32x32(tmem_dk + lane_base + part * 32, dk_raw);
+            uint32_t dv_raw[kPart];
+            uint32_t dk_raw[kPart];
+            sm100::tmem_ld_32x16(tmem_dv + lane_base + part * kPart, dv_raw);
+            sm100::tmem_ld_32x16(tmem_dk + lane_base + part * kPart, dk_raw);
             sm100::tmem_ld_wait();
             if (k_index < p.length) {
                 const long long at = seq * p.out_seq + head * p.out_head +
-                                     static_cast<long long>(k_index) * p.out_row + part * 32;
+                                     static_cast<long long>(k_index) * p.out_row + part * kPart;
                 __half* dk_out = static_cast<__half*>(p.out0) + at;
                 __half* dv_out = static_cast<__half*>(p.out1) + at;
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
+                for (int c = 0; c < kPart / 8; ++c) {
                     float a[8];
                     float bv[8];
 #pragma unroll
@@ -1108,7 +1119,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
-        init_bwd_barriers(bar, 256);
+        init_bwd_barriers(bar);
     }
     if (warp == 1) {
         sm100::tmem_alloc(sm100::smem_u32(&tmem_slot), 512);
@@ -1215,9 +1226,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                     if (sm100::elect_one()) {
                         const uint32_t dp_at = tmem_dp(b);
                         sm100::mma_f16_ts_at<-1>(tmem_dq, dp_at, k_sub, 0, kIdescPV, g != 0);
-                        sm100::mma_f16_ts_at<1>(tmem_dq, dp_at + 8, k_sub, 128, kIdescPV);
+                        sm100::mma_f16_ts_at<1>(tmem_dq, dp_at + 16, k_sub, 128, kIdescPV);
                         sm100::mma_f16_ts_at<1>(tmem_dq, dp_at + 32, k_sub, 256, kIdescPV);
-                        sm100::mma_f16_ts_at<1>(tmem_dq, dp_at + 40, k_sub, 384, kIdescPV);
+                        sm100::mma_f16_ts_at<1>(tmem_dq, dp_at + 48, k_sub, 384, kIdescPV);
                         sm100::mma_commit(bar.stage_empty(stage));
                         if (g + 1 == steps) {
                             sm100::mma_commit(bar.done());
@@ -1230,7 +1241,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
         }
     } else {
         const int quadrant = warp % 4;
-        const int part = (warp - 2) / 4;                 // which 32 of the 64 key columns
+        const int part = (warp - 2) / 4;                 // which 16 of the 64 key columns
         const int row = quadrant * 32 + lane;            // query row inside the tile
         const uint32_t lane_base = static_cast<uint32_t>(quadrant * 32) << 16;
         const float scale2 = p.scale * kLog2e;
@@ -1241,9 +1252,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
             }
             tile_row_to_tmem(tmem_q + lane_base, q_tile, row, part);
             tile_row_to_tmem(tmem_do + lane_base, do_tile, row, part);
-            sm100::tmem_st_wait();
-            sm100::tc_fence_before_sync();
-            sm100::mbar_arrive(bar.a_ready());
+            warp_arrive_after_stores(bar.a_ready(), lane);
             return true;
         };
         uint32_t before = 0;
@@ -1271,35 +1280,34 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                     break;
                 }
                 sm100::tc_fence_after_sync();
-                uint32_t s_raw[32];
-                uint32_t dp_raw[32];
-                sm100::tmem_ld_32x32(tmem_s(b) + lane_base + part * 32, s_raw);
-                sm100::tmem_ld_32x32(tmem_dp(b) + lane_base + part * 32, dp_raw);
+                const uint32_t my_weights = tmem_dp(b) + lane_base + part * kPart;
+                uint32_t s_raw[kPart];
+                uint32_t dp_raw[kPart];
+                sm100::tmem_ld_32x16(tmem_s(b) + lane_base + part * kPart, s_raw);
+                sm100::tmem_ld_32x16(my_weights, dp_raw);
                 sm100::tmem_ld_wait();
-                const int k0 = g * kSub + part * 32;  // first key of my columns
-                float dsv[32];
+                const int k0 = g * kSub + part * kPart;  // first key of my columns
+                float dsv[kPart];
                 if (g + 2 >= steps) {
                     // The diagonal tile: keys after the query are masked.
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
+                    for (int i = 0; i < kPart; ++i) {
                         const float e = fast_exp2(fmaf(__uint_as_float(s_raw[i]), scale2, -lse2));
                         dsv[i] =
                             (k0 + i <= q_index) ? e * (__uint_as_float(dp_raw[i]) - dlt) : 0.0f;
                     }
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
+                    for (int i = 0; i < kPart; ++i) {
                         const float e = fast_exp2(fmaf(__uint_as_float(s_raw[i]), scale2, -lse2));
                         dsv[i] = e * (__uint_as_float(dp_raw[i]) - dlt);
                     }
                 }
-                // dS goes back over the first 16 of the 32 dP columns this warp just read.
-                uint32_t packed[16];
+                // dS goes back over the first 8 of the 16 dP columns this thread just read.
+                uint32_t packed[8];
                 pack_pairs(packed, dsv);
-                sm100::tmem_st_32x16(tmem_dp(b) + lane_base + part * 32, packed);
-                sm100::tmem_st_wait();
-                sm100::tc_fence_before_sync();
-                sm100::mbar_arrive(bar.operands_ready(b));
+                sm100::tmem_st_32x8(my_weights, packed);
+                warp_arrive_after_stores(bar.operands_ready(b), lane);
             }
             before += steps;
             if (!ok) {
@@ -1314,14 +1322,14 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                 break;
             }
             sm100::tc_fence_after_sync();
-            uint32_t raw[32];
-            sm100::tmem_ld_32x32(tmem_dq + lane_base + part * 32, raw);
+            uint32_t raw[kPart];
+            sm100::tmem_ld_32x16(tmem_dq + lane_base + part * kPart, raw);
             sm100::tmem_ld_wait();
             if (row_valid) {
                 __half* out = static_cast<__half*>(p.out0) + seq * p.out_seq + head * p.out_head +
-                              static_cast<long long>(q_index) * p.out_row + part * 32;
+                              static_cast<long long>(q_index) * p.out_row + part * kPart;
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
+                for (int c = 0; c < kPart / 8; ++c) {
                     float a[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
