@@ -125,6 +125,19 @@ __device__ __forceinline__ void exp2_pair_fma(fb::F2 x, float& lo, float& hi) {
 #define FB_ATTN_FMA_EXP_OF_4 1
 #endif
 
+// Two exponentials; `pair` (a compile-time constant after unrolling) picks the pipe.
+#ifndef FB_ATTN_BWD_FMA_EXP_OF_4
+#define FB_ATTN_BWD_FMA_EXP_OF_4 1
+#endif
+__device__ __forceinline__ void exp2_two(int pair, float x0, float x1, float& e0, float& e1) {
+    if ((pair & 3) < FB_ATTN_BWD_FMA_EXP_OF_4) {
+        exp2_pair_fma(fb::f2_pack(x0, x1), e0, e1);
+    } else {
+        e0 = fast_exp2(x0);
+        e1 = fast_exp2(x1);
+    }
+}
+
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float r;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
@@ -970,8 +983,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                 // stage_full covers the statistics; scores_full the two accumulators (and,
                 // the tensor pipe being in order, that the MMAs which read this pair's
                 // previous P^T and dS^T have finished).
-                if (!sm100::mbar_wait(bar.stage_full(stage), (count / kBwdStages) & 1, abort) ||
-                    !sm100::mbar_wait(bar.scores_full(b), (count >> 1) & 1, abort)) {
+                if (!sm100::mbar_wait(bar.scores_full(b), (count >> 1) & 1, abort)) {
                     ok = false;
                     break;
                 }
@@ -982,6 +994,10 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                 uint32_t dp_raw[kPart];
                 sm100::tmem_ld_32x16(my_scores, s_raw);
                 sm100::tmem_ld_32x16(my_weights, dp_raw);
+                if (!sm100::mbar_wait(bar.stage_full(stage), (count / kBwdStages) & 1, abort)) {
+                    ok = false;
+                    break;
+                }
                 // My 16 queries' statistics: every lane reads the same addresses (broadcast).
                 const uint32_t stat = stats + stage * 2 * kStatBytes + part * kPart * 4;
                 float lse2[kPart];
@@ -1019,9 +1035,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                     }
                 } else {
 #pragma unroll
-                    for (int i = 0; i < kPart; ++i) {
-                        pv[i] = fast_exp2(fmaf(__uint_as_float(s_raw[i]), scale2, -lse2[i]));
+                    for (int i = 0; i < kPart; i += 2) {
+                        exp2_two(i / 2, fmaf(__uint_as_float(s_raw[i]), scale2, -lse2[i]),
+                                 fmaf(__uint_as_float(s_raw[i + 1]), scale2, -lse2[i + 1]), pv[i],
+                                 pv[i + 1]);
                         dsv[i] = pv[i] * (__uint_as_float(dp_raw[i]) - dlt[i]);
+                        dsv[i + 1] = pv[i + 1] * (__uint_as_float(dp_raw[i + 1]) - dlt[i + 1]);
                     }
                 }
                 // P^T and dS^T go back over the first 8 of the 16 columns this thread read.
@@ -1298,9 +1317,12 @@ __global__ void __launch_bounds__(kBwdThreads, 1)
                     }
                 } else {
 #pragma unroll
-                    for (int i = 0; i < kPart; ++i) {
-                        const float e = fast_exp2(fmaf(__uint_as_float(s_raw[i]), scale2, -lse2));
-                        dsv[i] = e * (__uint_as_float(dp_raw[i]) - dlt);
+                    for (int i = 0; i < kPart; i += 2) {
+                        float e0, e1;
+                        exp2_two(i / 2, fmaf(__uint_as_float(s_raw[i]), scale2, -lse2),
+                                 fmaf(__uint_as_float(s_raw[i + 1]), scale2, -lse2), e0, e1);
+                        dsv[i] = e0 * (__uint_as_float(dp_raw[i]) - dlt);
+                        dsv[i + 1] = e1 * (__uint_as_float(dp_raw[i + 1]) - dlt);
                     }
                 }
                 // dS goes back over the first 8 of the 16 dP columns this thread just read.
