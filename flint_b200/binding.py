@@ -133,6 +133,7 @@ _C_TYPES = {
     "const int*": ctypes.c_void_p,
     "double*": ctypes.c_void_p,
     "unsigned long long*": ctypes.POINTER(ctypes.c_ulonglong),
+    "long long*": ctypes.POINTER(ctypes.c_longlong),
     "size_t*": ctypes.POINTER(ctypes.c_size_t),
     "void**": ctypes.POINTER(ctypes.c_void_p),
     "const void**": ctypes.POINTER(ctypes.c_void_p),

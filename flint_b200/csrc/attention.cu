@@ -1527,6 +1527,82 @@ cudaError_t attention_backward(const AttentionView& dq, const AttentionView& dk,
                                 p);
 }
 
+// ---- diagnostic: MMA rate on an idle SM ----------------------------------------------------------
+
+__device__ long long g_mma_clocks[2];
+
+__global__ void __launch_bounds__(128, 1) fb_mma_clocks(int n, int a_in_tmem, int count) {
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t base = (sm100::smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar = base + 2 * kTileBytes;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+    const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x / 32), 0);
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        sm100::mbar_init(bar, 1);
+        sm100::mbar_fence_init();
+    }
+    for (int i = threadIdx.x; i < 2 * kTileBytes / 4; i += blockDim.x) {
+        asm volatile("st.shared.b32 [%0], %1;" ::"r"(base + 4u * i), "r"(0u) : "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (warp == 0) {
+        sm100::tmem_alloc(sm100::smem_u32(&tmem_slot), 512);
+    }
+    sm100::tc_fence_before_sync();
+    __syncthreads();
+    sm100::tc_fence_after_sync();
+    const uint32_t tmem = tmem_slot;
+    if (warp == 0) {
+        const uint32_t idesc = n == 128 ? sm100::instr_desc_f16(128, 128, false, false)
+                                        : sm100::instr_desc_f16(128, 64, false, false);
+        const uint64_t a_desc = desc_kmajor(base, 0);
+        const uint64_t b_desc = desc_kmajor(base + kTileBytes, 0);
+        const long long start = clock64();
+        long long issued = start;
+        if (sm100::elect_one()) {
+            for (int i = 0; i < count; ++i) {
+                const uint32_t step = (i & 3) * 2;
+                if (a_in_tmem != 0) {
+                    sm100::mma_f16_ts_at<1>(tmem, tmem + 256 + (i & 3) * 8, b_desc, step, idesc);
+                } else {
+                    sm100::mma_f16_ss_at<1>(tmem, a_desc, step, b_desc, step, idesc);
+                }
+            }
+            issued = clock64();
+            sm100::mma_commit(bar);
+        }
+        __syncwarp();
+        sm100::mbar_wait(bar, 0, &abort_flag);
+        const long long completed = clock64();
+        if (sm100::elect_one()) {
+            g_mma_clocks[0] = issued - start;
+            g_mma_clocks[1] = completed - start;
+        }
+        sm100::tc_fence_after_sync();
+    }
+    finish(abort_flag, tmem, 512, warp == 0 ? 1 : 0);
+}
+
+cudaError_t mma_clocks(int n, int a_in_tmem, int count, long long* issue, long long* complete,
+                       cudaStream_t stream) {
+    constexpr int kSmem = 1024 + 2 * kTileBytes + 64;
+    static std::atomic<bool> configured[64] = {};
+    cudaError_t e = fb::allow_shared_memory(fb_mma_clocks, kSmem, configured);
+    if (e != cudaSuccess) {
+        return e;
+    }
+    fb_mma_clocks<<<1, 128, kSmem, stream>>>(n, a_in_tmem, count);
+    e = fb::after_launch();
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    long long host[2] = {0, 0};
+    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(host, g_mma_clocks, sizeof host);
+    *issue = host[0];
+    *complete = host[1];
+    return e;
+}
+
 cudaError_t attention_error_flag(int* value, bool reset) {
     cudaError_t e = cudaMemcpyFromSymbol(value, g_attention_error, sizeof(int));
     if (e == cudaSuccess && reset && *value != 0) {
@@ -1616,6 +1692,22 @@ flint_status flint_b200_attention_backward(void* dq, void* dk, void* dv, const v
                                    static_cast<float*>(delta), heads_view(q, batches, length),
                                    heads_view(k, batches, length), heads_view(v, batches, length), shape, scale,
                                    stream));
+    return FLINT_OK;
+}
+
+flint_status flint_b200_mma_clocks(int n, int a_in_tmem, int count, long long* issue_clocks,
+                                   long long* complete_clocks, flint_stream stream) {
+    constexpr const char* name = "flint_b200_mma_clocks";
+    if (n != 64 && n != 128) {
+        return fb::fail(kBad, "%s: n (%d) must be 64 or 128", name, n);
+    }
+    if (count < 1 || count > 4096) {
+        return fb::fail(kBad, "%s: count (%d) must be between 1 and 4096", name, count);
+    }
+    if (issue_clocks == nullptr || complete_clocks == nullptr) {
+        return fb::fail(kBad, "%s: a result pointer is null", name);
+    }
+    FB_CUDA(fb::mma_clocks(n, a_in_tmem, count, issue_clocks, complete_clocks, stream));
     return FLINT_OK;
 }
 

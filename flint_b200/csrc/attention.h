@@ -36,6 +36,10 @@ cudaError_t attention_backward(const AttentionView& dq, const AttentionView& dk,
                                const AttentionView& v, const AttentionShape& shape, float scale,
                                cudaStream_t stream);
 
+// Clocks one CTA needs to get `count` small MMAs accepted and completed (a diagnostic).
+cudaError_t mma_clocks(int n, int a_in_tmem, int count, long long* issue, long long* complete,
+                       cudaStream_t stream);
+
 cudaError_t attention_error_flag(int* value, bool reset);
 
 }  // namespace fb

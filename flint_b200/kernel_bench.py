@@ -40,6 +40,7 @@ run under a profiler, with ``--rows`` reduced so that a capture stays small.
 """
 
 import argparse
+import ctypes
 import json
 import statistics
 import sys
@@ -735,9 +736,36 @@ def run(flint: Flint, groups, rows: int, quick: bool, once: bool = False, sigma_
     return results
 
 
+def mma_rates(flint: Flint, count: int = 256) -> list:
+    """Clocks per small tcgen05.mma (M 128, K 16) on an idle SM, by operand source and N: what
+    bounds attention with head width 64, whose MMAs are all of these shapes."""
+    results = []
+    for n in (64, 128):
+        for a_in_tmem in (0, 1):
+            issue, complete = ctypes.c_longlong(), ctypes.c_longlong()
+            for _ in range(3):
+                flint.check(flint.lib.flint_b200_mma_clocks(n, a_in_tmem, count, ctypes.byref(issue),
+                                                            ctypes.byref(complete), None))
+            results.append({"group": "mma", "case": f"M 128, N {n}, K 16, A from "
+                            f"{'tensor' if a_in_tmem else 'shared'} memory", "count": count,
+                            "issue_clocks_each": round(issue.value / count, 1),
+                            "complete_clocks_each": round(complete.value / count, 1),
+                            "tensor_clocks_each": n // 2})
+    return results
+
+
+def mma_table(results) -> str:
+    lines = ["| MMA | clocks until accepted, each | clocks until complete, each | tensor work, clocks |",
+             "| --- | ---: | ---: | ---: |"]
+    for r in results:
+        lines.append(f"| {r['case']} | {r['issue_clocks_each']} | {r['complete_clocks_each']} | "
+                     f"{r['tensor_clocks_each']} |")
+    return "\n".join(lines)
+
+
 def main(argv=None):
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    parser.add_argument("--group", default="all", choices=["all"] + list(GROUPS))
+    parser.add_argument("--group", default="all", choices=["all", "mma"] + list(GROUPS))
     parser.add_argument("--rows", type=int, default=8192, help="token rows (8 x 1024)")
     parser.add_argument("--quick", action="store_true", help="3 rounds of 25 ms samples instead of 10 x 100 ms")
     parser.add_argument("--once", action="store_true", help="one call per kernel, no timing")
@@ -747,6 +775,13 @@ def main(argv=None):
     parser.add_argument("--out", help="write the JSON lines and the table to this file too")
     args = parser.parse_args(argv)
     flint = Flint()
+    if args.group == "mma":
+        results = mma_rates(flint)
+        text = "\n".join(json.dumps(r) for r in results) + "\n\n" + mma_table(results)
+        print(text, flush=True)
+        if args.out:
+            Path(args.out).write_text(text + "\n")
+        return
     groups = list(GROUPS) if args.group == "all" else [args.group]
     lines = []
 

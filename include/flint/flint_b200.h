@@ -23,6 +23,18 @@ FLINT_API flint_status flint_b200_kernel_fault(int* raised);
 /* Kernels this library has launched in this process so far (host counter). */
 FLINT_API flint_status flint_b200_launch_count(unsigned long long* launches);
 
+/* Diagnostic (no counterpart in the reference): the rate of the tensor pipe for
+ * the small MMAs that attention with head width 64 is made of. One CTA on an
+ * otherwise idle GPU issues `count` (1 to 4,096) tcgen05.mma of kind::f16 with
+ * M = 128, K = 16 and N = `n` (64 or 128) back to back from one elected thread,
+ * the A operand read from shared memory or, when a_in_tmem is not 0, from tensor
+ * memory; operands are zeros. *issue_clocks receives the SM clocks until the last
+ * one was accepted, *complete_clocks until all had completed. Waits for the
+ * stream; meant for `python -m flint_b200.kernel_bench --group mma`. */
+FLINT_API flint_status flint_b200_mma_clocks(int n, int a_in_tmem, int count,
+                                             long long* issue_clocks, long long* complete_clocks,
+                                             flint_stream stream);
+
 /* Causal attention without materialising scores or probabilities:
  * o[b] = softmax(scale * q[b] k[b]^T + causal mask) v[b] for `batches`
  * (sequence, head) pairs, all FP16 [batches, length, head_width] contiguous;

@@ -86,6 +86,27 @@ def test_attention_backward_is_deterministic_over_many_items(flint):
         assert torch.equal(a.view(torch.int16), b.view(torch.int16))
 
 
+def test_mma_clock_probe(flint):
+    """The diagnostic behind `kernel_bench --group mma`: sane numbers and argument checks."""
+    import ctypes
+
+    from flint_b200.binding import FlintError
+    from flint_b200.kernel_bench import mma_rates
+
+    rates = {r["case"]: r for r in mma_rates(flint, 128)}
+    assert len(rates) == 4
+    for r in rates.values():
+        # No MMA can beat the tensor work of its shape; none should take ten times as long.
+        assert r["tensor_clocks_each"] * 0.9 <= r["complete_clocks_each"] <= r["tensor_clocks_each"] * 10
+        assert r["issue_clocks_each"] <= r["complete_clocks_each"]
+    clocks = ctypes.c_longlong()
+    for n, count in ((96, 16), (64, 0), (64, 5000)):
+        with pytest.raises(FlintError):
+            flint.check(flint.lib.flint_b200_mma_clocks(n, 0, count, ctypes.byref(clocks),
+                                                        ctypes.byref(clocks), None))
+    assert not flint.kernel_fault()
+
+
 def test_attention_does_not_depend_on_cache_state(flint):
     """The kernels' roles meet only through mbarriers, so a result must not depend on how
     long a load takes. Each trial first pushes Q, K, V out of the L2 with a 512 MB write
