@@ -114,6 +114,33 @@ cudaError_t encode_rows_map(void* map, const void* base, size_t rows, size_t col
                             int element_bytes, unsigned box_cols, unsigned box_rows,
                             int swizzle_bytes = 0);
 
+// Second passes of column sums that are put off and then run as one launch: the model on the
+// fused attention kernels collects a block's eight (four bias gradients, two LayerNorms'
+// gain and bias gradients) and finishes them together, which takes seven short dependent
+// launches per block off the stream. Each job's partial sums need their own workspace
+// region until then; an output is computed exactly as its own second pass would.
+struct ColumnFinishList {
+    static constexpr int kMost = 8;
+    struct Job {
+        void* out;
+        const void* partial;
+        size_t cols;
+        bool accumulate;
+    };
+    Job jobs[kMost];
+    int count = 0;
+    bool add(void* out, const void* partial, size_t cols, bool accumulate) {
+        if (count == kMost) {
+            return false;
+        }
+        jobs[count++] = Job{out, partial, cols, accumulate};
+        return true;
+    }
+};
+// Bytes of partial sums one column-sum job over [rows, cols] writes.
+size_t column_partial_bytes(size_t rows, size_t cols);
+cudaError_t launch_column_finishes(const ColumnFinishList& list, size_t rows, cudaStream_t stream);
+
 // flint_layernorm_backward's kernels without the argument checks, for the model
 // assembly; dx_half, when not null, also receives dx rounded to FP16 (the next
 // GEMM's operand), which saves a separate conversion pass over dx.
@@ -121,16 +148,19 @@ cudaError_t launch_layernorm_backward(void* dx, void* dgamma, void* dbeta, const
                                       const void* x, const void* mean, const void* rstd,
                                       const void* gamma, size_t rows, size_t cols,
                                       bool accumulate_dx, bool accumulate_params, void* workspace,
-                                      cudaStream_t stream, void* dx_half, bool plain);
+                                      cudaStream_t stream, void* dx_half, bool plain,
+                                      ColumnFinishList* later = nullptr);
 
 // flint_bias_gradient's kernels without the argument checks. `plain` (here and above)
 // selects column sums whose row streams use ordinary FP32 adds, merged by compensated
 // adds in the same fixed order: deterministic, within a few 2^-24 of the pinned
 // arithmetic's result, about seven times less FP32 work. The public entry points pass
 // false; the model built on the fused attention kernels passes true.
+// With `later` (both launchers) the second passes are appended to the list instead of being
+// launched; the workspace must then stay untouched until launch_column_finishes has run.
 cudaError_t launch_bias_gradient(void* dbias, const void* dy, size_t rows, size_t cols,
                                  bool accumulate, void* workspace, cudaStream_t stream,
-                                 bool plain);
+                                 bool plain, ColumnFinishList* later = nullptr);
 
 // Device error word of the column-sum kernels: set when a bounded wait for a
 // staged row gave up (read, and cleared if asked, by flint_b200_kernel_fault).

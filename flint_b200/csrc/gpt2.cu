@@ -133,6 +133,14 @@ flint_status size_workspaces(flint_gpt2& m) {
         most = std::max(most, bytes);
     }
     m.tn_workspace_bytes = most;
+    // fcproj bias, fc bias, LayerNorm 2 (gain then bias), proj bias, qkv bias, LayerNorm 1.
+    const size_t region_cols[6] = {w, 4 * w, 2 * w, w, 3 * w, 2 * w};
+    size_t at = 0;
+    for (int r = 0; r < 6; ++r) {
+        m.column_offsets[r] = at;
+        at += (fb::column_partial_bytes(m.rows, region_cols[r]) + 255) / 256 * 256;
+    }
+    m.column_workspace_bytes = at;
     return FLINT_OK;
 }
 
@@ -249,6 +257,9 @@ flint_status plan(flint_gpt2& m) {
         }
         want(m, &m.workspace, m.workspace_bytes);
         want(m, &m.tn_workspace, m.tn_workspace_bytes);
+        if (m.flash) {
+            want(m, &m.column_workspace, m.column_workspace_bytes);
+        }
     } else {
         // One set of activations shared by every block; the residual stream
         // ping-pongs between x_in and x_mid.
@@ -388,18 +399,25 @@ flint_status forward_block(const flint_gpt2& m, size_t i, flint_stream s) {
                                        a.x_mid, rows, w, 4 * w, s);
 }
 
+void* region_of(const flint_gpt2& m, int region) {
+    return static_cast<unsigned char*>(m.column_workspace) + m.column_offsets[region];
+}
+
 flint_status weight_gradient(const flint_gpt2& m, const Tensor* weight, const void* dy,
                              const void* input, int accumulate, flint_stream s) {
     return flint_gemm_tn(weight->gradient, dy, input, weight->rows, weight->cols, m.rows,
                          accumulate, m.tn_workspace, m.tn_workspace_bytes, s);
 }
 
+// `later` and `region` (which of the block's six partial-sum regions) are used by the model on
+// the fused attention kernels, whose second passes run together at the end of the block.
 flint_status bias_gradient(const flint_gpt2& m, const Tensor* bias, const void* dy, int accumulate,
-                           flint_stream s) {
+                           flint_stream s, fb::ColumnFinishList* later = nullptr, int region = 0) {
     if (m.flash) {
         // The extension model: bandwidth-bound column sums (see fb::launch_bias_gradient).
+        void* workspace = later == nullptr ? m.workspace : region_of(m, region);
         FB_CUDA(fb::launch_bias_gradient(bias->gradient, dy, m.rows, bias->cols, accumulate != 0,
-                                         m.workspace, s, true));
+                                         workspace, s, true, later));
         return FLINT_OK;
     }
     return flint_bias_gradient(bias->gradient, dy, m.rows, bias->cols, accumulate, m.workspace,
@@ -411,11 +429,13 @@ flint_status bias_gradient(const flint_gpt2& m, const Tensor* bias, const void* 
 // the GEMMs that follow.
 flint_status layernorm_backward(const flint_gpt2& m, const Tensor* gain, const Tensor* bias,
                                 const void* x, const void* mean, const void* rstd,
-                                int accumulate_dx, int accumulate, bool half_copy, flint_stream s) {
+                                int accumulate_dx, int accumulate, bool half_copy, flint_stream s,
+                                fb::ColumnFinishList* later = nullptr, int region = 0) {
+    void* workspace = later == nullptr ? m.workspace : region_of(m, region);
     FB_CUDA(fb::launch_layernorm_backward(m.dres, gain->gradient, bias->gradient, m.dh, x, mean,
                                           rstd, gain->data, m.rows, m.config.width,
-                                          accumulate_dx != 0, accumulate != 0, m.workspace, s,
-                                          half_copy ? m.dres_half : nullptr, m.flash));
+                                          accumulate_dx != 0, accumulate != 0, workspace, s,
+                                          half_copy ? m.dres_half : nullptr, m.flash, later));
     return FLINT_OK;
 }
 
@@ -431,19 +451,24 @@ flint_status backward_block(const flint_gpt2& m, size_t i, int accumulate, flint
     const size_t hb = m.head_batches;
     const size_t len = c.length;
 
+    // The fused-attention model runs the block's eight column-sum second passes as one launch
+    // at the end (the first passes write to six separate regions meanwhile).
+    fb::ColumnFinishList finishes;
+    fb::ColumnFinishList* later = m.flash ? &finishes : nullptr;
+
     // MLP. dres_half already holds dres in FP16 (written by the LayerNorm backward before).
     FB_TRY(weight_gradient(m, wt.fcproj_w, m.dres_half, a.gelu, accumulate, s));
-    FB_TRY(bias_gradient(m, wt.fcproj_b, m.dres_half, accumulate, s));
+    FB_TRY(bias_gradient(m, wt.fcproj_b, m.dres_half, accumulate, s, later, 0));
     FB_TRY(flint_gemm_nn_dgelu(m.dpre, m.dres_half, wt.fcproj_w->half, a.pre, rows, 4 * w, w, s));
     FB_TRY(weight_gradient(m, wt.fc_w, m.dpre, a.h2, accumulate, s));
-    FB_TRY(bias_gradient(m, wt.fc_b, m.dpre, accumulate, s));
+    FB_TRY(bias_gradient(m, wt.fc_b, m.dpre, accumulate, s, later, 1));
     FB_TRY(flint_gemm_nn(m.dh, m.dpre, wt.fc_w->half, rows, w, 4 * w, s));
     FB_TRY(layernorm_backward(m, wt.ln2_w, wt.ln2_b, a.x_mid, a.mean2, a.rstd2, 1, accumulate, true,
-                              s));
+                              s, later, 2));
 
     // Attention output projection.
     FB_TRY(weight_gradient(m, wt.proj_w, m.dres_half, a.attn, accumulate, s));
-    FB_TRY(bias_gradient(m, wt.proj_b, m.dres_half, accumulate, s));
+    FB_TRY(bias_gradient(m, wt.proj_b, m.dres_half, accumulate, s, later, 3));
     FB_TRY(flint_gemm_nn(m.dh, m.dres_half, wt.proj_w->half, rows, w, w, s));
     if (m.flash) {
         // dO is dh (rows layout), O is the saved attention output, and dQ, dK, dV land
@@ -471,11 +496,13 @@ flint_status backward_block(const flint_gpt2& m, size_t i, int accumulate, flint
         }
     }
     FB_TRY(weight_gradient(m, wt.attn_w, m.qkv, a.h1, accumulate, s));
-    FB_TRY(bias_gradient(m, wt.attn_b, m.qkv, accumulate, s));
+    FB_TRY(bias_gradient(m, wt.attn_b, m.qkv, accumulate, s, later, 4));
     FB_TRY(flint_gemm_nn(m.dh, m.qkv, wt.attn_w->half, rows, w, 3 * w, s));
     // Block 0's result feeds the embedding backward, which reads FP32.
-    return layernorm_backward(m, wt.ln1_w, wt.ln1_b, a.x_in, a.mean1, a.rstd1, 1, accumulate, i > 0,
-                              s);
+    FB_TRY(layernorm_backward(m, wt.ln1_w, wt.ln1_b, a.x_in, a.mean1, a.rstd1, 1, accumulate, i > 0,
+                              s, later, 5));
+    FB_CUDA(fb::launch_column_finishes(finishes, rows, s));
+    return FLINT_OK;
 }
 
 flint_status create(const char* name, const flint_gpt2_config* config, bool flash,

@@ -97,6 +97,11 @@ struct flint_gpt2 {
     size_t workspace_bytes = 0;
     void* tn_workspace = nullptr;
     size_t tn_workspace_bytes = 0;
+    // The fused-attention model puts a block's column-sum second passes off to one launch:
+    // six regions of partial sums, in the order backward_block produces them.
+    void* column_workspace = nullptr;
+    size_t column_workspace_bytes = 0;
+    size_t column_offsets[6] = {};
 
     struct Slot {
         void** target;

@@ -398,15 +398,10 @@ __global__ void __launch_bounds__(kTilePieces * (kLaneRows + 1))
 // Second pass: a warp per 4 columns.
 constexpr int kFinishWarps = 8;
 
-__global__ void __launch_bounds__(32 * kFinishWarps)
-    fb_column_finish(float4* __restrict__ out, const float4* __restrict__ partial, size_t chunks,
-                     int quads, bool accumulate) {
-    fb::dependency_wait();
-    fb::dependency_release();
-    const int quad = blockIdx.x * kFinishWarps + threadIdx.x / 32;
-    if (quad >= quads) {
-        return;
-    }
+// The sums of columns [4 quad, 4 quad + 4) over all chunks, by one warp.
+__device__ __forceinline__ void finish_quad(float4* __restrict__ out,
+                                            const float4* __restrict__ partial, size_t chunks,
+                                            int quads, int quad, bool accumulate) {
     const int lane = threadIdx.x % 32;
     Comp total[4];
     for (size_t chunk = lane; chunk < chunks; chunk += 32) {
@@ -443,6 +438,43 @@ __global__ void __launch_bounds__(32 * kFinishWarps)
                              __fadd_rn(old.z, result.z), __fadd_rn(old.w, result.w));
     }
     out[quad] = result;
+}
+
+__global__ void __launch_bounds__(32 * kFinishWarps)
+    fb_column_finish(float4* __restrict__ out, const float4* __restrict__ partial, size_t chunks,
+                     int quads, bool accumulate) {
+    fb::dependency_wait();
+    fb::dependency_release();
+    const int quad = blockIdx.x * kFinishWarps + threadIdx.x / 32;
+    if (quad < quads) {
+        finish_quad(out, partial, chunks, quads, quad, accumulate);
+    }
+}
+
+// Several second passes in one launch: job j owns blocks [first_block[j], first_block[j + 1]).
+struct FinishJobs {
+    float4* out[fb::ColumnFinishList::kMost];
+    const float4* partial[fb::ColumnFinishList::kMost];
+    int quads[fb::ColumnFinishList::kMost];
+    int first_block[fb::ColumnFinishList::kMost + 1];
+    unsigned accumulate;  // bit j
+    int count;
+};
+
+__global__ void __launch_bounds__(32 * kFinishWarps)
+    fb_column_finish_many(const __grid_constant__ FinishJobs jobs, size_t chunks) {
+    fb::dependency_wait();
+    fb::dependency_release();
+    int j = 0;
+    while (j + 1 < jobs.count && static_cast<int>(blockIdx.x) >= jobs.first_block[j + 1]) {
+        ++j;
+    }
+    const int quad =
+        (static_cast<int>(blockIdx.x) - jobs.first_block[j]) * kFinishWarps + threadIdx.x / 32;
+    if (quad < jobs.quads[j]) {
+        finish_quad(jobs.out[j], jobs.partial[j], chunks, jobs.quads[j], quad,
+                    ((jobs.accumulate >> j) & 1u) != 0);
+    }
 }
 
 template <Source kSource, bool kPlain = false>
@@ -916,9 +948,44 @@ cudaError_t reductions_error_flag(int* value, bool reset) {
 }
 
 // Internal launchers, also used by the model assembly.
+size_t column_partial_bytes(size_t rows, size_t cols) { return column_sum_workspace(rows, cols); }
+
+cudaError_t launch_column_finishes(const ColumnFinishList& list, size_t rows, cudaStream_t stream) {
+    if (list.count == 0) {
+        return cudaSuccess;
+    }
+    FinishJobs jobs = {};
+    jobs.count = list.count;
+    int blocks = 0;
+    for (int j = 0; j < list.count; ++j) {
+        const ColumnFinishList::Job& job = list.jobs[j];
+        jobs.out[j] = static_cast<float4*>(job.out);
+        jobs.partial[j] = static_cast<const float4*>(job.partial);
+        jobs.quads[j] = static_cast<int>(job.cols / 4);
+        jobs.first_block[j] = blocks;
+        jobs.accumulate |= job.accumulate ? 1u << j : 0u;
+        blocks += (jobs.quads[j] + kFinishWarps - 1) / kFinishWarps;
+    }
+    jobs.first_block[list.count] = blocks;
+    const size_t chunks = (rows + kChunkRows - 1) / kChunkRows;
+    return fb::launch_dependent(fb_column_finish_many, dim3(static_cast<unsigned>(blocks)),
+                                dim3(32 * kFinishWarps), 0, stream, jobs, chunks);
+}
+
+namespace {
+// The second pass now, or noted for launch_column_finishes.
+cudaError_t finish_or_defer(void* out, const void* workspace, size_t rows, size_t cols,
+                            bool accumulate, cudaStream_t stream, ColumnFinishList* later) {
+    if (later == nullptr) {
+        return launch_finish(out, workspace, rows, cols, accumulate, stream);
+    }
+    return later->add(out, workspace, cols, accumulate) ? cudaSuccess : cudaErrorInvalidValue;
+}
+}  // namespace
+
 cudaError_t launch_bias_gradient(void* dbias, const void* dy, size_t rows, size_t cols,
                                  bool accumulate, void* workspace, cudaStream_t stream,
-                                 bool plain) {
+                                 bool plain, ColumnFinishList* later) {
     cudaError_t e =
         plain ? launch_partials<Source::kHalf, true>(workspace, dy, nullptr, nullptr, nullptr, rows,
                                                      cols, stream)
@@ -927,14 +994,15 @@ cudaError_t launch_bias_gradient(void* dbias, const void* dy, size_t rows, size_
     if (e != cudaSuccess) {
         return e;
     }
-    return launch_finish(dbias, workspace, rows, cols, accumulate, stream);
+    return finish_or_defer(dbias, workspace, rows, cols, accumulate, stream, later);
 }
 
 cudaError_t launch_layernorm_backward(void* dx, void* dgamma, void* dbeta, const void* dy,
                                       const void* x, const void* mean, const void* rstd,
                                       const void* gamma, size_t rows, size_t cols,
                                       bool accumulate_dx, bool accumulate_params, void* workspace,
-                                      cudaStream_t stream, void* dx_half, bool plain) {
+                                      cudaStream_t stream, void* dx_half, bool plain,
+                                      ColumnFinishList* later) {
     cudaError_t e = cudaSuccess;
     if (plain) {
         // One pass over dy serves both parameter gradients: dgamma's partial sums fill the
@@ -945,12 +1013,13 @@ cudaError_t launch_layernorm_backward(void* dx, void* dgamma, void* dbeta, const
         if (e != cudaSuccess) {
             return e;
         }
-        e = launch_finish(dgamma, workspace, rows, cols, accumulate_params, stream);
+        e = finish_or_defer(dgamma, workspace, rows, cols, accumulate_params, stream, later);
         if (e != cudaSuccess) {
             return e;
         }
-        e = launch_finish(dbeta, static_cast<unsigned char*>(workspace) + column_sum_workspace(rows, cols),
-                          rows, cols, accumulate_params, stream);
+        e = finish_or_defer(dbeta,
+                            static_cast<unsigned char*>(workspace) + column_sum_workspace(rows, cols),
+                            rows, cols, accumulate_params, stream, later);
         if (e != cudaSuccess) {
             return e;
         }
