@@ -114,6 +114,12 @@ cudaError_t encode_rows_map(void* map, const void* base, size_t rows, size_t col
                             int element_bytes, unsigned box_cols, unsigned box_rows,
                             int swizzle_bytes = 0);
 
+// LayerNorm forward whose row sums use plain FP32 adds (see rowwise.cu); returns false, having
+// launched nothing, for shapes it does not cover.
+bool launch_layernorm_forward_plain(void* y, void* mean, void* rstd, const void* x,
+                                    const void* gamma, const void* beta, size_t rows, size_t cols,
+                                    float eps, cudaStream_t stream, cudaError_t* error);
+
 // Second passes of column sums that are put off and then run as one launch: the model on the
 // fused attention kernels collects a block's eight (four bias gradients, two LayerNorms'
 // gain and bias gradients) and finishes them together, which takes seven short dependent

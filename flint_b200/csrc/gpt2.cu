@@ -355,6 +355,15 @@ float score_scale(size_t head_width) { return 1.0f / std::sqrt(static_cast<float
 
 flint_status layernorm(const flint_gpt2& m, const Tensor* gain, const Tensor* bias, const void* x,
                        void* y, void* mean, void* rstd, flint_stream s) {
+    if (m.flash) {
+        // The extension model is not bound to the reference's bit pattern: plain row sums.
+        cudaError_t e = cudaSuccess;
+        if (fb::launch_layernorm_forward_plain(y, mean, rstd, x, gain->data, bias->data, m.rows,
+                                               m.config.width, kEps, s, &e)) {
+            FB_CUDA(e);
+            return FLINT_OK;
+        }
+    }
     return flint_layernorm_forward(y, mean, rstd, x, gain->data, bias->data, m.rows,
                                    m.config.width, kEps, s);
 }
