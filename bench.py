@@ -270,6 +270,7 @@ def per_kernel_summary(flint):
                     "baseline_us": base["us"] if base else None,
                     "flint_over_baseline": ratio["median"] if ratio else None,
                     "copy_same_bytes_us": r.get("copy_same_bytes_us"),
+                    "timing": r.get("timing"),
                     "sm_mhz": r["sm_mhz_median"]})
     return {"protocol": "operands rotated past 4x L2, 3 interleaved rounds of 25 ms samples per arm "
                         "(python -m flint_b200.kernel_bench runs 10 rounds of 100 ms); baseline = "
