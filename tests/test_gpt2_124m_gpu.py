@@ -151,6 +151,44 @@ def test_gpt2_124m_forward_and_backward_match_the_oracle(flint, two_sequences, f
     run_and_check(flint, two_sequences, flash)
 
 
+@pytest.mark.parametrize("flash", [None, True], ids=["reference-layout", "fused-attention"])
+def test_gpt2_124m_gradients_do_not_depend_on_cache_state(flint, flash):
+    """Every kernel of the step hands work between its warps through mbarriers and between
+    kernels through stream order (with programmatic dependent launch), so no result may depend
+    on how long a load takes: forward + backward of 4 x 1024 tokens run four times, twice with
+    the L2 flushed before the pass and twice warm, must leave bit-identical logits gradients
+    and parameter gradients (one arena read compares all 148)."""
+    sequences = 4
+    config = flint_b200.Gpt2Config(CFG["n_layer"], CFG["n_head"], CFG["n_embd"], CFG["block_size"],
+                                   CFG["vocab_size"], CFG["padded_vocab_size"], sequences, LENGTH,
+                                   0, 1)
+    rows = sequences * LENGTH
+    idx, targets = oracle.synthetic_tokens(sequences, LENGTH, CFG["vocab_size"], seed=21)
+    tokens, wanted = u16(idx.flatten()), u16(targets.flatten())
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=DEV)
+    with flint_b200.Gpt2(flint, config, flash) as model:
+        model.load({k: v.to(DEV) for k, v in weights().items()})
+        grads = list(model.gradients())
+        first_address = min(address for _, address, _, _ in grads)
+        floats = (max(address + 4 * r * c for _, address, r, c in grads) - first_address) // 4
+        _, dlogits_at, _ = model.outputs()
+        first = None
+        for trial in range(4):
+            if trial % 2 == 0:
+                flush.fill_(trial)
+            model.forward(tokens, wanted, LOSS_SCALE / rows)
+            model.backward(tokens, False)
+            torch.cuda.synchronize()
+            assert not flint.kernel_fault()
+            got = (model.read(first_address, (floats,), torch.float32).clone(),
+                   model.read(dlogits_at, (rows, CFG["padded_vocab_size"]), torch.float16).clone())
+            if first is None:
+                first = got
+                continue
+            assert torch.equal(first[0].view(torch.int32), got[0].view(torch.int32)), trial
+            assert torch.equal(first[1].view(torch.int16), got[1].view(torch.int16)), trial
+
+
 @pytest.mark.full_size
 @pytest.mark.parametrize("flash", [None, True], ids=["reference-layout", "fused-attention"])
 def test_gpt2_124m_single_step_configuration_at_8x1024(flint, flash, full_batch):
