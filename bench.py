@@ -280,6 +280,38 @@ def per_kernel_summary(flint):
             "cases": out}
 
 
+class Watchdog:
+    """Ends the process when a phase of the bench takes far longer than it can (a collective that
+    never completes, say): a bench that hangs costs its caller the whole time limit and every
+    other rank with it. `phase` names what is running and how long it may take."""
+
+    def __init__(self):
+        import threading
+
+        self.deadline, self.name = None, ""
+        self.lock = threading.Lock()
+        threading.Thread(target=self._watch, daemon=True).start()
+
+    def phase(self, name: str, seconds: float) -> None:
+        with self.lock:
+            self.name, self.deadline = name, time.monotonic() + seconds
+
+    def done(self) -> None:
+        with self.lock:
+            self.deadline = None
+
+    def _watch(self) -> None:
+        while True:
+            time.sleep(1.0)
+            with self.lock:
+                late = self.deadline is not None and time.monotonic() > self.deadline
+                name = self.name
+            if late:
+                print(f"bench.py: '{name}' exceeded its time limit; giving up", file=sys.stderr,
+                      flush=True)
+                os._exit(3)
+
+
 def run_flint(args):
     import numpy as np
     import torch
@@ -292,6 +324,8 @@ def run_flint(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
+    watchdog = Watchdog()
+    watchdog.phase("process group, model and NCCL communicator set-up", 240)
     group = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -336,6 +370,7 @@ def run_flint(args):
         return t.item()
 
     # ---- device-resident inputs ------------------------------------------------------
+    watchdog.phase("warm-up and timed steps", 120 + 2.0 * (args.warmup + 2 * args.steps))
     for i in range(args.warmup):
         trainer.step(*device_batches[i % pool])
         trainer.finish_step()
@@ -371,6 +406,8 @@ def run_flint(args):
     if flint.kernel_fault():
         raise RuntimeError("a tensor-core kernel gave up on a barrier wait during the bench")
 
+    # The rest runs on rank 0 alone and on the host's clock: no limit that a slow box could hit.
+    watchdog.done()
     roofline = gemm_roofline(flint, torch, rows) if rank == 0 else None
     run_facts = {"loss_scale": trainer.scaler.scale, "skipped_steps": trainer.skipped,
                  "last_loss": round(last_loss, 4)}

@@ -102,6 +102,11 @@ flint_status load_nccl(Nccl** out) {
     if (name == nullptr || name[0] == '\0') {
         name = "libnccl.so.2";
     }
+    // In-switch reductions (NVLS) stay off unless the caller's environment asks for them: every
+    // multi-rank number of this library was measured that way (two, four and eight ranks), and
+    // the one eight-rank run with NVLS on did not get through communicator set-up in ten
+    // minutes. NCCL reads the variable when the first communicator is created.
+    setenv("NCCL_NVLS_ENABLE", "0", 0);
     void* handle = dlopen(name, RTLD_NOW | RTLD_GLOBAL);
     if (handle == nullptr) {
         return fail(FLINT_ERROR_CUDA, "flint_train: cannot open %s (%s); set FLINT_NCCL_LIBRARY",

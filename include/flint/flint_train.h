@@ -13,7 +13,9 @@
  * adds the host-side step around it: one process per GPU, a second stream for
  * collectives, NCCL loaded at run time with dlopen (so neither library links
  * it; FLINT_NCCL_LIBRARY names the file, default libnccl.so.2) and used only
- * when world > 1. Two ways to share the work across ranks:
+ * when world > 1; NCCL_NVLS_ENABLE is set to 0 unless the environment already
+ * sets it (the configuration every multi-rank figure was measured in). Two ways
+ * to share the work across ranks:
  *   replicated  every gradient bucket is summed with ncclAllReduce while the
  *               backward pass continues; every rank runs the whole AdamW
  *   sharded     (shard_optimizer) every bucket is summed with ncclReduceScatter,
