@@ -84,3 +84,25 @@ def test_two_ranks_sum_to_the_global_mean_gradient():
     results = manager.dict()
     mp.spawn(_rank_main, args=(world, _free_port(), results), nprocs=world, join=True)
     assert dict(results) == {0: True, 1: True}
+
+
+def test_bench_watchdog_ends_a_phase_that_never_finishes():
+    """bench.py's watchdog: a phase past its limit ends the process with status 3 and a
+    message naming the phase; a phase that was closed in time does not."""
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    late = subprocess.run(
+        [sys.executable, "-c",
+         "import bench, time; w = bench.Watchdog(); w.phase('stuck collective', 0.5); time.sleep(10)"],
+        cwd=root, capture_output=True, text=True, timeout=60)
+    assert late.returncode == 3
+    assert "stuck collective" in late.stderr
+    fine = subprocess.run(
+        [sys.executable, "-c",
+         "import bench, time; w = bench.Watchdog(); w.phase('quick', 0.5); w.done(); "
+         "time.sleep(2.5); print('finished')"],
+        cwd=root, capture_output=True, text=True, timeout=60)
+    assert fine.returncode == 0 and "finished" in fine.stdout
