@@ -563,15 +563,23 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
                 }
                 sm100::tmem_st_wait();
                 sm100::tc_fence_before_sync();
+                // A parity wait is only right while the barrier is neither behind nor ahead by
+                // more than the phase waited for. After the item's last step the thread waits
+                // for that step's P V; the MMA warp may still be one P V short of it, so the
+                // last but one is awaited first, and here, before this warp's arrival lets the
+                // last one be issued at all (afterwards a slow warp could find both complete
+                // and wait for a parity that no longer comes).
+                if (j == qb && qb > 0 &&
+                    !sm100::mbar_wait(bar.pv_done(tile), (before + qb - 1) & 1, abort)) {
+                    ok = false;
+                    break;
+                }
                 __syncwarp();
                 if (lane == 0) {
                     sm100::mbar_arrive(bar.p_ready(n % 3));
                 }
             }
-            // A parity wait is only right when at most one phase is outstanding, and the MMA
-            // warp may be two P V behind here: wait for the last but one first.
-            if (!ok || (qb > 0 && !sm100::mbar_wait(bar.pv_done(tile), (before + qb - 1) & 1, abort)) ||
-                !sm100::mbar_wait(bar.pv_done(tile), (before + qb) & 1, abort)) {
+            if (!ok || !sm100::mbar_wait(bar.pv_done(tile), (before + qb) & 1, abort)) {
                 ok = false;
                 break;
             }
