@@ -1,4 +1,4 @@
-"""The forward attention kernel's synchronisation protocol, model-checked on the CPU.
+"""The attention kernels' synchronisation protocols, model-checked on the CPU.
 
 `fb_attention_forward` (flint_b200/csrc/attention.cu) hands work between a TMA producer, an
 MMA-issuing warp and sixteen softmax warps through mbarriers whose waits carry only a phase
@@ -17,8 +17,9 @@ against the data it must see:
   reading O before the P V it needs has finished;
 * a ring slot or a query buffer reloaded before its readers are done; a deadlock.
 
-The last two tests put two earlier forms of the kernel's final waits into the model and require
+Two tests put two earlier forms of the forward kernel's final waits into the model and require
 the checker to find their faults, which is what pins the model's power to find that class of bug.
+The second half models the dK/dV kernel (and, with queries and keys exchanged, dQ) the same way.
 """
 
 import random
@@ -291,34 +292,32 @@ class Model:
             for quadrant in range(4):
                 for half in range(2):
                     roles[f"softmax{tile}.{quadrant}.{half}"] = self.softmax_warp(tile, quadrant, half)
-        idle_rounds = 0
-        while roles:
-            progressed = False
-            names = list(roles)
-            self.rng.shuffle(names)
-            for name in names:
-                if self.rng.random() < 0.5:
-                    continue                      # this role is "slow" this round
-                before = self.snapshot()
-                try:
-                    next(roles[name])
-                except StopIteration:
-                    del roles[name]
-                    progressed = True
-                    continue
-                progressed = progressed or self.snapshot() != before or True
-            if self.tma and self.rng.random() < 0.35:
-                self.run_tma()
-                idle_rounds = 0
-            if self.pipe and self.rng.random() < 0.35:
-                self.run_pipe()
-                idle_rounds = 0
-            idle_rounds += 1
-            need(idle_rounds < 20000, f"deadlock: {sorted(roles)} still waiting")
+        schedule(self.rng, roles, [(self.tma, self.run_tma), (self.pipe, self.run_pipe)])
         need(not self.tma and len(self.pv_done) == len(self.steps), "work left over at the end")
 
-    def snapshot(self):
-        return (len(self.tma), len(self.pipe), sum(b.completed for b in self.bar.values()))
+
+def schedule(rng, roles, engines):
+    """Runs the role generators to completion in a random interleaving: every round each role
+    makes a step with probability one half (so any role can fall far behind the others), and
+    each engine (pending loads, the tensor pipe's queue) completes one operation with
+    probability 0.35. No engine operation for 20,000 rounds while roles still wait is a deadlock."""
+    quiet = 0
+    while roles:
+        names = list(roles)
+        rng.shuffle(names)
+        for name in names:
+            if rng.random() < 0.5:
+                continue
+            try:
+                next(roles[name])
+            except StopIteration:
+                del roles[name]
+        for queue, run in engines:
+            if queue and rng.random() < 0.35:
+                run()
+                quiet = 0
+        quiet += 1
+        need(quiet < 20000, f"deadlock: {sorted(roles)} still waiting")
 
 
 ITEM_LISTS = [[0], [1], [7], [0, 0, 0], [2, 1, 0], [7, 4, 1], [3, 3, 3, 3], [0, 7, 0, 5, 1]]
@@ -355,3 +354,177 @@ def test_the_checker_notices_a_wait_that_comes_too_late():
             found += 1
             assert "deadlock" in str(violation)
     assert found > 0
+
+
+# ---- the dK/dV kernel -------------------------------------------------------------------------
+#
+# fb_attention_dkv: the producer fetches an item's K and V tiles (one shared-memory pair,
+# refilled once the compute warps have copied the item before into tensor memory) and streams
+# 64-query stages through a ring of four; the MMA warp issues the scores of sub-step h + 1
+# before it waits for sub-step h's probabilities (two accumulator pairs), then the gradient
+# MMAs; sixteen compute warps turn scores into probabilities in place, install the next item's
+# K and V after their last sub-step and write the item's gradients out. fb_attention_dq has the
+# same protocol with the roles of queries and keys exchanged.
+
+STAGES = 4         # kBwdStages
+COMPUTE = 16       # kBwdComputeWarps
+
+
+class BackwardModel:
+    def __init__(self, items, seed):
+        self.items = items                     # sub-steps of each item (even numbers)
+        self.rng = random.Random(seed)
+        self.bar = {("resident", 0): Barrier("resident", 1), ("done", 0): Barrier("done", 1),
+                    ("a_ready", 0): Barrier("a_ready", COMPUTE)}
+        for b in range(2):
+            self.bar["scores_full", b] = Barrier(f"scores_full{b}", 1)
+            self.bar["operands_ready", b] = Barrier(f"operands_ready{b}", COMPUTE)
+        for s in range(STAGES):
+            self.bar["stage_full", s] = Barrier(f"stage_full{s}", 1)
+            self.bar["stage_empty", s] = Barrier(f"stage_empty{s}", 1)
+        self.tma, self.pipe = [], []
+        self.shared_item = None                # item whose K/V the shared-memory pair holds
+        self.installed = {}                    # item -> warps that copied it to tensor memory
+        self.stage_content = [None] * STAGES
+        self.stage_reads = [0] * STAGES        # MMA groups issued on the stage, not yet executed
+        self.scores_done, self.scores_started, self.grads_done = set(), set(), set()
+        self.written = {}                      # sub-step count -> warps that wrote probabilities
+        self.first_count = [sum(items[:i]) for i in range(len(items))]
+
+    def wait(self, kind, index, parity, phase):
+        bar = self.bar[kind, index]
+        while not bar.passed(parity & 1):
+            yield
+        need(bar.completed > phase, f"aliased wait on {bar.name}: meant phase {phase}, "
+                                    f"{bar.completed} completed")
+
+    def producer(self):
+        stage, phase = 0, 0
+        uses = [0] * STAGES
+        for round_, steps in enumerate(self.items):
+            if round_ > 0:
+                yield from self.wait("a_ready", 0, (round_ - 1) & 1, round_ - 1)
+                need(self.installed.get(round_ - 1, 0) == COMPUTE,
+                     "K/V in shared memory replaced before every warp copied them")
+            self.shared_item = None
+            self.tma.append(("resident", round_))
+            for h in range(steps):
+                yield from self.wait("stage_empty", stage, phase ^ 1, uses[stage] - 1)
+                need(self.stage_reads[stage] == 0, f"stage {stage} refilled while still read")
+                self.stage_content[stage] = None
+                self.tma.append(("stage", (stage, self.first_count[round_] + h)))
+                uses[stage] += 1
+                stage += 1
+                if stage == STAGES:
+                    stage, phase = 0, phase ^ 1
+                yield
+
+    def mma_warp(self):
+        before = 0
+        for round_, steps in enumerate(self.items):
+            yield from self.wait("a_ready", 0, round_ & 1, round_)
+
+            def issue_scores(g):
+                count = before + g
+                stage = count % STAGES
+                yield from self.wait("stage_full", stage, (count // STAGES) & 1, count // STAGES)
+                need(self.stage_content[stage] == count, f"stage {stage} holds the wrong sub-step")
+                self.stage_reads[stage] += 1
+                self.pipe.append(("scores", count, stage, round_))
+                self.pipe.append(("commit", ("scores_full", g & 1)))
+
+            yield from issue_scores(0)
+            for h in range(steps):
+                b = h & 1
+                count = before + h
+                if h + 1 < steps:
+                    yield from issue_scores(h + 1)
+                yield from self.wait("operands_ready", b, (count >> 1) & 1, count >> 1)
+                stage = count % STAGES
+                self.stage_reads[stage] += 1
+                self.pipe.append(("grads", count, stage))
+                self.pipe.append(("commit", ("stage_empty", stage)))
+                if h + 1 == steps:
+                    self.pipe.append(("commit", ("done", 0)))
+                yield
+            before += steps
+
+    def compute_warp(self, index):
+        def install(round_):
+            yield from self.wait("resident", 0, round_ & 1, round_)
+            need(self.shared_item == round_, "the wrong item's K/V copied to tensor memory")
+            if round_ > 0:
+                last = self.first_count[round_ - 1] + self.items[round_ - 1] - 1
+                need(last in self.scores_done,
+                     "K/V in tensor memory replaced before the item's last scores")
+            self.installed[round_] = self.installed.get(round_, 0) + 1
+            self.bar["a_ready", 0].arrive()
+
+        before = 0
+        yield from install(0)
+        for round_, steps in enumerate(self.items):
+            for h in range(steps):
+                b = h & 1
+                count = before + h
+                stage = count % STAGES
+                yield from self.wait("scores_full", b, (count >> 1) & 1, count >> 1)
+                need(count in self.scores_done and (count + 2) not in self.scores_started,
+                     f"scores of sub-step {count} read while absent or overwritten")
+                yield from self.wait("stage_full", stage, (count // STAGES) & 1, count // STAGES)
+                need(self.stage_content[stage] == count, "statistics of the wrong sub-step read")
+                yield
+                need((count + 2) not in self.scores_started, "probabilities written over newer scores")
+                self.written[count] = self.written.get(count, 0) + 1
+                self.bar["operands_ready", b].arrive()
+                yield
+            before += steps
+            if round_ + 1 < len(self.items):
+                yield from install(round_ + 1)
+            yield from self.wait("done", 0, round_ & 1, round_)
+            need((before - 1) in self.grads_done, "gradients written out before the last MMAs")
+            yield
+
+    def run_tma(self):
+        kind, payload = self.tma.pop(self.rng.randrange(len(self.tma)))
+        if kind == "resident":
+            self.shared_item = payload
+            self.bar["resident", 0].arrive()
+        else:
+            stage, count = payload
+            self.stage_content[stage] = count
+            self.bar["stage_full", stage].arrive()
+
+    def run_pipe(self):
+        op = self.pipe.pop(0)
+        if op[0] == "commit":
+            self.bar[op[1]].arrive()
+        elif op[0] == "scores":
+            _, count, stage, round_ = op
+            need(self.installed.get(round_, 0) == COMPUTE and round_ + 1 not in self.installed,
+                 f"scores of sub-step {count} read K/V that are not (or no longer) the item's")
+            need(count < 2 or (count - 2) in self.grads_done,
+                 f"scores of sub-step {count} overwrite probabilities still to be read")
+            self.scores_started.add(count)
+            self.scores_done.add(count)
+            self.stage_reads[stage] -= 1
+        else:
+            _, count, stage = op
+            need(self.written.get(count, 0) == COMPUTE, f"gradient MMAs of {count} before all warps wrote")
+            self.grads_done.add(count)
+            self.stage_reads[stage] -= 1
+
+    def run(self):
+        roles = {"producer": self.producer(), "mma": self.mma_warp()}
+        for index in range(COMPUTE):
+            roles[f"compute{index}"] = self.compute_warp(index)
+        schedule(self.rng, roles, [(self.tma, self.run_tma), (self.pipe, self.run_pipe)])
+        need(not self.tma and len(self.grads_done) == sum(self.items), "work left over at the end")
+
+
+BACKWARD_ITEMS = [[2], [16], [2, 2, 2], [16, 14, 2], [4, 8, 4, 2], [6, 6, 6]]
+
+
+@pytest.mark.parametrize("items", BACKWARD_ITEMS, ids=[str(i) for i in BACKWARD_ITEMS])
+def test_backward_protocol_holds_under_random_schedules(items):
+    for seed in range(40):
+        BackwardModel(items, seed).run()
